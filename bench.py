@@ -1,0 +1,337 @@
+"""Benchmark of the MoE layer forward + backward.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2] [--impl reference]
+
+One "step" is one forward + backward pass of the layer (router gate, top-k, softmax, routing sort, routed
+SwiGLU experts, gate-weighted combine; all gradients) over one batch of synthetic tokens.  At N = 1 the
+workload is the Mixtral-shaped configuration (8 experts, top-2, hidden 4096, intermediate 14336, 16384
+tokens, bf16).  At N > 1 the experts are sharded over the ranks (expert parallel), every rank keeps its
+own 16384 tokens (weak scaling) and rows travel by NCCL all-to-all.
+
+Prints ONE JSON line on rank 0.  `value` is TFLOP/s of routed-expert GEMM work (18*T*k*H*I per step) with the
+inputs resident in HBM; `e2e` is the same metric with host buffers (pinned) copied in and results copied
+out inside the timed region; `roofline` describes the tcgen05 grouped-GEMM kernel (all six launches of a
+step) against the measured bf16 peak; `cpu_baseline` times the CPU port of the reference torch path on a
+bounded token sample.  `--impl reference` runs only that CPU path and prints its own line.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from kernel_hyperdrive_b200 import synthetic  # noqa: E402
+
+METRIC = "moe_layer_fwd_bwd_tflops"
+UNIT = "TFLOP/s"
+FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the grouped-GEMM kernel from an ncu capture,
+# keyed by workload; None until a capture of that workload has been summarised under profiles/.
+NCU_TRAFFIC_BYTES_PER_STEP = {}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.samples:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------------------
+# CPU arm: the port of the reference torch path (oracle) on the host cores, bounded token sample
+# --------------------------------------------------------------------------------------------------
+
+
+def cpu_reference_run(w: synthetic.MoEWorkload, steps: int, warmup: int, sample_tokens: int, weights=None):
+    """Times forward + backward of the reference torch formulation on CPU in the workload's dtype.
+
+    Returns (TFLOP/s of the sample, seconds per step, description of the sample, threads used).
+    """
+    from oracle import moe_oracle as orc  # the one place the benchmark executes the oracle
+
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    dtype = synthetic.TORCH_DTYPES[w.dtype]
+    ws = synthetic.scaled(w, tokens=sample_tokens)
+    if weights is None:
+        # N(0, std) blocks drawn once per projection; expert e uses the block rolled by 17*e rows (distinct
+        # matrices with the same distribution) so that start-up stays short on the host
+        g = torch.Generator().manual_seed(0)
+        E, H, I = w.num_experts, w.hidden, w.intermediate
+        fc = (torch.randn(2 * I, H, generator=g) * w.weight_std).to(dtype)
+        pj = (torch.randn(H, I, generator=g) * w.weight_std).to(dtype)
+        weights = dict(
+            gate=(torch.randn(E, H, generator=g) * w.weight_std).to(dtype),
+            w_fc=torch.stack([fc.roll(17 * e, 0) for e in range(E)]),
+            w_proj=torch.stack([pj.roll(17 * e, 0) for e in range(E)]),
+        )
+    x, gy = synthetic.make_tokens(ws, 0)
+    x, gy = x.to(dtype), gy.to(dtype)
+    rw, sel = synthetic.make_routing(ws, x.float(), weights["gate"].float(), 0)
+    rw = rw.to(dtype)
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        orc.experts_with_grads(x, weights["w_fc"], weights["w_proj"], rw, sel, gy)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    sec = sum(times) / len(times)
+    flops = 18.0 * sample_tokens * w.top_k * w.hidden * w.intermediate
+    sample = f"{sample_tokens} of {w.tokens} tokens, all {w.num_experts} experts, full H={w.hidden} I={w.intermediate}, {w.dtype}, {steps} timed passes"
+    return flops / sec / 1e12, sec, sample, threads
+
+
+def run_reference_arm(args, w):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warmup = max(1, min(args.steps, 3)), min(args.warmup, 1)
+    val, sec, sample, threads = cpu_reference_run(w, steps, warmup, args.cpu_sample_tokens)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
+        "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
+        "config": workload_config(w, args.gpus),
+        "tokens_per_s": args.cpu_sample_tokens / sec,
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(w, n_gpus):
+    return {
+        "workload": f"{w.name}: {w.num_experts} experts top-{w.top_k}, hidden {w.hidden}, SwiGLU intermediate {w.intermediate}, {w.tokens} tokens per GPU, {w.dtype}, routing={w.routing}",
+        "tokens_per_gpu": w.tokens, "num_experts": w.num_experts, "top_k": w.top_k, "hidden": w.hidden, "intermediate": w.intermediate,
+        "parallelism": "single GPU" if n_gpus == 1 else f"expert parallel ep{n_gpus} (experts sharded, NCCL all-to-all dispatch/combine)",
+        "l2": "inputs_exceed_l2 (expert weights and activations are GBs, L2 is 126 MB)",
+    }
+
+
+# --------------------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------------------
+
+
+def run_gpu_arm(args, w):
+    import torch.distributed as dist
+
+    import kernel_hyperdrive_b200 as kh
+    from kernel_hyperdrive_b200 import _lib, scattermoe
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world} (launch with torch.distributed.run)"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    dtype = synthetic.TORCH_DTYPES[w.dtype]
+    E, k, H, I, T = w.num_experts, w.top_k, w.hidden, w.intermediate, w.tokens
+
+    if world > 1:
+        from kernel_hyperdrive_b200.expert_parallel import MoE_B200_EP
+
+        layer = MoE_B200_EP(E, k, H, I, kh.swiglu_unchunked_torch, True, False, w.weight_std, group=dist.group.WORLD, device=dev, dtype=dtype, seed=0)
+    else:
+        torch.manual_seed(0)
+        with torch.device(dev):
+            layer = kh.MoE_B200(E, k, H, I, kh.swiglu_unchunked_torch, True, False, w.weight_std)
+        layer = layer.to(dtype)
+    params = [p for p in layer.parameters()]
+
+    gen = torch.Generator().manual_seed(1000 + rank)
+    x_host = torch.randn(T, H, generator=gen).to(dtype).pin_memory()
+    g_host = torch.randn(T, H, generator=gen).to(dtype).pin_memory()
+    y_host = torch.empty(T, H, dtype=dtype).pin_memory()
+    dx_host = torch.empty(T, H, dtype=dtype).pin_memory()
+    x_dev = x_host.to(dev).requires_grad_(True)
+    g_dev = g_host.to(dev)
+
+    def step_resident():
+        for p in params:
+            p.grad = None
+        x_dev.grad = None
+        y, _ = layer(x_dev)
+        y.backward(g_dev)
+        return y
+
+    def step_e2e():
+        for p in params:
+            p.grad = None
+        x = x_host.to(dev, non_blocking=True).requires_grad_(True)
+        g = g_host.to(dev, non_blocking=True)
+        y, _ = layer(x)
+        y.backward(g)
+        y_host.copy_(y.detach(), non_blocking=True)
+        dx_host.copy_(x.grad, non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            fn()
+        end.record()
+        barrier()
+        ms = torch.tensor([start.elapsed_time(end)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item()
+
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    _lib.check_status(dev)
+
+    sink = []
+    scattermoe.set_timing_sink(sink)
+    launches0 = _lib.launch_count()
+    with ClockSampler(local_rank) as clocks:
+        total_ms = timed(step_resident, args.steps)
+    launches = _lib.launch_count() - launches0
+    scattermoe.set_timing_sink(None)
+    torch.cuda.synchronize()
+    per_kernel = {}
+    for name, s, e in sink:
+        per_kernel.setdefault(name, []).append(s.elapsed_time(e))
+    clock_summary = clocks.summary()
+
+    for _ in range(2):
+        step_e2e()
+    e2e_ms = timed(step_e2e, args.steps)
+    _lib.check_status(dev)
+
+    flops_step = w.flops_fwd_bwd() * world  # every rank brings T tokens
+    ms_step = total_ms / args.steps
+    value = flops_step / (ms_step * 1e-3) / 1e12
+    e2e_value = flops_step / (e2e_ms / args.steps * 1e-3) / 1e12
+    peaks, peak_kind = measured_peaks()
+    peak = peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"])
+
+    gemm_ms = {n: sum(v) / len(v) for n, v in per_kernel.items()}
+    gemm_total_ms = sum(gemm_ms.values())
+    local_flops = w.flops_fwd_bwd()
+    achieved = local_flops / (gemm_total_ms * 1e-3) / 1e12 if gemm_total_ms > 0 else None
+    share = {"up_forward": 4, "down_forward": 2, "down_dgrad": 2, "down_wgrad": 2, "up_wgrad": 4, "up_dgrad": 4}
+    per_launch = {n: {"ms": ms, "tflops": (share[n] / 18.0) * local_flops / (ms * 1e-3) / 1e12} for n, ms in gemm_ms.items() if n in share}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
+        "config": workload_config(w, world),
+        "tokens_per_s": T * world / (ms_step * 1e-3),
+        "frac_of_bf16_peak_burst": value / world / peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]),
+        "frac_of_bf16_peak_sustained": value / world / peak,
+        "clocks": clock_summary,
+        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": 2 * x_host.numel() * x_host.element_size(), "d2h_bytes_per_step": 2 * y_host.numel() * y_host.element_size()},
+        "gpu_launches": launches,
+        "roofline": {
+            "bound": "tensor", "kernel": "umma_grouped_kernel (6 launches per step)", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+            "frac": (achieved / peak) if achieved else None, "peak_kind": f"bf16_tflops_sustained of {peak_kind}",
+            "traffic": NCU_TRAFFIC_BYTES_PER_STEP.get(w.name), "per_launch": per_launch, "gemm_ms_per_step": gemm_total_ms,
+        },
+    }
+
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu_w = dict(gate=layer.gate.weight.detach().cpu(), w_fc=layer.c_fc.weight.detach().cpu(), w_proj=layer.c_proj.weight.detach().cpu())
+        val, sec, sample, threads = cpu_reference_run(w, 1, 1, args.cpu_sample_tokens, weights=cpu_w)
+        line["cpu_baseline"] = {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(synthetic.WORKLOADS))
+    ap.add_argument("--tokens", type=int, default=None, help="override tokens per GPU (profiling on a small case)")
+    ap.add_argument("--cpu-sample-tokens", type=int, default=256)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    w = synthetic.WORKLOADS[args.workload]
+    if args.tokens:
+        w = synthetic.scaled(w, tokens=args.tokens)
+    if args.impl == "reference":
+        run_reference_arm(args, w)
+    else:
+        run_gpu_arm(args, w)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,15 @@
+"""B200-native (sm_100a) implementation of the scattermoe MoE layer path."""
+
+from .custom_op import set_cute_tracing
+from .ops import combine, contiguous_count_cute, group, group_bwd_W, scatter2scatter, swiglu_unchunked_cute, swiglu_unchunked_torch
+from .scattermoe import (
+    Experts_B200,
+    Experts_Torch,
+    Experts_Triton,
+    MoE_B200,
+    MoE_Torch,
+    MoE_Triton,
+    fused_swiglu_experts,
+    route,
+    scattered_experts,
+)

@@ -1,0 +1,164 @@
+"""Loader of the C-ABI library `libb200moe.so` (declared in include/b200moe.h) and its build recipe.
+
+The library is the only compute path of this package: if it is missing, importing an operator raises;
+there is no CPU or PyTorch fallback.  `build()` compiles it in-tree with nvcc for sm_100a (works without
+a GPU); loading it needs only the CUDA runtime it links against.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+import threading
+
+import torch
+
+PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(PKG_DIR, "csrc")
+LIB_PATH = os.path.join(PKG_DIR, "libb200moe.so")
+SOURCES = ["api.cu", "routing.cu", "rowops.cu", "simt_gemm.cu", "umma_gemm.cu"]
+HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(PKG_DIR, "..", "include", "b200moe.h")]
+
+F32, BF16, F16 = 0, 1, 2
+ENGINE_AUTO, ENGINE_SIMT, ENGINE_UMMA = 0, 1, 2
+DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
+
+_lock = threading.Lock()
+_lib = None
+
+
+def nvcc_command(out: str = LIB_PATH, extra: list[str] | None = None) -> list[str]:
+    nvcc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
+    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared", "--expt-relaxed-constexpr"]
+    cmd += extra or []
+    cmd += ["-o", out] + [os.path.join(CSRC, s) for s in SOURCES]
+    return cmd
+
+
+def needs_build() -> bool:
+    if not os.path.exists(LIB_PATH):
+        return True
+    built = os.path.getmtime(LIB_PATH)
+    deps = [os.path.join(CSRC, s) for s in SOURCES] + HEADERS + [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cuh")]
+    return any(os.path.exists(d) and os.path.getmtime(d) > built for d in deps)
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile the library in-tree for sm_100a.  Returns the path of the shared object."""
+    if force or needs_build():
+        tmp = LIB_PATH + f".tmp{os.getpid()}"
+        proc = subprocess.run(nvcc_command(tmp, ["-Xptxas", "-v"] if verbose else None), capture_output=True, text=True)
+        if proc.returncode != 0:
+            raise RuntimeError("nvcc failed:\n" + proc.stdout + proc.stderr)
+        os.replace(tmp, LIB_PATH)
+        if verbose:
+            print(proc.stderr)
+    return LIB_PATH
+
+
+def _declare(lib):
+    c = ctypes
+    vp, i32, i64 = c.c_void_p, c.c_int, c.c_int64
+    sig = {
+        "b200moe_version": (i32, []),
+        "b200moe_error_string": (c.c_char_p, [i32]),
+        "b200moe_last_error_detail": (c.c_char_p, []),
+        "b200moe_set_engine": (i32, [i32]),
+        "b200moe_launch_count": (i64, []),
+        "b200moe_check_status": (i32, [vp, vp]),
+        "b200moe_contiguous_count": (i32, [vp, i32, i64, vp, i32, vp]),
+        "b200moe_padded_rows_cap": (i64, [i64, i32]),
+        "b200moe_route_workspace_bytes": (i64, [i64, i32]),
+        "b200moe_route": (i32, [vp, i64, i32, i32, vp, vp, vp, vp, vp, vp, i64, vp, i64, vp, vp]),
+        "b200moe_scatter2scatter_workspace_bytes": (i64, [i64, i32]),
+        "b200moe_scatter2scatter": (i32, [vp, i64, vp, i64, i64, i64, vp, vp, vp, i64, i64, i32, i32, i32, i32, i32, i32, i32, vp, i64, vp, vp]),
+        "b200moe_group_bwd_W": (i32, [vp, i64, vp, i64, vp, vp, i64, i64, i64, i64, i32, i32, i32, i32, vp, vp]),
+        "b200moe_group": (i32, [vp, i64, vp, vp, i64, vp, i32, i64, i32, i32, vp]),
+        "b200moe_combine": (i32, [vp, i64, vp, vp, i64, i64, i32, i32, i32, vp]),
+        "b200moe_swiglu_unchunked_forward": (i32, [vp, i64, vp, i64, i64, i32, i32, vp]),
+        "b200moe_swiglu_unchunked_backward": (i32, [vp, i64, vp, i64, vp, i64, i64, i32, i32, vp]),
+        "b200moe_up_forward": (i32, [vp, i64, vp, vp, vp, vp, vp, i64, i32, i32, i32, i64, i32, vp, vp]),
+        "b200moe_down_forward": (i32, [vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, i64, i32, vp, vp]),
+        "b200moe_down_dgrad": (i32, [vp, i64, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i64, i32, vp, vp]),
+        "b200moe_wgrad": (i32, [vp, i64, vp, vp, i64, vp, vp, vp, i32, i32, i32, i64, i32, vp, vp]),
+        "b200moe_up_dgrad": (i32, [vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, i64, i32, vp, vp]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(lib, name)  # AttributeError here means the library does not export a declared symbol
+        fn.restype = res
+        fn.argtypes = args
+    return sig
+
+
+EXPORTED = None
+
+
+def lib():
+    """The loaded library.  Raises if it has not been built: there is no other compute path."""
+    global _lib, EXPORTED
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                if not os.path.exists(LIB_PATH):
+                    raise RuntimeError(
+                        f"{LIB_PATH} is missing: build it with `python -c 'import __graft_entry__ as g; g.build()'` "
+                        "(nvcc, sm_100a).  This package has no CPU or PyTorch fallback."
+                    )
+                handle = ctypes.CDLL(LIB_PATH)
+                EXPORTED = _declare(handle)
+                _lib = handle
+    return _lib
+
+
+class B200MoEError(RuntimeError):
+    pass
+
+
+def check(code: int, what: str = "") -> None:
+    if code != 0:
+        L = lib()
+        msg = L.b200moe_error_string(code).decode()
+        detail = L.b200moe_last_error_detail().decode()
+        raise B200MoEError(f"{what}: {msg} ({code}): {detail}")
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def stream_ptr(device=None) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    try:
+        return DTYPE_CODE[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {t.dtype}: expected float32, bfloat16 or float16") from None
+
+
+_status = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """One int32 per device that kernels write when they give up on a bounded wait or see a bad index."""
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    t = _status.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _status[key] = t
+    return t
+
+
+def check_status(device: torch.device) -> None:
+    """Synchronises the current stream and raises if a kernel reported a device-side failure."""
+    check(lib().b200moe_check_status(ptr(status_word(device)), stream_ptr(device)), "device status")
+
+
+def set_engine(engine: int) -> int:
+    return lib().b200moe_set_engine(engine)
+
+
+def launch_count() -> int:
+    return lib().b200moe_launch_count()

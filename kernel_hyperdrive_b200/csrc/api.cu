@@ -1,0 +1,395 @@
+// extern "C" entry points of the grouped-GEMM operators and of the fused layer path, argument checks,
+// engine selection and the host-side error plumbing.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+
+#include "common.cuh"
+
+namespace b200moe {
+
+static thread_local char g_detail[512] = "";
+static std::atomic<int64_t> g_launches{0};
+static std::atomic<int> g_engine{B200MOE_ENGINE_AUTO};
+
+void set_error_detail(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_detail, sizeof(g_detail), fmt, ap);
+    va_end(ap);
+}
+
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+int check_launch(const char* what) {
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) {
+        set_error_detail("%s: %s", what, cudaGetErrorString(err));
+        return B200MOE_ERR_LAUNCH;
+    }
+    return B200MOE_OK;
+}
+
+int current_engine() { return g_engine.load(); }
+
+int launch_offsets_from_sorted(const int64_t* sorted, int64_t M, int E, int64_t* offsets, cudaStream_t stream);
+int launch_make_row_maps(const int64_t* idx, int64_t M, int fan_out, int32_t* src_map, int32_t* dst_map,
+                         cudaStream_t stream);
+
+namespace {
+
+bool dtype_ok(int dtype) { return dtype == B200MOE_F32 || dtype == B200MOE_BF16 || dtype == B200MOE_F16; }
+
+// Picks the engine for one problem; returns <0 on error, else 0 (SIMT) or 1 (UMMA).
+template <typename G, typename F>
+int pick_engine(const G& g, int dtype, F&& supported, const char* what) {
+    int eng = current_engine();
+    if (eng == B200MOE_ENGINE_SIMT) return 0;
+    bool ok = dtype != B200MOE_F32 && supported(g, dtype);
+    if (eng == B200MOE_ENGINE_UMMA) {
+        if (!ok) {
+            set_error_detail("%s: shape/dtype not handled by the tcgen05 engine", what);
+            return B200MOE_ERR_LAYOUT;
+        }
+        return 1;
+    }
+    return ok ? 1 : 0;
+}
+
+int run_row_gemm(const RowGemm& g, int dtype, int32_t* status, cudaStream_t stream, const char* what) {
+    int eng = pick_engine(g, dtype, umma_row_gemm_supported, what);
+    if (eng < 0) return eng;
+    return eng ? umma_row_gemm(g, dtype, status, stream) : simt_row_gemm(g, dtype, stream);
+}
+
+int run_w_gemm(const WGemm& g, int dtype, int32_t* status, cudaStream_t stream, const char* what) {
+    int eng = pick_engine(g, dtype, umma_w_gemm_supported, what);
+    if (eng < 0) return eng;
+    return eng ? umma_w_gemm(g, dtype, status, stream) : simt_w_gemm(g, dtype, stream);
+}
+
+}  // namespace
+}  // namespace b200moe
+
+using namespace b200moe;
+
+extern "C" int b200moe_version(void) { return 100; }
+
+extern "C" const char* b200moe_error_string(int code) {
+    switch (code) {
+        case B200MOE_OK:
+            return "ok";
+        case B200MOE_ERR_ARG:
+            return "bad argument";
+        case B200MOE_ERR_DTYPE:
+            return "unknown dtype";
+        case B200MOE_ERR_LAYOUT:
+            return "unsupported stride or alignment";
+        case B200MOE_ERR_WORKSPACE:
+            return "workspace too small";
+        case B200MOE_ERR_LAUNCH:
+            return "CUDA launch error";
+        case B200MOE_ERR_UNSUPPORTED:
+            return "unsupported problem size";
+        case B200MOE_ERR_DRIVER:
+            return "CUDA driver entry point unavailable";
+        case B200MOE_ERR_DEVICE:
+            return "device-side failure (bounded wait expired or index out of range)";
+        default:
+            return "unknown error code";
+    }
+}
+
+extern "C" const char* b200moe_last_error_detail(void) { return g_detail; }
+
+extern "C" int b200moe_set_engine(int engine) {
+    if (engine < B200MOE_ENGINE_AUTO || engine > B200MOE_ENGINE_UMMA) return B200MOE_ERR_ARG;
+    return g_engine.exchange(engine);
+}
+
+extern "C" int64_t b200moe_launch_count(void) { return g_launches.load(); }
+
+extern "C" int b200moe_check_status(int32_t* status_device, b200moe_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    B200MOE_REQUIRE(status_device != nullptr, B200MOE_ERR_ARG, "check_status: NULL status");
+    int32_t v = 0;
+    if (cudaMemcpyAsync(&v, status_device, sizeof(v), cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
+        cudaStreamSynchronize(stream) != cudaSuccess)
+        return check_launch("check_status copy");
+    if (v != 0) {
+        cudaMemsetAsync(status_device, 0, sizeof(v), stream);
+        set_error_detail("device status word = %d", v);
+        return B200MOE_ERR_DEVICE;
+    }
+    return B200MOE_OK;
+}
+
+// ---- reference-signature operators ---------------------------------------------------------------
+
+extern "C" int64_t b200moe_scatter2scatter_workspace_bytes(int64_t M, int E) {
+    // offsets int64 (E) + two int32 row maps (M), each region 16-byte aligned
+    int64_t off = ((int64_t)E * 8 + 15) / 16 * 16;
+    int64_t map = (M * 4 + 15) / 16 * 16;
+    return off + 2 * map;
+}
+
+extern "C" int b200moe_scatter2scatter(const void* X, int64_t ldx, const void* W, int64_t w_se, int64_t w_sk,
+                                       int64_t w_sn, const int64_t* sorted_expert_idxs,
+                                       const int64_t* sorted_scattered_idxs, void* out, int64_t ldo, int64_t M, int K,
+                                       int N, int E, int fan_out, int x_grouped, int y_grouped, int dtype,
+                                       void* workspace, int64_t workspace_bytes, int32_t* status,
+                                       b200moe_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    B200MOE_REQUIRE(dtype_ok(dtype), B200MOE_ERR_DTYPE, "scatter2scatter: dtype %d", dtype);
+    B200MOE_REQUIRE(M >= 0 && K >= 0 && N >= 0 && fan_out > 0, B200MOE_ERR_ARG, "scatter2scatter: bad sizes");
+    B200MOE_REQUIRE(E > 0 && E <= kMaxExperts, B200MOE_ERR_UNSUPPORTED, "scatter2scatter: E=%d", E);
+    if (M == 0 || N == 0) return B200MOE_OK;
+    B200MOE_REQUIRE(X && W && out && sorted_expert_idxs && sorted_scattered_idxs, B200MOE_ERR_ARG,
+                    "scatter2scatter: NULL pointer");
+    B200MOE_REQUIRE(w_sk == 1 || w_sn == 1 || K == 1 || N == 1, B200MOE_ERR_LAYOUT,
+                    "scatter2scatter: W needs unit stride along K or N");
+    B200MOE_REQUIRE(workspace && workspace_bytes >= b200moe_scatter2scatter_workspace_bytes(M, E),
+                    B200MOE_ERR_WORKSPACE, "scatter2scatter: workspace too small");
+    char* ws = (char*)workspace;
+    int64_t* offsets = (int64_t*)ws;
+    int64_t off_bytes = ((int64_t)E * 8 + 15) / 16 * 16, map_bytes = (M * 4 + 15) / 16 * 16;
+    int32_t* src_map = (int32_t*)(ws + off_bytes);
+    int32_t* dst_map = (int32_t*)(ws + off_bytes + map_bytes);
+    int rc = launch_offsets_from_sorted(sorted_expert_idxs, M, E, offsets, stream);
+    if (rc) return rc;
+    bool need_src = !x_grouped, need_dst = !y_grouped;
+    if (need_src || need_dst) {
+        rc = launch_make_row_maps(sorted_scattered_idxs, M, fan_out, need_src ? src_map : nullptr,
+                                  need_dst ? dst_map : nullptr, stream);
+        if (rc) return rc;
+    }
+    RowGemm g{};
+    g.A = X;
+    g.lda = ldx;
+    g.a_map = need_src ? src_map : nullptr;
+    g.W = W;
+    g.w_se = w_se;
+    g.w_sk = w_sk;
+    g.w_sn = w_sn;
+    g.out = out;
+    g.ldo = ldo;
+    g.o_map = need_dst ? dst_map : nullptr;
+    g.offsets = offsets;
+    g.padded = 0;
+    g.rows_cap = M;
+    g.K = K;
+    g.N = N;
+    g.E = E;
+    g.epi = EPI_STORE;
+    return run_row_gemm(g, dtype, status, stream, "scatter2scatter");
+}
+
+extern "C" int b200moe_group_bwd_W(const void* DY, int64_t lddy, const void* X, int64_t ldx,
+                                   const int64_t* expert_offsets, void* DW, int64_t d_se, int64_t d_sk, int64_t d_sn,
+                                   int64_t M, int K, int N, int E, int dtype, int32_t* status,
+                                   b200moe_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    B200MOE_REQUIRE(dtype_ok(dtype), B200MOE_ERR_DTYPE, "group_bwd_W: dtype %d", dtype);
+    B200MOE_REQUIRE(M >= 0 && K >= 0 && N >= 0, B200MOE_ERR_ARG, "group_bwd_W: bad sizes");
+    B200MOE_REQUIRE(E > 0 && E <= kMaxExperts, B200MOE_ERR_UNSUPPORTED, "group_bwd_W: E=%d", E);
+    if (K == 0 || N == 0) return B200MOE_OK;
+    B200MOE_REQUIRE(DW && expert_offsets && (M == 0 || (DY && X)), B200MOE_ERR_ARG, "group_bwd_W: NULL pointer");
+    // DW[e][kk, n] = sum X[r, kk] * DY[r, n].  The operand whose feature index has unit stride in DW becomes
+    // the column operand of the engine.
+    WGemm g{};
+    if (d_sk == 1 && d_sn != 1) {
+        g.P = DY, g.ldp = lddy, g.Mout = N, g.d_sm = d_sn;
+        g.Q = X, g.ldq = ldx, g.Nout = K, g.d_sn = d_sk;
+    } else {
+        g.P = X, g.ldp = ldx, g.Mout = K, g.d_sm = d_sk;
+        g.Q = DY, g.ldq = lddy, g.Nout = N, g.d_sn = d_sn;
+    }
+    g.DW = DW;
+    g.d_se = d_se;
+    g.offsets = expert_offsets;
+    g.padded = 0;
+    g.rows_cap = M;
+    g.E = E;
+    return run_w_gemm(g, dtype, status, stream, "group_bwd_W");
+}
+
+// ---- fused layer path ----------------------------------------------------------------------------
+
+#define REQUIRE_COMMON(name)                                                                       \
+    B200MOE_REQUIRE(dtype_ok(dtype), B200MOE_ERR_DTYPE, name ": dtype %d", dtype);                  \
+    B200MOE_REQUIRE(E > 0 && E <= kMaxExperts, B200MOE_ERR_UNSUPPORTED, name ": E=%d", E);          \
+    B200MOE_REQUIRE(H > 0 && I > 0 && m_cap >= 0 && m_cap % kPadRows == 0, B200MOE_ERR_ARG,         \
+                    name ": bad H/I/m_cap (m_cap must be a multiple of 128)")
+
+extern "C" int b200moe_up_forward(const void* x, int64_t ldx, const void* w_fc, const int64_t* expert_offsets,
+                                  const int32_t* row_token, void* h, void* a, int64_t T, int H, int I, int E,
+                                  int64_t m_cap, int dtype, int32_t* status, b200moe_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    REQUIRE_COMMON("up_forward");
+    if (m_cap == 0) return B200MOE_OK;
+    B200MOE_REQUIRE(x && w_fc && expert_offsets && row_token && h && a && T >= 0, B200MOE_ERR_ARG,
+                    "up_forward: NULL pointer");
+    RowGemm g{};
+    g.A = x;
+    g.lda = ldx;
+    g.a_map = row_token;
+    g.W = w_fc;  // (E, 2I, H): element (e, kk, n) at e*2I*H + n*H + kk
+    g.w_se = (int64_t)2 * I * H;
+    g.w_sk = 1;
+    g.w_sn = H;
+    g.out = h;
+    g.ldo = 2 * (int64_t)I;
+    g.o_map = nullptr;
+    g.offsets = expert_offsets;
+    g.padded = 1;
+    g.rows_cap = m_cap;
+    g.K = H;
+    g.N = 2 * I;
+    g.E = E;
+    g.epi = EPI_SWIGLU;
+    g.out2 = a;
+    int eng = pick_engine(g, dtype, umma_row_gemm_supported, "up_forward");
+    if (eng < 0) return eng;
+    if (eng) return umma_row_gemm(g, dtype, status, stream);
+    g.epi = EPI_STORE;
+    int rc = simt_row_gemm(g, dtype, stream);
+    if (rc) return rc;
+    return launch_swiglu_forward(h, 2 * (int64_t)I, a, I, m_cap, I, dtype, stream);
+}
+
+extern "C" int b200moe_down_forward(const void* a, const void* w_proj, const int64_t* expert_offsets,
+                                    const int32_t* row_slot, const void* gates, void* y_expanded, int64_t ldy,
+                                    int64_t M, int H, int I, int E, int64_t m_cap, int dtype, int32_t* status,
+                                    b200moe_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    REQUIRE_COMMON("down_forward");
+    if (m_cap == 0 || M == 0) return B200MOE_OK;
+    B200MOE_REQUIRE(a && w_proj && expert_offsets && row_slot && y_expanded, B200MOE_ERR_ARG,
+                    "down_forward: NULL pointer");
+    RowGemm g{};
+    g.A = a;
+    g.lda = I;
+    g.a_map = nullptr;
+    g.W = w_proj;  // (E, H, I): element (e, kk, n) at e*H*I + n*I + kk
+    g.w_se = (int64_t)H * I;
+    g.w_sk = 1;
+    g.w_sn = I;
+    g.out = y_expanded;
+    g.ldo = ldy;
+    g.o_map = row_slot;
+    g.scale = gates;
+    g.offsets = expert_offsets;
+    g.padded = 1;
+    g.rows_cap = m_cap;
+    g.K = I;
+    g.N = H;
+    g.E = E;
+    g.epi = EPI_STORE;
+    return run_row_gemm(g, dtype, status, stream, "down_forward");
+}
+
+extern "C" int b200moe_down_dgrad(const void* grad_out, int64_t ldg, const void* w_proj,
+                                  const int64_t* expert_offsets, const int32_t* row_token, const int32_t* row_slot,
+                                  const void* gates, const void* h, void* dh, void* ag, float* d_gates, int64_t M,
+                                  int H, int I, int E, int64_t m_cap, int dtype, int32_t* status,
+                                  b200moe_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    REQUIRE_COMMON("down_dgrad");
+    if (m_cap == 0 || M == 0) return B200MOE_OK;
+    B200MOE_REQUIRE(grad_out && w_proj && expert_offsets && row_token && row_slot && h && dh && ag && d_gates,
+                    B200MOE_ERR_ARG, "down_dgrad: NULL pointer");
+    RowGemm g{};
+    g.A = grad_out;
+    g.lda = ldg;
+    g.a_map = row_token;
+    g.W = w_proj;  // reduction over H now: element (e, kk=h, n=i) at e*H*I + kk*I + n
+    g.w_se = (int64_t)H * I;
+    g.w_sk = I;
+    g.w_sn = 1;
+    g.out = dh;
+    g.ldo = 2 * (int64_t)I;
+    g.o_map = nullptr;
+    g.offsets = expert_offsets;
+    g.padded = 1;
+    g.rows_cap = m_cap;
+    g.K = H;
+    g.N = I;
+    g.E = E;
+    g.epi = EPI_DGRAD_DOWN;
+    g.out2 = ag;
+    g.h = h;
+    g.d_gates = d_gates;
+    g.g_map = row_slot;
+    g.scale = gates;
+    int eng = pick_engine(g, dtype, umma_row_gemm_supported, "down_dgrad");
+    if (eng < 0) return eng;
+    if (eng) {
+        if (cudaMemsetAsync(d_gates, 0, (size_t)M * sizeof(float), stream) != cudaSuccess)
+            return check_launch("down_dgrad memset");
+        return umma_row_gemm(g, dtype, status, stream);
+    }
+    // CUDA-core engine: u into the ag buffer, then the element-wise tail
+    g.epi = EPI_STORE;
+    g.out = ag;
+    g.ldo = I;
+    g.scale = nullptr;
+    int rc = simt_row_gemm(g, dtype, stream);
+    if (rc) return rc;
+    return launch_dgrad_down_post(h, dh, ag, row_slot, gates, d_gates, m_cap, I, dtype, stream);
+}
+
+extern "C" int b200moe_wgrad(const void* P, int64_t ldp, const int32_t* p_map, const void* Q, int64_t ldq,
+                             const int32_t* q_map, const int64_t* expert_offsets, void* DW, int n_out, int n_in, int E,
+                             int64_t m_cap, int dtype, int32_t* status, b200moe_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    B200MOE_REQUIRE(dtype_ok(dtype), B200MOE_ERR_DTYPE, "wgrad: dtype %d", dtype);
+    B200MOE_REQUIRE(E > 0 && E <= kMaxExperts, B200MOE_ERR_UNSUPPORTED, "wgrad: E=%d", E);
+    B200MOE_REQUIRE(n_out > 0 && n_in > 0 && m_cap >= 0, B200MOE_ERR_ARG, "wgrad: bad sizes");
+    B200MOE_REQUIRE(P && Q && DW && expert_offsets, B200MOE_ERR_ARG, "wgrad: NULL pointer");
+    WGemm g{};
+    g.P = P;
+    g.ldp = ldp;
+    g.p_map = p_map;
+    g.Q = Q;
+    g.ldq = ldq;
+    g.q_map = q_map;
+    g.DW = DW;
+    g.d_se = (int64_t)n_out * n_in;
+    g.d_sm = n_in;
+    g.d_sn = 1;
+    g.offsets = expert_offsets;
+    g.padded = 1;
+    g.rows_cap = m_cap;
+    g.Mout = n_out;
+    g.Nout = n_in;
+    g.E = E;
+    return run_w_gemm(g, dtype, status, stream, "wgrad");
+}
+
+extern "C" int b200moe_up_dgrad(const void* dh, const void* w_fc, const int64_t* expert_offsets,
+                                const int32_t* row_slot, void* dx_expanded, int64_t ldd, int64_t M, int H, int I,
+                                int E, int64_t m_cap, int dtype, int32_t* status, b200moe_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    REQUIRE_COMMON("up_dgrad");
+    if (m_cap == 0 || M == 0) return B200MOE_OK;
+    B200MOE_REQUIRE(dh && w_fc && expert_offsets && row_slot && dx_expanded, B200MOE_ERR_ARG, "up_dgrad: NULL pointer");
+    RowGemm g{};
+    g.A = dh;
+    g.lda = 2 * (int64_t)I;
+    g.a_map = nullptr;
+    g.W = w_fc;  // reduction over 2I: element (e, kk, n=h) at e*2I*H + kk*H + n
+    g.w_se = (int64_t)2 * I * H;
+    g.w_sk = H;
+    g.w_sn = 1;
+    g.out = dx_expanded;
+    g.ldo = ldd;
+    g.o_map = row_slot;
+    g.offsets = expert_offsets;
+    g.padded = 1;
+    g.rows_cap = m_cap;
+    g.K = 2 * I;
+    g.N = H;
+    g.E = E;
+    g.epi = EPI_STORE;
+    return run_row_gemm(g, dtype, status, stream, "up_dgrad");
+}

@@ -1,0 +1,124 @@
+// Shared definitions of the b200moe CUDA sources: element-type helpers, the two grouped-GEMM problem
+// descriptions every engine consumes, and the host-side error plumbing.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/b200moe.h"
+
+namespace b200moe {
+
+constexpr int kMaxExperts = B200MOE_MAX_EXPERTS;
+constexpr int kPadRows = 128;  // every expert segment of the padded grouped order starts at a multiple of this
+
+// ---- host-side error plumbing -------------------------------------------------------------------
+void set_error_detail(const char* fmt, ...);
+void count_launch(int n = 1);
+int check_launch(const char* what);  // cudaGetLastError -> B200MOE_ERR_LAUNCH with detail
+
+#define B200MOE_REQUIRE(cond, code, ...)            \
+    do {                                            \
+        if (!(cond)) {                              \
+            ::b200moe::set_error_detail(__VA_ARGS__); \
+            return (code);                          \
+        }                                           \
+    } while (0)
+
+// ---- element types ------------------------------------------------------------------------------
+template <typename T>
+struct Elem;
+template <>
+struct Elem<float> {
+    static __device__ __forceinline__ float to_f(float v) { return v; }
+    static __device__ __forceinline__ float from_f(float v) { return v; }
+};
+template <>
+struct Elem<__nv_bfloat16> {
+    static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+    static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
+};
+template <>
+struct Elem<__half> {
+    static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+    static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
+};
+
+static inline int dtype_size(int dtype) { return dtype == B200MOE_F32 ? 4 : 2; }
+
+// Logistic function split by sign so that exp never overflows.
+__device__ __forceinline__ float sigmoidf_stable(float x) {
+    if (x >= 0.f) {
+        return 1.f / (1.f + __expf(-x));
+    }
+    float e = __expf(x);
+    return e / (1.f + e);
+}
+
+// ---- segment layout -----------------------------------------------------------------------------
+// Both problem descriptions address rows through a "segment layout": expert e owns layout rows
+// [seg_start(e), seg_start(e) + count(e)), where count comes from the inclusive int64 offsets and
+// seg_start(e) is offsets[e-1] (grouped order) or 128 * sum_{e'<e} ceil(count(e') / 128) (padded grouped).
+
+// Family R: out[dst(p), n] = scale(p) * sum_k A[src(p), k] * W[e(p)][k, n]
+struct RowGemm {
+    const void* A;
+    int64_t lda;
+    const int32_t* a_map;  // layout row -> row of A (negative: zero row); NULL: identity
+    const void* W;
+    int64_t w_se, w_sk, w_sn;  // element strides of W (E, K, N); one of w_sk, w_sn is 1
+    void* out;
+    int64_t ldo;
+    const int32_t* o_map;  // layout row -> row of out (negative: skip); NULL: identity
+    const void* scale;     // element type of the call; indexed by the out row; NULL: 1
+    const int64_t* offsets;
+    int padded;
+    int64_t rows_cap;  // upper bound of layout rows (grid sizing)
+    int K, N, E;
+    // fused epilogues (tcgen05 engine only)
+    int epi;               // 0 store, 1 SwiGLU forward, 2 down-projection dgrad
+    void* out2;            // SwiGLU: activation output a (rows_cap, N/2); dgrad: ag (rows_cap, N)
+    const void* h;         // dgrad: pre-activation (rows_cap, 2N)
+    float* d_gates;        // dgrad: fp32 (M) accumulated with atomics, indexed by o_map
+    const int32_t* g_map;  // dgrad: layout row -> flat slot index for gates / d_gates
+};
+
+// Family W: DW[e][m, n] = sum_{p in segment e} P[pmap(p), m] * Q[qmap(p), n]
+struct WGemm {
+    const void* P;
+    int64_t ldp;
+    const int32_t* p_map;
+    const void* Q;
+    int64_t ldq;
+    const int32_t* q_map;
+    void* DW;
+    int64_t d_se, d_sm, d_sn;
+    const int64_t* offsets;
+    int padded;
+    int64_t rows_cap;  // rows of P / Q when they are indexed by layout rows (tensor-map extent)
+    int Mout, Nout, E;
+};
+
+enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_DGRAD_DOWN = 2 };
+
+// engines
+int simt_row_gemm(const RowGemm& g, int dtype, cudaStream_t stream);
+int simt_w_gemm(const WGemm& g, int dtype, cudaStream_t stream);
+bool umma_row_gemm_supported(const RowGemm& g, int dtype);
+bool umma_w_gemm_supported(const WGemm& g, int dtype);
+int umma_row_gemm(const RowGemm& g, int dtype, int32_t* status, cudaStream_t stream);
+int umma_w_gemm(const WGemm& g, int dtype, int32_t* status, cudaStream_t stream);
+
+// row-wise kernels used by the API layer
+int launch_swiglu_forward(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t rows, int h, int dtype,
+                          cudaStream_t stream);
+int launch_swiglu_backward(const void* x, int64_t ldx, const void* dy, int64_t lddy, void* dx, int64_t lddx,
+                           int64_t rows, int h, int dtype, cudaStream_t stream);
+int launch_dgrad_down_post(const void* h, void* dh, void* ag, const int32_t* row_slot, const void* gates,
+                           float* d_gates, int64_t rows, int I, int dtype, cudaStream_t stream);
+
+int current_engine();
+
+}  // namespace b200moe

@@ -1,0 +1,284 @@
+// Row-wise, HBM-bound kernels of the path: row gather with coefficient (`group`), the sum over the k
+// slots of a token (`combine`), SwiGLU forward / backward on a fused (rows, 2h) tensor, and the
+// element-wise tail of the down-projection input gradient used by the CUDA-core engine.
+// All of them move 16 bytes per thread access when pointers, row strides and widths allow it.
+#include "common.cuh"
+
+namespace b200moe {
+
+namespace {
+
+template <typename T, int V>
+struct alignas(sizeof(T) * V) Pack {
+    T v[V];
+};
+
+template <typename T>
+constexpr int vec_elems() {
+    return 16 / (int)sizeof(T);
+}
+
+static inline bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
+// ---- group ---------------------------------------------------------------------------------------
+template <typename T, int V>
+__global__ void group_kernel(const T* __restrict__ A, int64_t lda, const int64_t* __restrict__ idx,
+                             T* __restrict__ out, int64_t ldo, const T* __restrict__ coeff, int fan_out, int64_t M,
+                             int K) {
+    int64_t n = blockIdx.x;
+    if (n >= M) return;
+    int64_t s = idx[n];
+    const T* src = A + (s / fan_out) * lda;
+    T* dst = out + n * ldo;
+    float c = coeff ? Elem<T>::to_f(coeff[s]) : 1.f;
+    for (int col = threadIdx.x * V; col < K; col += blockDim.x * V) {
+        Pack<T, V> p = *reinterpret_cast<const Pack<T, V>*>(src + col);
+        if (coeff) {
+#pragma unroll
+            for (int i = 0; i < V; ++i) p.v[i] = Elem<T>::from_f(Elem<T>::to_f(p.v[i]) * c);
+        }
+        *reinterpret_cast<Pack<T, V>*>(dst + col) = p;
+    }
+}
+
+// ---- combine -------------------------------------------------------------------------------------
+template <typename T, int V>
+__global__ void combine_kernel(const T* __restrict__ in, int64_t ldi, const T* __restrict__ gates,
+                               T* __restrict__ out, int64_t ldo, int64_t Tn, int k, int H) {
+    int64_t t = blockIdx.x;
+    if (t >= Tn) return;
+    for (int col = threadIdx.x * V; col < H; col += blockDim.x * V) {
+        float acc[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = 0.f;
+        for (int j = 0; j < k; ++j) {
+            Pack<T, V> p = *reinterpret_cast<const Pack<T, V>*>(in + (t * k + j) * ldi + col);
+            float g = gates ? Elem<T>::to_f(gates[t * k + j]) : 1.f;
+#pragma unroll
+            for (int i = 0; i < V; ++i) acc[i] += g * Elem<T>::to_f(p.v[i]);
+        }
+        Pack<T, V> o;
+#pragma unroll
+        for (int i = 0; i < V; ++i) o.v[i] = Elem<T>::from_f(acc[i]);
+        *reinterpret_cast<Pack<T, V>*>(out + t * ldo + col) = o;
+    }
+}
+
+// ---- SwiGLU --------------------------------------------------------------------------------------
+template <typename T, int V>
+__global__ void swiglu_fwd_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__ y, int64_t ldy,
+                                  int64_t rows, int h) {
+    int64_t r = blockIdx.x;
+    if (r >= rows) return;
+    for (int col = threadIdx.x * V; col < h; col += blockDim.x * V) {
+        Pack<T, V> up = *reinterpret_cast<const Pack<T, V>*>(x + r * ldx + col);
+        Pack<T, V> gt = *reinterpret_cast<const Pack<T, V>*>(x + r * ldx + h + col);
+        Pack<T, V> o;
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            float g = Elem<T>::to_f(gt.v[i]);
+            o.v[i] = Elem<T>::from_f(Elem<T>::to_f(up.v[i]) * g * sigmoidf_stable(g));
+        }
+        *reinterpret_cast<Pack<T, V>*>(y + r * ldy + col) = o;
+    }
+}
+
+template <typename T, int V>
+__global__ void swiglu_bwd_kernel(const T* __restrict__ x, int64_t ldx, const T* __restrict__ dy, int64_t lddy,
+                                  T* __restrict__ dx, int64_t lddx, int64_t rows, int h) {
+    int64_t r = blockIdx.x;
+    if (r >= rows) return;
+    for (int col = threadIdx.x * V; col < h; col += blockDim.x * V) {
+        Pack<T, V> up = *reinterpret_cast<const Pack<T, V>*>(x + r * ldx + col);
+        Pack<T, V> gt = *reinterpret_cast<const Pack<T, V>*>(x + r * ldx + h + col);
+        Pack<T, V> d = *reinterpret_cast<const Pack<T, V>*>(dy + r * lddy + col);
+        Pack<T, V> du, dg;
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            float g = Elem<T>::to_f(gt.v[i]), u = Elem<T>::to_f(up.v[i]), dv = Elem<T>::to_f(d.v[i]);
+            float sg = sigmoidf_stable(g);
+            du.v[i] = Elem<T>::from_f(dv * g * sg);
+            dg.v[i] = Elem<T>::from_f(dv * u * (sg + g * sg * (1.f - sg)));
+        }
+        *reinterpret_cast<Pack<T, V>*>(dx + r * lddx + col) = du;
+        *reinterpret_cast<Pack<T, V>*>(dx + r * lddx + h + col) = dg;
+    }
+}
+
+// ---- tail of the down-projection input gradient (CUDA-core engine) --------------------------------
+// On entry ag[p, :] holds u[p, :] = grad_out[token(p), :] @ w_proj[e]; one block per padded grouped row.
+template <typename T>
+__global__ void dgrad_down_post_kernel(const T* __restrict__ h, T* __restrict__ dh, T* __restrict__ ag,
+                                       const int32_t* __restrict__ row_slot, const T* __restrict__ gates,
+                                       float* __restrict__ d_gates, int64_t rows, int I) {
+    int64_t p = blockIdx.x;
+    if (p >= rows) return;
+    int slot = row_slot[p];
+    T* dh_row = dh + p * 2 * (int64_t)I;
+    T* ag_row = ag + p * (int64_t)I;
+    if (slot < 0) {  // filler row of the padded order: keep it zero
+        for (int c = threadIdx.x; c < I; c += blockDim.x) {
+            dh_row[c] = Elem<T>::from_f(0.f);
+            dh_row[I + c] = Elem<T>::from_f(0.f);
+            ag_row[c] = Elem<T>::from_f(0.f);
+        }
+        return;
+    }
+    const T* h_row = h + p * 2 * (int64_t)I;
+    float g = gates ? Elem<T>::to_f(gates[slot]) : 1.f;
+    float dot = 0.f;
+    for (int c = threadIdx.x; c < I; c += blockDim.x) {
+        float up = Elem<T>::to_f(h_row[c]), gt = Elem<T>::to_f(h_row[I + c]);
+        float u = Elem<T>::to_f(ag_row[c]);
+        float sg = sigmoidf_stable(gt);
+        float act = Elem<T>::to_f(Elem<T>::from_f(up * gt * sg));  // the forward stores it in T
+        dot += act * u;
+        float da = Elem<T>::to_f(Elem<T>::from_f(g * u));
+        dh_row[c] = Elem<T>::from_f(da * gt * sg);
+        dh_row[I + c] = Elem<T>::from_f(da * up * (sg + gt * sg * (1.f - sg)));
+        ag_row[c] = Elem<T>::from_f(g * act);
+    }
+    __shared__ float red[32];
+    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = dot;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (threadIdx.x == 0) d_gates[slot] = v;
+    }
+}
+
+template <typename F>
+int dispatch_dtype(int dtype, F&& f) {
+    switch (dtype) {
+        case B200MOE_F32:
+            return f(float{});
+        case B200MOE_BF16:
+            return f(__nv_bfloat16{});
+        case B200MOE_F16:
+            return f(__half{});
+        default:
+            set_error_detail("unknown dtype code %d", dtype);
+            return B200MOE_ERR_DTYPE;
+    }
+}
+
+static inline int row_threads(int width, int vec) {
+    int t = (width / vec + 31) / 32 * 32;
+    return t < 32 ? 32 : (t > 256 ? 256 : t);
+}
+
+}  // namespace
+
+int launch_swiglu_forward(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t rows, int h, int dtype,
+                          cudaStream_t stream) {
+    if (rows == 0 || h == 0) return B200MOE_OK;
+    return dispatch_dtype(dtype, [&](auto tag) {
+        using T = decltype(tag);
+        constexpr int V = vec_elems<T>();
+        bool vec = h % V == 0 && ldx % V == 0 && ldy % V == 0 && aligned16(x) && aligned16(y);
+        if (vec) {
+            swiglu_fwd_kernel<T, V><<<(unsigned)rows, row_threads(h, V), 0, stream>>>((const T*)x, ldx, (T*)y, ldy, rows, h);
+        } else {
+            swiglu_fwd_kernel<T, 1><<<(unsigned)rows, row_threads(h, 1), 0, stream>>>((const T*)x, ldx, (T*)y, ldy, rows, h);
+        }
+        count_launch();
+        return check_launch("swiglu_forward");
+    });
+}
+
+int launch_swiglu_backward(const void* x, int64_t ldx, const void* dy, int64_t lddy, void* dx, int64_t lddx,
+                           int64_t rows, int h, int dtype, cudaStream_t stream) {
+    if (rows == 0 || h == 0) return B200MOE_OK;
+    return dispatch_dtype(dtype, [&](auto tag) {
+        using T = decltype(tag);
+        constexpr int V = vec_elems<T>();
+        bool vec = h % V == 0 && ldx % V == 0 && lddy % V == 0 && lddx % V == 0 && aligned16(x) && aligned16(dy) &&
+                   aligned16(dx);
+        if (vec) {
+            swiglu_bwd_kernel<T, V><<<(unsigned)rows, row_threads(h, V), 0, stream>>>((const T*)x, ldx, (const T*)dy, lddy,
+                                                                                     (T*)dx, lddx, rows, h);
+        } else {
+            swiglu_bwd_kernel<T, 1><<<(unsigned)rows, row_threads(h, 1), 0, stream>>>((const T*)x, ldx, (const T*)dy, lddy,
+                                                                                     (T*)dx, lddx, rows, h);
+        }
+        count_launch();
+        return check_launch("swiglu_backward");
+    });
+}
+
+int launch_dgrad_down_post(const void* h, void* dh, void* ag, const int32_t* row_slot, const void* gates,
+                           float* d_gates, int64_t rows, int I, int dtype, cudaStream_t stream) {
+    if (rows == 0) return B200MOE_OK;
+    return dispatch_dtype(dtype, [&](auto tag) {
+        using T = decltype(tag);
+        dgrad_down_post_kernel<T><<<(unsigned)rows, 256, 0, stream>>>((const T*)h, (T*)dh, (T*)ag, row_slot,
+                                                                     (const T*)gates, d_gates, rows, I);
+        count_launch();
+        return check_launch("dgrad_down_post");
+    });
+}
+
+}  // namespace b200moe
+
+using namespace b200moe;
+
+extern "C" int b200moe_group(const void* A, int64_t lda, const int64_t* idx, void* out, int64_t ldo,
+                             const void* coeff, int fan_out, int64_t M, int K, int dtype, b200moe_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    B200MOE_REQUIRE(M >= 0 && K >= 0 && fan_out > 0, B200MOE_ERR_ARG, "group: bad sizes");
+    if (M == 0 || K == 0) return B200MOE_OK;
+    B200MOE_REQUIRE(A && idx && out, B200MOE_ERR_ARG, "group: NULL pointer");
+    return dispatch_dtype(dtype, [&](auto tag) {
+        using T = decltype(tag);
+        constexpr int V = vec_elems<T>();
+        bool vec = K % V == 0 && lda % V == 0 && ldo % V == 0 && aligned16(A) && aligned16(out);
+        if (vec) {
+            group_kernel<T, V><<<(unsigned)M, row_threads(K, V), 0, stream>>>((const T*)A, lda, idx, (T*)out, ldo,
+                                                                             (const T*)coeff, fan_out, M, K);
+        } else {
+            group_kernel<T, 1><<<(unsigned)M, row_threads(K, 1), 0, stream>>>((const T*)A, lda, idx, (T*)out, ldo,
+                                                                             (const T*)coeff, fan_out, M, K);
+        }
+        count_launch();
+        return check_launch("group");
+    });
+}
+
+extern "C" int b200moe_combine(const void* in, int64_t ldi, const void* gates, void* out, int64_t ldo, int64_t T_,
+                               int k, int H, int dtype, b200moe_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    B200MOE_REQUIRE(T_ >= 0 && k > 0 && H >= 0, B200MOE_ERR_ARG, "combine: bad sizes");
+    if (T_ == 0 || H == 0) return B200MOE_OK;
+    B200MOE_REQUIRE(in && out, B200MOE_ERR_ARG, "combine: NULL pointer");
+    return dispatch_dtype(dtype, [&](auto tag) {
+        using T = decltype(tag);
+        constexpr int V = vec_elems<T>();
+        bool vec = H % V == 0 && ldi % V == 0 && ldo % V == 0 && aligned16(in) && aligned16(out);
+        if (vec) {
+            combine_kernel<T, V><<<(unsigned)T_, row_threads(H, V), 0, stream>>>((const T*)in, ldi, (const T*)gates,
+                                                                                (T*)out, ldo, T_, k, H);
+        } else {
+            combine_kernel<T, 1><<<(unsigned)T_, row_threads(H, 1), 0, stream>>>((const T*)in, ldi, (const T*)gates,
+                                                                                (T*)out, ldo, T_, k, H);
+        }
+        count_launch();
+        return check_launch("combine");
+    });
+}
+
+extern "C" int b200moe_swiglu_unchunked_forward(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t rows, int h,
+                                                int dtype, b200moe_stream_t stream) {
+    B200MOE_REQUIRE(rows >= 0 && h >= 0, B200MOE_ERR_ARG, "swiglu_forward: bad sizes");
+    B200MOE_REQUIRE(rows == 0 || h == 0 || (x && y), B200MOE_ERR_ARG, "swiglu_forward: NULL pointer");
+    return launch_swiglu_forward(x, ldx, y, ldy, rows, h, dtype, (cudaStream_t)stream);
+}
+
+extern "C" int b200moe_swiglu_unchunked_backward(const void* x, int64_t ldx, const void* dy, int64_t lddy, void* dx,
+                                                 int64_t lddx, int64_t rows, int h, int dtype,
+                                                 b200moe_stream_t stream) {
+    B200MOE_REQUIRE(rows >= 0 && h >= 0, B200MOE_ERR_ARG, "swiglu_backward: bad sizes");
+    B200MOE_REQUIRE(rows == 0 || h == 0 || (x && dy && dx), B200MOE_ERR_ARG, "swiglu_backward: NULL pointer");
+    return launch_swiglu_backward(x, ldx, dy, lddy, dx, lddx, rows, h, dtype, (cudaStream_t)stream);
+}

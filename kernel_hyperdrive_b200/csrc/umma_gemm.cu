@@ -1,0 +1,892 @@
+// Tensor-core engine (sm_100a) for the two grouped-GEMM families.
+//
+// One persistent CTA per SM, 128 x 256 output tiles, 64-deep k steps, 4-stage shared-memory ring,
+// tcgen05.mma (cta_group::1, kind::f16, M=128, N=256, K=16) accumulating fp32 in tensor memory.  Two
+// accumulators of 256 columns each fill the 512 TMEM columns, so the epilogue of tile i overlaps the
+// main loop of tile i+1.
+//
+// Warp roles (320 threads):
+//   warp 0      TMA producer: operands that are plain 2-D tiles of a matrix (cp.async.bulk.tensor, SW128)
+//   warp 1      allocates TMEM, then one lane issues every tcgen05.mma / tcgen05.commit
+//   warps 2-5   gather producers: operands whose rows are picked by an index list (token gather) are
+//               copied with 16-byte cp.async into the same 128-byte-swizzled layout TMA would write
+//   warps 6-9   epilogue: tcgen05.ld of the accumulator, fused element-wise work, global stores
+//
+// Shared-memory tile layout (both operands): rows of 128 bytes (64 elements), 8-row groups of 1024 bytes,
+// 16-byte chunk index XOR (row & 7).  For a K-major operand a row is one M/N index and holds 64
+// consecutive k; for an MN-major operand a row is one k index and holds 64 consecutive M/N indices, and
+// a 128- or 256-wide operand is 2 or 4 such [64 k][128 B] blocks one after the other.
+//
+// Every wait on an mbarrier is bounded: after about two seconds the waiting thread raises a CTA-wide
+// abort flag, writes a code to the status word and every role leaves its loop; TMEM is freed on the way
+// out.  Nothing here uses cluster multicast.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace b200moe {
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KB
+constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KB
+constexpr int NUM_THREADS = 320;
+constexpr int GATHER_THREADS = 128;
+constexpr int GATHER_LAG = 2;  // a gather thread signals stage n once it has issued stage n + GATHER_LAG
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
+
+struct UmmaParams {
+    int wfam;    // 0: family R (row tiles), 1: family W (per-expert weight gradient)
+    int E, padded;
+    const int64_t* offsets;
+    int K;          // R: reduction extent
+    int N;          // columns of the output (R: N, W: Nout)
+    int Mout;       // W: rows of the output
+    int nb_count;   // column blocks
+    int mb_count;   // W: row blocks
+    int swiglu_half;  // EPI_SWIGLU: I (columns of one half); tiles cover 128 columns of each half
+    // operand A (R: activations; W: P)
+    int a_tma, a_mn;
+    const void* a_ptr;
+    int64_t a_ld;
+    const int32_t* a_map;
+    // operand B (R: weights; W: Q)
+    int b_tma, b_mn;
+    const void* b_ptr;
+    int64_t b_ld;
+    const int32_t* b_map;
+    int b_rows_per_expert;  // R: rows of the 2-D weight matrix one expert owns
+    // epilogue
+    void* out;
+    int64_t ldo;
+    const int32_t* o_map;
+    const void* scale;
+    void* out2;
+    const void* h;
+    float* d_gates;
+    const int32_t* g_map;
+    int64_t d_se;
+    int32_t* status;
+    uint32_t idesc;
+    int is_f16;
+    int full_count;  // arrivals per full barrier
+};
+
+// ---- PTX wrappers --------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+
+// Bounded wait.  Returns false when the CTA is aborting (this thread or another one gave up).
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
+                                            int code) {
+    long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            *abort_flag = 1;
+            if (status) atomicCAS(status, 0, code);
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
+                                          int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag, status, code);
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                       uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle, version 1 (sm_100).
+// K-major: 8-row groups 1024 B apart (SBO); LBO unused.  MN-major: 8-k groups 1024 B apart (SBO), 64-wide
+// blocks along M/N 8192 B apart (LBO).
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, int mn_major) {
+    uint32_t lo = ((smem_addr >> 4) & 0x3FFFu) | ((mn_major ? (8192u >> 4) : 1u) << 16);
+    uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    return ((uint64_t)hi << 32) | lo;
+}
+
+// ---- element helpers (bf16 / fp16 chosen at run time, uniform per launch) --------------------------
+__device__ __forceinline__ uint32_t pack2(float a, float b, int is_f16) {
+    if (is_f16) {
+        __half2 v = __floats2half2_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float2 unpack2(uint32_t u, int is_f16) {
+    if (is_f16) return __half22float2(*reinterpret_cast<__half2*>(&u));
+    return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u));
+}
+__device__ __forceinline__ float load_scalar(const void* p, int64_t i, int is_f16) {
+    if (is_f16) return __half2float(((const __half*)p)[i]);
+    return __bfloat162float(((const __nv_bfloat16*)p)[i]);
+}
+__device__ __forceinline__ float round_elem(float v, int is_f16) {
+    if (is_f16) return __half2float(__float2half_rn(v));
+    return __bfloat162float(__float2bfloat16_rn(v));
+}
+
+// ---- tile bookkeeping ----------------------------------------------------------------------------
+struct Tables {
+    int seg_start[kMaxExperts];    // first layout row of the expert's segment
+    int seg_cnt[kMaxExperts];      // rows the expert really has
+    int tile_prefix[kMaxExperts + 1];  // R: row tiles before the expert
+};
+
+struct Tile {
+    int e, row0, rows_valid, nb, mb, ksteps;
+};
+
+__device__ __forceinline__ int total_tiles(const UmmaParams& p, const Tables& tb) {
+    return p.wfam ? p.E * p.mb_count * p.nb_count : tb.tile_prefix[p.E] * p.nb_count;
+}
+
+__device__ __forceinline__ void decode_tile(const UmmaParams& p, const Tables& tb, int t, Tile& ti) {
+    if (p.wfam) {
+        int per_e = p.mb_count * p.nb_count;
+        ti.e = t / per_e;
+        int local = t - ti.e * per_e;
+        if (p.mb_count <= p.nb_count) {  // walk the shorter side fastest: its operand panel stays L2-resident
+            ti.mb = local % p.mb_count;
+            ti.nb = local / p.mb_count;
+        } else {
+            ti.nb = local % p.nb_count;
+            ti.mb = local / p.nb_count;
+        }
+        ti.row0 = tb.seg_start[ti.e];
+        ti.rows_valid = tb.seg_cnt[ti.e];
+        ti.ksteps = (ti.rows_valid + BK - 1) / BK;
+    } else {
+        int lo = 0, hi = p.E - 1;  // last e with tile_prefix[e] * nb <= t
+        while (lo < hi) {
+            int mid = (lo + hi + 1) >> 1;
+            if (tb.tile_prefix[mid] * p.nb_count <= t) {
+                lo = mid;
+            } else {
+                hi = mid - 1;
+            }
+        }
+        ti.e = lo;
+        int mt_e = tb.tile_prefix[lo + 1] - tb.tile_prefix[lo];
+        int local = t - tb.tile_prefix[lo] * p.nb_count;
+        ti.nb = local / mt_e;  // all row tiles of one column block first: the weight panel is shared
+        int mt = local - ti.nb * mt_e;
+        ti.mb = mt;
+        ti.row0 = tb.seg_start[lo] + mt * BM;
+        int cover = p.padded ? (tb.seg_cnt[lo] + kPadRows - 1) / kPadRows * kPadRows : tb.seg_cnt[lo];
+        ti.rows_valid = min(BM, cover - mt * BM);
+        ti.ksteps = (p.K + BK - 1) / BK;
+    }
+}
+
+// ---- the kernel ----------------------------------------------------------------------------------
+template <int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    umma_grouped_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a,
+                        const __grid_constant__ CUtensorMap tmap_b) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + STAGES * A_STAGE_BYTES;
+    uint64_t* bars = (uint64_t*)(smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES));
+    uint64_t* full_bar = bars;
+    uint64_t* empty_bar = bars + STAGES;
+    uint64_t* tmem_full_bar = bars + 2 * STAGES;
+    uint64_t* tmem_empty_bar = bars + 2 * STAGES + 2;
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    Tables& tb = *(Tables*)(tmem_slot + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // segment tables
+    for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
+        int64_t prev = e ? p.offsets[e - 1] : 0;
+        tb.seg_cnt[e] = (int)(p.offsets[e] - prev);
+    }
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), p.full_count);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&tmem_full_bar[a]), 1);
+            mbar_init(smem_u32(&tmem_empty_bar[a]), 128);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int start = 0, tiles = 0;
+        for (int e = 0; e < p.E; ++e) {
+            int cnt = tb.seg_cnt[e];
+            int cover = p.padded ? (cnt + kPadRows - 1) / kPadRows * kPadRows : cnt;
+            tb.seg_start[e] = start;
+            tb.tile_prefix[e] = tiles;
+            start += cover;
+            tiles += (cover + BM - 1) / BM;
+        }
+        tb.tile_prefix[p.E] = tiles;
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int ntiles = total_tiles(p, tb);
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0 && (p.a_tma || p.b_tma)) {
+            const uint32_t tx_bytes = (p.a_tma ? A_STAGE_BYTES : 0) + (p.b_tma ? B_STAGE_BYTES : 0);
+            int stage = 0;
+            uint32_t phase = 0;
+            Tile ti;
+            bool ok = true;
+            for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
+                decode_tile(p, tb, t, ti);
+                for (int ks = 0; ks < ti.ksteps; ++ks) {
+                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 201)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t bar = smem_u32(&full_bar[stage]);
+                    mbar_arrive_expect_tx(bar, tx_bytes);
+                    const uint32_t sa = smem_u32(smem_a + stage * A_STAGE_BYTES);
+                    const uint32_t sb = smem_u32(smem_b + stage * B_STAGE_BYTES);
+                    const int k0 = ks * BK;
+                    if (p.wfam) {
+                        // both operands MN-major: boxes of 64 columns x 64 token rows
+                        int krow = ti.row0 + k0;
+                        if (p.a_tma) {
+#pragma unroll
+                            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &tmap_a, bar, ti.mb * BM + j * 64, krow);
+                        }
+                        if (p.b_tma) {
+#pragma unroll
+                            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tmap_b, bar, ti.nb * BN + j * 64, krow);
+                        }
+                    } else {
+                        if (p.a_tma) tma_load_2d(sa, &tmap_a, bar, k0, ti.row0);  // box 64 x 128
+                        if (p.b_tma) {
+                            if (p.b_mn) {
+                                int krow = ti.e * p.b_rows_per_expert + k0;
+#pragma unroll
+                                for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tmap_b, bar, ti.nb * BN + j * 64, krow);
+                            } else {
+                                int r0, r1;
+                                if (EPI == EPI_SWIGLU) {
+                                    r0 = ti.e * p.b_rows_per_expert + ti.nb * 128;
+                                    r1 = r0 + p.swiglu_half;
+                                } else {
+                                    r0 = ti.e * p.b_rows_per_expert + ti.nb * BN;
+                                    r1 = r0 + 128;
+                                }
+                                tma_load_2d(sb, &tmap_b, bar, k0, r0);  // box 64 x 128
+                                tma_load_2d(sb + 16384, &tmap_b, bar, k0, r1);
+                            }
+                        }
+                    }
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            Tile ti;
+            bool ok = true;
+            const uint32_t a_step = p.a_mn ? 128u : 2u;  // descriptor address units (16 B) per 16-deep MMA
+            const uint32_t b_step = p.b_mn ? 128u : 2u;
+            for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
+                decode_tile(p, tb, t, ti);
+                if (!mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1, abort_flag, p.status, 202)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int ks = 0; ks < ti.ksteps; ++ks) {
+                    if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, 203)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    uint64_t adesc = make_desc(smem_u32(smem_a + stage * A_STAGE_BYTES), p.a_mn);
+                    uint64_t bdesc = make_desc(smem_u32(smem_b + stage * B_STAGE_BYTES), p.b_mn);
+#pragma unroll
+                    for (int j = 0; j < BK / 16; ++j) {
+                        tc_mma(d_tmem, adesc + (uint64_t)(j * a_step), bdesc + (uint64_t)(j * b_step), p.idesc,
+                               (ks | j) ? 1u : 0u);
+                    }
+                    tc_commit(smem_u32(&empty_bar[stage]));  // frees the stage when these MMAs have read it
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (!ok) break;
+                tc_commit(smem_u32(&tmem_full_bar[acc]));  // accumulator complete
+                if (++acc == 2) {
+                    acc = 0;
+                    acc_phase ^= 1;
+                }
+            }
+        }
+    } else if (warp < 6) {
+        // ---------------- gather producers ----------------
+        if (!p.a_tma || !p.b_tma) {
+            const int g = threadIdx.x - 64;  // 0..127
+            const int chunk = g & 7, rbase = g >> 3;  // this thread copies chunk `chunk` of rows rbase + 16 i
+            const uint32_t swz = (uint32_t)((chunk ^ (rbase & 7)) << 4);
+            const int esz = 2;
+            int stage = 0;
+            uint32_t phase = 0;
+            int issued = 0;          // k steps issued so far (all tiles)
+            int sig_stage = 0;       // next stage to signal
+            Tile ti;
+            bool ok = true;
+            for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
+                decode_tile(p, tb, t, ti);
+                int src_r[8];
+                if (!p.wfam) {
+                    // K-major gather of operand A: 128 rows, fixed per tile
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        int r = rbase + 16 * i, src = -1;
+                        if (r < ti.rows_valid) src = p.a_map ? p.a_map[ti.row0 + r] : ti.row0 + r;
+                        src_r[i] = src;
+                    }
+                }
+                for (int ks = 0; ks < ti.ksteps; ++ks) {
+                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 204)) {
+                        ok = false;
+                        break;
+                    }
+                    const int k0 = ks * BK;
+                    if (!p.wfam) {
+                        const uint32_t sa = smem_u32(smem_a + stage * A_STAGE_BYTES) + rbase * 128 + swz;
+                        const int kcol = k0 + chunk * 8;
+                        const bool kin = kcol < p.K;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            int src = src_r[i];
+                            bool v = kin && src >= 0;
+                            const uint8_t* gp = (const uint8_t*)p.a_ptr + (v ? ((int64_t)src * p.a_ld + kcol) * esz : 0);
+                            cp_async_16(sa + i * 2048, gp, v ? 16u : 0u);
+                        }
+                    } else {
+                        // MN-major gather: 64 token rows per stage, 4 per thread
+                        int srcs_a[4], srcs_b[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            int r = k0 + rbase + 16 * i;
+                            int sa_ = -1, sb_ = -1;
+                            if (r < ti.rows_valid) {
+                                sa_ = p.a_map ? p.a_map[ti.row0 + r] : ti.row0 + r;
+                                sb_ = p.b_map ? p.b_map[ti.row0 + r] : ti.row0 + r;
+                            }
+                            srcs_a[i] = sa_;
+                            srcs_b[i] = sb_;
+                        }
+                        if (!p.a_tma) {
+                            const uint32_t sa = smem_u32(smem_a + stage * A_STAGE_BYTES) + rbase * 128 + swz;
+#pragma unroll
+                            for (int j = 0; j < BM / 64; ++j) {
+                                int col = ti.mb * BM + j * 64 + chunk * 8;
+                                bool cin = col < p.Mout;
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    bool v = cin && srcs_a[i] >= 0;
+                                    const uint8_t* gp =
+                                        (const uint8_t*)p.a_ptr + (v ? ((int64_t)srcs_a[i] * p.a_ld + col) * esz : 0);
+                                    cp_async_16(sa + j * 8192 + i * 2048, gp, v ? 16u : 0u);
+                                }
+                            }
+                        }
+                        if (!p.b_tma) {
+                            const uint32_t sb = smem_u32(smem_b + stage * B_STAGE_BYTES) + rbase * 128 + swz;
+#pragma unroll
+                            for (int j = 0; j < BN / 64; ++j) {
+                                int col = ti.nb * BN + j * 64 + chunk * 8;
+                                bool cin = col < p.N;
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    bool v = cin && srcs_b[i] >= 0;
+                                    const uint8_t* gp =
+                                        (const uint8_t*)p.b_ptr + (v ? ((int64_t)srcs_b[i] * p.b_ld + col) * esz : 0);
+                                    cp_async_16(sb + j * 8192 + i * 2048, gp, v ? 16u : 0u);
+                                }
+                            }
+                        }
+                    }
+                    cp_async_commit();
+                    ++issued;
+                    if (issued > GATHER_LAG) {
+                        cp_async_wait<GATHER_LAG>();
+                        fence_proxy_async();
+                        mbar_arrive(smem_u32(&full_bar[sig_stage]));
+                        if (++sig_stage == STAGES) sig_stage = 0;
+                    }
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+            // drain: signal the stages still in flight
+            cp_async_wait<0>();
+            fence_proxy_async();
+            if (ok) {
+                int pending = issued < GATHER_LAG ? issued : GATHER_LAG;
+                for (int i = 0; i < pending; ++i) {
+                    mbar_arrive(smem_u32(&full_bar[sig_stage]));
+                    if (++sig_stage == STAGES) sig_stage = 0;
+                }
+            }
+        }
+    } else {
+        // ---------------- epilogue ----------------
+        const int q = warp & 3;               // TMEM lane quarter this warp may read
+        const int r = q * 32 + lane;          // row of the tile this thread owns
+        const int is_f16 = p.is_f16;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        Tile ti;
+        for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+            decode_tile(p, tb, t, ti);
+            if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status, 205)) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+            const bool have_acc = ti.ksteps > 0;
+
+            if (EPI == EPI_STORE) {
+                bool row_ok;
+                int64_t dst;
+                float sc = 1.f;
+                uint8_t* orow;
+                int n0;
+                if (p.wfam) {
+                    int m = ti.mb * BM + r;
+                    row_ok = m < p.Mout;
+                    dst = m;
+                    n0 = ti.nb * BN;
+                    orow = (uint8_t*)p.out + ((int64_t)ti.e * p.d_se + dst * p.ldo + n0) * 2;
+                } else {
+                    row_ok = r < ti.rows_valid;
+                    int d = -1;
+                    if (row_ok) d = p.o_map ? p.o_map[ti.row0 + r] : ti.row0 + r;
+                    row_ok = d >= 0;
+                    dst = d;
+                    if (row_ok && p.scale) sc = load_scalar(p.scale, dst, is_f16);
+                    n0 = ti.nb * BN;
+                    orow = (uint8_t*)p.out + (dst * p.ldo + n0) * 2;
+                }
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t v[32];
+                    if (have_acc) {
+                        tc_ld32(taddr + c, v);
+                        tc_wait_ld();
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = 0u;
+                    }
+                    if (row_ok) {
+#pragma unroll
+                        for (int qd = 0; qd < 4; ++qd) {
+                            if (n0 + c + qd * 8 < p.N) {
+                                uint4 o;
+                                o.x = pack2(__uint_as_float(v[qd * 8 + 0]) * sc, __uint_as_float(v[qd * 8 + 1]) * sc, is_f16);
+                                o.y = pack2(__uint_as_float(v[qd * 8 + 2]) * sc, __uint_as_float(v[qd * 8 + 3]) * sc, is_f16);
+                                o.z = pack2(__uint_as_float(v[qd * 8 + 4]) * sc, __uint_as_float(v[qd * 8 + 5]) * sc, is_f16);
+                                o.w = pack2(__uint_as_float(v[qd * 8 + 6]) * sc, __uint_as_float(v[qd * 8 + 7]) * sc, is_f16);
+                                *reinterpret_cast<uint4*>(orow + (c + qd * 8) * 2) = o;
+                            }
+                        }
+                    }
+                }
+            } else if (EPI == EPI_SWIGLU) {
+                // accumulator columns [0,128) = up, [128,256) = gate, for output columns nb*128 .. +128 of each half
+                const int I = p.swiglu_half;
+                const bool row_ok = r < ti.rows_valid;
+                const int64_t prow = ti.row0 + r;
+                const int n0 = ti.nb * 128;
+                uint8_t* hrow = (uint8_t*)p.out + (prow * p.ldo + n0) * 2;
+                uint8_t* arow = (uint8_t*)p.out2 + (prow * (int64_t)I + n0) * 2;
+#pragma unroll 1
+                for (int c = 0; c < 128; c += 32) {
+                    uint32_t u[32], gt[32];
+                    tc_ld32(taddr + c, u);
+                    tc_ld32(taddr + 128 + c, gt);
+                    tc_wait_ld();
+                    if (row_ok) {
+#pragma unroll
+                        for (int qd = 0; qd < 4; ++qd) {
+                            if (n0 + c + qd * 8 < I) {
+                                uint32_t hu[4], hg[4], av[4];
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    hu[i] = pack2(__uint_as_float(u[qd * 8 + 2 * i]), __uint_as_float(u[qd * 8 + 2 * i + 1]), is_f16);
+                                    hg[i] = pack2(__uint_as_float(gt[qd * 8 + 2 * i]), __uint_as_float(gt[qd * 8 + 2 * i + 1]), is_f16);
+                                    // the activation sees the values as stored (rounded to the tensor type)
+                                    float2 fu = unpack2(hu[i], is_f16), fg = unpack2(hg[i], is_f16);
+                                    av[i] = pack2(fu.x * fg.x * sigmoidf_stable(fg.x), fu.y * fg.y * sigmoidf_stable(fg.y), is_f16);
+                                }
+                                *reinterpret_cast<uint4*>(hrow + (c + qd * 8) * 2) = make_uint4(hu[0], hu[1], hu[2], hu[3]);
+                                *reinterpret_cast<uint4*>(hrow + ((int64_t)I + c + qd * 8) * 2) = make_uint4(hg[0], hg[1], hg[2], hg[3]);
+                                *reinterpret_cast<uint4*>(arow + (c + qd * 8) * 2) = make_uint4(av[0], av[1], av[2], av[3]);
+                            }
+                        }
+                    }
+                }
+            } else {  // EPI_DGRAD_DOWN
+                const int I = p.N;
+                const bool row_ok = r < ti.rows_valid;
+                const int64_t prow = ti.row0 + r;
+                const int n0 = ti.nb * BN;
+                int slot = -1;
+                if (row_ok) slot = p.g_map[prow];
+                float g = 0.f;
+                if (slot >= 0) g = p.scale ? load_scalar(p.scale, slot, is_f16) : 1.f;
+                const uint8_t* hrow = (const uint8_t*)p.h + (prow * 2 * (int64_t)I + n0) * 2;
+                uint8_t* dhrow = (uint8_t*)p.out + (prow * 2 * (int64_t)I + n0) * 2;
+                uint8_t* agrow = (uint8_t*)p.out2 + (prow * (int64_t)I + n0) * 2;
+                float dot = 0.f;
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t u[32];
+                    tc_ld32(taddr + c, u);
+                    tc_wait_ld();
+                    if (row_ok) {
+#pragma unroll
+                        for (int qd = 0; qd < 4; ++qd) {
+                            if (n0 + c + qd * 8 < I) {
+                                uint4 hu = *reinterpret_cast<const uint4*>(hrow + (c + qd * 8) * 2);
+                                uint4 hg = *reinterpret_cast<const uint4*>(hrow + ((int64_t)I + c + qd * 8) * 2);
+                                const uint32_t hua[4] = {hu.x, hu.y, hu.z, hu.w}, hga[4] = {hg.x, hg.y, hg.z, hg.w};
+                                uint32_t du[4], dg[4], ag[4];
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    float2 up = unpack2(hua[i], is_f16), gt = unpack2(hga[i], is_f16);
+                                    float u0 = __uint_as_float(u[qd * 8 + 2 * i]), u1 = __uint_as_float(u[qd * 8 + 2 * i + 1]);
+                                    float s0 = sigmoidf_stable(gt.x), s1 = sigmoidf_stable(gt.y);
+                                    float a0 = round_elem(up.x * gt.x * s0, is_f16), a1 = round_elem(up.y * gt.y * s1, is_f16);
+                                    dot += a0 * u0 + a1 * u1;
+                                    float d0 = round_elem(g * u0, is_f16), d1 = round_elem(g * u1, is_f16);
+                                    du[i] = pack2(d0 * gt.x * s0, d1 * gt.y * s1, is_f16);
+                                    dg[i] = pack2(d0 * up.x * (s0 + gt.x * s0 * (1.f - s0)), d1 * up.y * (s1 + gt.y * s1 * (1.f - s1)), is_f16);
+                                    ag[i] = pack2(g * a0, g * a1, is_f16);
+                                }
+                                *reinterpret_cast<uint4*>(dhrow + (c + qd * 8) * 2) = make_uint4(du[0], du[1], du[2], du[3]);
+                                *reinterpret_cast<uint4*>(dhrow + ((int64_t)I + c + qd * 8) * 2) = make_uint4(dg[0], dg[1], dg[2], dg[3]);
+                                *reinterpret_cast<uint4*>(agrow + (c + qd * 8) * 2) = make_uint4(ag[0], ag[1], ag[2], ag[3]);
+                            }
+                        }
+                    }
+                }
+                if (slot >= 0) atomicAdd(p.d_gates + slot, dot);
+            }
+            tc_fence_before();
+            mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
+            if (++acc == 2) {
+                acc = 0;
+                acc_phase ^= 1;
+            }
+        }
+    }
+
+    // ---------------- teardown ----------------
+    if (*abort_flag) {
+        // give copies still in flight time to land before shared memory is released
+        for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
+constexpr int SMEM_BYTES = 1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 128 + (int)sizeof(Tables) + 64;
+
+// ---- host side -----------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+// 2-D row-major matrix [rows][cols] with row stride ld (elements), box of 64 columns x box_rows rows.
+int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows, int is_f16) {
+    EncodeTiledFn fn = encode_fn();
+    B200MOE_REQUIRE(fn != nullptr, B200MOE_ERR_DRIVER, "cuTensorMapEncodeTiled not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult rc = fn(map, is_f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims,
+                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    B200MOE_REQUIRE(rc == CUDA_SUCCESS, B200MOE_ERR_DRIVER, "cuTensorMapEncodeTiled failed with %d (rows=%lld cols=%lld ld=%lld)",
+                    (int)rc, (long long)rows, (long long)cols, (long long)ld);
+    return B200MOE_OK;
+}
+
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (!cached[dev]) cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev);
+    return cached[dev] > 0 ? cached[dev] : 148;
+}
+
+bool aligned16(const void* p) { return p != nullptr && ((uintptr_t)p & 15) == 0; }
+
+uint32_t make_idesc(int a_mn, int b_mn, int is_f16) {
+    uint32_t fmt = is_f16 ? 0u : 1u;
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) | ((uint32_t)(BN >> 3) << 17) |
+           ((uint32_t)(BM >> 4) << 24);
+}
+
+template <int EPI>
+int launch(const UmmaParams& p, const CUtensorMap& ma, const CUtensorMap& mb, cudaStream_t stream) {
+    auto kern = umma_grouped_kernel<EPI>;
+    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (err != cudaSuccess) {
+        set_error_detail("cudaFuncSetAttribute(smem=%d): %s", SMEM_BYTES, cudaGetErrorString(err));
+        return B200MOE_ERR_LAUNCH;
+    }
+    kern<<<sm_count(), NUM_THREADS, SMEM_BYTES, stream>>>(p, ma, mb);
+    count_launch();
+    return check_launch("umma_grouped_kernel");
+}
+
+}  // namespace
+
+bool umma_row_gemm_supported(const RowGemm& g, int dtype) {
+    if (dtype != B200MOE_BF16 && dtype != B200MOE_F16) return false;
+    if (g.E > kMaxExperts || g.K % 8 || g.N % 8 || g.lda % 8 || g.ldo % 8) return false;
+    if (!aligned16(g.A) || !aligned16(g.W) || !aligned16(g.out)) return false;
+    if (g.rows_cap >= ((int64_t)1 << 31) || (int64_t)g.E * (g.w_sk == 1 ? g.N : g.K) >= ((int64_t)1 << 31)) return false;
+    if (g.w_sk == 1) {  // K-major weights: (E*N, K) matrix
+        if (g.w_sn % 8 || g.w_sn < g.K || g.w_se != (int64_t)g.N * g.w_sn) return false;
+    } else if (g.w_sn == 1) {  // MN-major: (E*K, N) matrix
+        if (g.w_sk % 8 || g.w_sk < g.N || g.w_se != (int64_t)g.K * g.w_sk) return false;
+    } else {
+        return false;
+    }
+    if (g.epi == EPI_SWIGLU && (g.w_sk != 1 || (g.N / 2) % 8 || !aligned16(g.out2))) return false;
+    if (g.epi == EPI_DGRAD_DOWN && (!aligned16(g.out2) || !aligned16(g.h))) return false;
+    return true;
+}
+
+bool umma_w_gemm_supported(const WGemm& g, int dtype) {
+    if (dtype != B200MOE_BF16 && dtype != B200MOE_F16) return false;
+    if (g.E > kMaxExperts || g.Mout % 8 || g.Nout % 8 || g.ldp % 8 || g.ldq % 8) return false;
+    if (g.d_sn != 1 || g.d_sm % 8 || g.d_se % 8) return false;
+    if (!aligned16(g.P) || !aligned16(g.Q) || !aligned16(g.DW)) return false;
+    return true;
+}
+
+int umma_row_gemm(const RowGemm& g, int dtype, int32_t* status, cudaStream_t stream) {
+    if (g.rows_cap == 0 || g.N == 0) return B200MOE_OK;
+    UmmaParams p{};
+    p.wfam = 0;
+    p.E = g.E;
+    p.padded = g.padded;
+    p.offsets = g.offsets;
+    p.K = g.K;
+    p.is_f16 = dtype == B200MOE_F16;
+    p.a_mn = 0;
+    p.a_tma = g.a_map == nullptr;
+    p.a_ptr = g.A;
+    p.a_ld = g.lda;
+    p.a_map = g.a_map;
+    p.b_tma = 1;
+    p.b_mn = g.w_sn == 1 && g.w_sk != 1;
+    p.b_ptr = g.W;
+    p.out = g.out;
+    p.ldo = g.ldo;
+    p.o_map = g.o_map;
+    p.scale = g.scale;
+    p.out2 = g.out2;
+    p.h = g.h;
+    p.d_gates = g.d_gates;
+    p.g_map = g.g_map;
+    p.status = status;
+    p.idesc = make_idesc(0, p.b_mn, p.is_f16);
+    p.full_count = 1 + (p.a_tma ? 0 : GATHER_THREADS);
+
+    CUtensorMap ma{}, mb{};
+    int rc;
+    if (p.a_tma) {
+        rc = make_map(&ma, g.A, g.rows_cap, g.K, g.lda, 128, p.is_f16);
+        if (rc) return rc;
+    }
+    if (p.b_mn) {
+        p.b_rows_per_expert = g.K;
+        rc = make_map(&mb, g.W, (int64_t)g.E * g.K, g.N, g.w_sk, 64, p.is_f16);
+    } else {
+        p.b_rows_per_expert = g.N;
+        rc = make_map(&mb, g.W, (int64_t)g.E * g.N, g.K, g.w_sn, 128, p.is_f16);
+    }
+    if (rc) return rc;
+    if (!p.a_tma) ma = mb;  // unused, but the parameter must hold a valid descriptor
+
+    if (g.epi == EPI_SWIGLU) {
+        p.swiglu_half = g.N / 2;
+        p.N = g.N;
+        p.nb_count = (p.swiglu_half + 127) / 128;
+        return launch<EPI_SWIGLU>(p, ma, mb, stream);
+    }
+    p.N = g.N;
+    p.nb_count = (g.N + BN - 1) / BN;
+    if (g.epi == EPI_DGRAD_DOWN) return launch<EPI_DGRAD_DOWN>(p, ma, mb, stream);
+    return launch<EPI_STORE>(p, ma, mb, stream);
+}
+
+int umma_w_gemm(const WGemm& g, int dtype, int32_t* status, cudaStream_t stream) {
+    if (g.Mout == 0 || g.Nout == 0 || g.E == 0) return B200MOE_OK;
+    UmmaParams p{};
+    p.wfam = 1;
+    p.E = g.E;
+    p.padded = g.padded;
+    p.offsets = g.offsets;
+    p.is_f16 = dtype == B200MOE_F16;
+    p.Mout = g.Mout;
+    p.N = g.Nout;
+    p.mb_count = (g.Mout + BM - 1) / BM;
+    p.nb_count = (g.Nout + BN - 1) / BN;
+    p.a_mn = 1;
+    p.b_mn = 1;
+    // An operand can come through TMA only when its rows are the layout rows themselves and filler rows are
+    // known to be zero, i.e. in the padded order; everything else is gathered with zero fill.
+    p.a_tma = g.padded && g.p_map == nullptr && g.rows_cap > 0;
+    p.b_tma = g.padded && g.q_map == nullptr && g.rows_cap > 0;
+    p.a_ptr = g.P;
+    p.a_ld = g.ldp;
+    p.a_map = g.p_map;
+    p.b_ptr = g.Q;
+    p.b_ld = g.ldq;
+    p.b_map = g.q_map;
+    p.out = g.DW;
+    p.ldo = g.d_sm;
+    p.d_se = g.d_se;
+    p.status = status;
+    p.idesc = make_idesc(1, 1, p.is_f16);
+    p.full_count = ((p.a_tma || p.b_tma) ? 1 : 0) + ((!p.a_tma || !p.b_tma) ? GATHER_THREADS : 0);
+
+    CUtensorMap ma{}, mb{};
+    int rc;
+    bool have = false;
+    if (p.a_tma) {
+        rc = make_map(&ma, g.P, g.rows_cap, g.Mout, g.ldp, 64, p.is_f16);
+        if (rc) return rc;
+        have = true;
+    }
+    if (p.b_tma) {
+        rc = make_map(&mb, g.Q, g.rows_cap, g.Nout, g.ldq, 64, p.is_f16);
+        if (rc) return rc;
+        if (!have) ma = mb;
+    } else if (have) {
+        mb = ma;
+    }
+    return launch<EPI_STORE>(p, ma, mb, stream);
+}
+
+}  // namespace b200moe

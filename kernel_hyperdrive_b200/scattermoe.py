@@ -1,0 +1,413 @@
+"""MoE layer modules and the autograd functions behind them.
+
+Public names follow the reference so that a user can switch packages without touching call sites:
+`MoE_Torch` (eager torch module, the on-device reference), `MoE_Triton` / `MoE_B200` (this package's
+kernels; the former name is kept as an alias), `Experts_Torch`, `Experts_Triton` / `Experts_B200`,
+`scattered_experts` (cute_kernels/kernels/scattermoe/torch_implementation.py:10-199,
+cute_kernels/kernels/scattermoe/triton_implementation/__init__.py:11-101, ops.py:133-301).
+
+Two execution paths exist in `MoE_B200._compute_experts`:
+  * fused: taken when the layer is a GLU layer whose activation is SwiGLU on the fused tensor.  One
+    routing call, then up-projection + SwiGLU, down-projection + gate scaling, slot sum; the backward
+    runs five kernels.  Intermediates live in the padded grouped order.
+  * generic: any other activation callable.  The same sequence of operators as the reference
+    (`scattered_experts` twice around `self.act`), each operator running on this package's kernels.
+"""
+
+from __future__ import annotations
+
+from typing import Callable
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import _lib
+from ._lib import check, dtype_code, lib, ptr, status_word, stream_ptr
+from .custom_op import b200_op
+from .ops import _workspace, combine, contiguous_count_cute, group, group_bwd_W, scatter2scatter, swiglu_unchunked_cute, swiglu_unchunked_torch
+
+# --------------------------------------------------------------------------------------------------
+# routing
+# --------------------------------------------------------------------------------------------------
+
+
+def padded_rows_cap(M: int, E: int) -> int:
+    return (M // 128 + E) * 128
+
+
+def _route_fake(expert_ids: torch.Tensor, num_experts: int, k: int, want_sorted: bool, want_row_maps: bool):
+    M, dev = expert_ids.numel(), expert_ids.device
+    cap = padded_rows_cap(M, num_experts) if want_row_maps else 0
+    return (
+        torch.empty(M if want_sorted else 0, dtype=torch.int64, device=dev),
+        torch.empty(M if want_sorted else 0, dtype=torch.int64, device=dev),
+        torch.empty(num_experts, dtype=torch.int64, device=dev),
+        torch.empty(num_experts, dtype=torch.int32, device=dev),
+        torch.empty(cap, dtype=torch.int32, device=dev),
+        torch.empty(cap, dtype=torch.int32, device=dev),
+    )
+
+
+@b200_op("route", mutates_args=(), fake_func=_route_fake)
+def route(expert_ids: torch.Tensor, num_experts: int, k: int, want_sorted: bool, want_row_maps: bool) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Stable sort of flat expert ids by expert with histogram and inclusive offsets.
+
+    Returns (sorted_expert_idxs int64 (M), sorted_scattered_idxs int64 (M), expert_offsets int64 (E),
+    counts int32 (E), row_token int32 (cap), row_slot int32 (cap)); the first two are empty unless
+    `want_sorted`, the last two unless `want_row_maps`.  Equals `ids.sort(stable=True)`,
+    `bincount(minlength=E)` and its `cumsum` bit for bit.
+    """
+    assert expert_ids.dim() == 1 and expert_ids.dtype == torch.int64 and expert_ids.is_cuda
+    expert_ids = expert_ids.contiguous()
+    M, dev = expert_ids.numel(), expert_ids.device
+    outs = _route_fake(expert_ids, num_experts, k, want_sorted, want_row_maps)
+    se, ss, offsets, counts, row_token, row_slot = outs
+    nbytes = lib().b200moe_route_workspace_bytes(M, num_experts)
+    ws = _workspace(dev, nbytes)
+    check(
+        lib().b200moe_route(
+            ptr(expert_ids), M, num_experts, k,
+            ptr(se) if want_sorted else None, ptr(ss) if want_sorted else None, ptr(offsets), ptr(counts),
+            ptr(row_token) if want_row_maps else None, ptr(row_slot) if want_row_maps else None, row_token.numel(),
+            ptr(ws), ws.numel(), ptr(status_word(dev)), stream_ptr(dev),
+        ),
+        "route",
+    )
+    return outs
+
+
+# --------------------------------------------------------------------------------------------------
+# generic path: the reference's autograd function on this package's operators
+# --------------------------------------------------------------------------------------------------
+
+
+class _ScatteredExperts(torch.autograd.Function):
+    """One expert projection with fused gather / scatter; same contract as the reference's function of
+    the same name (cute_kernels/kernels/scattermoe/triton_implementation/ops.py:133-277)."""
+
+    @staticmethod
+    def forward(ctx, x, expert_weights, k, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets, gates=None, grouped_in=False, grouped_out=False):
+        M = sorted_expert_idxs.size(0)
+        expanded = torch.empty(M, expert_weights.size(-1), device=x.device, dtype=x.dtype)
+        scatter2scatter(X=x, W=expert_weights, sorted_expert_idxs=sorted_expert_idxs, sorted_scattered_idxs=sorted_scattered_idxs, out=expanded, FAN_OUT=k, x_grouped=grouped_in, y_grouped=grouped_out)
+        if gates is None:
+            output, kept = expanded, None
+        else:
+            output = torch.empty(gates.size(0), expanded.size(1), device=x.device, dtype=x.dtype)
+            combine(expanded, gates, output, gates.size(1))
+            kept = expanded
+        ctx.save_for_backward(x, expert_weights, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets, gates, kept)
+        ctx.flags = (k, grouped_in, grouped_out)
+        return output
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, expert_weights, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets, gates, expanded = ctx.saved_tensors
+        k, grouped_in, grouped_out = ctx.flags
+        M, E = sorted_expert_idxs.size(0), expert_weights.size(0)
+        grad_out = grad_out.contiguous()
+
+        d_gates = None
+        if gates is not None:
+            # d_gates[t, j] = <expanded[t, j, :], grad_out[t, :]>
+            d_gates = torch.bmm(expanded.view(gates.size(0), gates.size(1), -1), grad_out.unsqueeze(2)).squeeze(-1)
+
+        if grouped_out:
+            grouped_grad_out = grad_out
+        else:
+            # the expanded buffer is dead after d_gates: reuse it for the grouped upstream gradient
+            grouped_grad_out = expanded if expanded is not None else torch.empty(M, grad_out.size(1), device=x.device, dtype=x.dtype)
+            group(A=grad_out, sorted_expert_idxs=sorted_scattered_idxs, out=grouped_grad_out, coeff=None if gates is None else gates.flatten(), fan_out=1 if gates is None else gates.size(1))
+
+        if grouped_in:
+            grouped_x = x
+            d_expanded_input = torch.empty(M, expert_weights.size(1), device=x.device, dtype=x.dtype)
+        else:
+            grouped_x = torch.empty(M, x.size(1), dtype=x.dtype, device=x.device)
+            group(A=x, sorted_expert_idxs=sorted_scattered_idxs, out=grouped_x, fan_out=k)
+            d_expanded_input = grouped_x  # overwritten only after the weight gradient has consumed it
+
+        # same strides as the (possibly permuted) weight view; every element is written by the kernel
+        d_weights = torch.empty_like(expert_weights)
+        group_bwd_W(DY=grouped_grad_out, X=grouped_x, expert_offsets=expert_offsets, DW=d_weights, E=E)
+
+        scatter2scatter(X=grouped_grad_out, W=expert_weights.permute(0, 2, 1), sorted_expert_idxs=sorted_expert_idxs, sorted_scattered_idxs=sorted_scattered_idxs, out=d_expanded_input, FAN_OUT=1, x_grouped=True, y_grouped=grouped_in)
+
+        if k == 1:
+            d_input = d_expanded_input
+        else:
+            d_input = torch.empty(x.size(0), d_expanded_input.size(1), device=x.device, dtype=x.dtype)
+            combine(d_expanded_input, None, d_input, k)
+        return d_input, d_weights, None, None, None, None, d_gates, None, None
+
+
+def scattered_experts(inputs, expert_weights, k, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets, gates=None, grouped_in=False, grouped_out=False):
+    return _ScatteredExperts.apply(inputs, expert_weights, k, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets, gates, grouped_in, grouped_out)
+
+
+# --------------------------------------------------------------------------------------------------
+# fused path
+# --------------------------------------------------------------------------------------------------
+
+# When a list is installed here, every grouped-GEMM launch of the fused path is bracketed by two CUDA
+# events on the current stream and (name, start, end) is appended; the benchmark reads kernel durations
+# from it without synchronising inside the step.
+_timing_sink: list | None = None
+
+
+def set_timing_sink(sink: list | None) -> None:
+    global _timing_sink
+    _timing_sink = sink
+
+
+def _launch(name: str, fn, *args) -> None:
+    sink = _timing_sink
+    if sink is None:
+        fn(*args)
+        return
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    fn(*args)
+    end.record()
+    sink.append((name, start, end))
+
+
+
+@b200_op("up_forward", mutates_args={"h", "a"})
+def _up_forward(x: torch.Tensor, w_fc: torch.Tensor, expert_offsets: torch.Tensor, row_token: torch.Tensor, h: torch.Tensor, a: torch.Tensor) -> None:
+    E, I2, H = w_fc.shape
+    check(
+        lib().b200moe_up_forward(ptr(x), x.stride(0), ptr(w_fc), ptr(expert_offsets), ptr(row_token), ptr(h), ptr(a), x.size(0), H, I2 // 2, E, h.size(0), dtype_code(x), ptr(status_word(x.device)), stream_ptr(x.device)),
+        "up_forward",
+    )
+
+
+@b200_op("down_forward", mutates_args={"y_expanded"})
+def _down_forward(a: torch.Tensor, w_proj: torch.Tensor, expert_offsets: torch.Tensor, row_slot: torch.Tensor, gates: torch.Tensor | None, y_expanded: torch.Tensor) -> None:
+    E, H, I = w_proj.shape
+    check(
+        lib().b200moe_down_forward(ptr(a), ptr(w_proj), ptr(expert_offsets), ptr(row_slot), ptr(gates), ptr(y_expanded), y_expanded.stride(0), y_expanded.size(0), H, I, E, a.size(0), dtype_code(a), ptr(status_word(a.device)), stream_ptr(a.device)),
+        "down_forward",
+    )
+
+
+@b200_op("down_dgrad", mutates_args={"dh", "ag", "d_gates"})
+def _down_dgrad(grad_out: torch.Tensor, w_proj: torch.Tensor, expert_offsets: torch.Tensor, row_token: torch.Tensor, row_slot: torch.Tensor, gates: torch.Tensor | None, h: torch.Tensor, dh: torch.Tensor, ag: torch.Tensor, d_gates: torch.Tensor) -> None:
+    E, H, I = w_proj.shape
+    check(
+        lib().b200moe_down_dgrad(
+            ptr(grad_out), grad_out.stride(0), ptr(w_proj), ptr(expert_offsets), ptr(row_token), ptr(row_slot), ptr(gates), ptr(h), ptr(dh), ptr(ag), ptr(d_gates),
+            d_gates.numel(), H, I, E, h.size(0), dtype_code(h), ptr(status_word(h.device)), stream_ptr(h.device),
+        ),
+        "down_dgrad",
+    )
+
+
+@b200_op("wgrad", mutates_args={"DW"})
+def _wgrad(P: torch.Tensor, p_map: torch.Tensor | None, Q: torch.Tensor, q_map: torch.Tensor | None, expert_offsets: torch.Tensor, DW: torch.Tensor, m_cap: int) -> None:
+    E, n_out, n_in = DW.shape
+    check(
+        lib().b200moe_wgrad(ptr(P), P.stride(0), ptr(p_map), ptr(Q), Q.stride(0), ptr(q_map), ptr(expert_offsets), ptr(DW), n_out, n_in, E, m_cap, dtype_code(P), ptr(status_word(P.device)), stream_ptr(P.device)),
+        "wgrad",
+    )
+
+
+@b200_op("up_dgrad", mutates_args={"dx_expanded"})
+def _up_dgrad(dh: torch.Tensor, w_fc: torch.Tensor, expert_offsets: torch.Tensor, row_slot: torch.Tensor, dx_expanded: torch.Tensor) -> None:
+    E, I2, H = w_fc.shape
+    check(
+        lib().b200moe_up_dgrad(ptr(dh), ptr(w_fc), ptr(expert_offsets), ptr(row_slot), ptr(dx_expanded), dx_expanded.stride(0), dx_expanded.size(0), H, I2 // 2, E, dh.size(0), dtype_code(dh), ptr(status_word(dh.device)), stream_ptr(dh.device)),
+        "up_dgrad",
+    )
+
+
+class _FusedSwiGLUExperts(torch.autograd.Function):
+    """Routed SwiGLU experts with externally supplied routing, forward and backward, on the fused kernels.
+
+    Same mathematical contract as `MoE_Triton._compute_experts` with the SwiGLU activation
+    (cute_kernels/kernels/scattermoe/triton_implementation/__init__.py:76-101): gradients flow to the
+    input, both weight tensors (in their stored (E, out, in) layout) and the router weights.
+    """
+
+    @staticmethod
+    def forward(ctx, x, w_fc, w_proj, router_weights, selected_experts):
+        T, H = x.shape
+        E, I2, _ = w_fc.shape
+        I = I2 // 2
+        k = selected_experts.size(1)
+        M = T * k
+        assert w_fc.is_contiguous() and w_proj.is_contiguous(), "expert weights must be stored contiguously as (E, out, in)"
+        assert w_proj.shape == (E, H, I) and router_weights.shape == (T, k)
+        if x.stride(1) != 1:
+            x = x.contiguous()
+        gates = router_weights.to(x.dtype).contiguous()
+        with torch.no_grad():
+            _, _, offsets, _, row_token, row_slot = route(selected_experts.reshape(-1), E, k, False, True)
+        cap = row_token.numel()
+        h = torch.empty(cap, I2, device=x.device, dtype=x.dtype)
+        a = torch.empty(cap, I, device=x.device, dtype=x.dtype)
+        _launch("up_forward", _up_forward, x, w_fc, offsets, row_token, h, a)
+        y_expanded = torch.empty(M, H, device=x.device, dtype=x.dtype)
+        _launch("down_forward", _down_forward, a, w_proj, offsets, row_slot, gates, y_expanded)
+        if k == 1:
+            y = y_expanded
+        else:
+            y = torch.empty(T, H, device=x.device, dtype=x.dtype)
+            combine(y_expanded, None, y, k)
+        ctx.save_for_backward(x, w_fc, w_proj, gates, offsets, row_token, row_slot, h)
+        ctx.k = k
+        ctx.rw_dtype = router_weights.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        x, w_fc, w_proj, gates, offsets, row_token, row_slot, h = ctx.saved_tensors
+        k = ctx.k
+        T, H = x.shape
+        E, I2, _ = w_fc.shape
+        I = I2 // 2
+        M, cap = T * k, h.size(0)
+        grad_y = grad_y.contiguous()
+        need_x, need_w1, need_w2, need_g = ctx.needs_input_grad[:4]
+
+        dh = torch.empty(cap, I2, device=x.device, dtype=x.dtype)
+        ag = torch.empty(cap, I, device=x.device, dtype=x.dtype)
+        d_gates = torch.empty(M, device=x.device, dtype=torch.float32)
+        _launch("down_dgrad", _down_dgrad, grad_y, w_proj, offsets, row_token, row_slot, gates, h, dh, ag, d_gates)
+
+        d_w_proj = d_w_fc = d_x = d_rw = None
+        if need_w2:
+            d_w_proj = torch.empty_like(w_proj)
+            _launch("down_wgrad", _wgrad, grad_y, row_token, ag, None, offsets, d_w_proj, cap)
+        del ag
+        if need_w1:
+            d_w_fc = torch.empty_like(w_fc)
+            _launch("up_wgrad", _wgrad, dh, None, x, row_token, offsets, d_w_fc, cap)
+        if need_x:
+            dx_expanded = torch.empty(M, H, device=x.device, dtype=x.dtype)
+            _launch("up_dgrad", _up_dgrad, dh, w_fc, offsets, row_slot, dx_expanded)
+            if k == 1:
+                d_x = dx_expanded
+            else:
+                d_x = torch.empty(T, H, device=x.device, dtype=x.dtype)
+                combine(dx_expanded, None, d_x, k)
+        if need_g:
+            d_rw = d_gates.view(T, k).to(ctx.rw_dtype)
+        return d_x, d_w_fc, d_w_proj, d_rw, None
+
+
+def fused_swiglu_experts(x, w_fc, w_proj, router_weights, selected_experts):
+    return _FusedSwiGLUExperts.apply(x, w_fc, w_proj, router_weights, selected_experts)
+
+
+# --------------------------------------------------------------------------------------------------
+# modules
+# --------------------------------------------------------------------------------------------------
+
+
+class Experts_Torch(nn.Module):
+    """Per-expert linear layers held as one (E, out, in) parameter; eager evaluation expert by expert."""
+
+    def __init__(self, num_experts: int, in_features: int, out_features: int, add_bias: bool = True, std: float | None = None) -> None:
+        super().__init__()
+        self.num_experts, self.in_features, self.out_features, self.std = num_experts, in_features, out_features, std
+        self.weight = nn.Parameter(torch.empty(num_experts, out_features, in_features))
+        self.bias = nn.Parameter(torch.empty(num_experts, out_features)) if add_bias else None
+        self.reset_parameters()
+
+    @torch.no_grad()
+    def reset_parameters(self) -> None:
+        nn.init.normal_(self.weight, mean=0, std=self.std)
+        if self.bias is not None:
+            self.bias.zero_()
+
+    def forward(self, input, expert_frequency: torch.Tensor, return_list: bool):
+        chunks = input.split(expert_frequency.tolist(), dim=0) if isinstance(input, torch.Tensor) else input
+        outs = [F.linear(chunks[e], self.weight[e], None if self.bias is None else self.bias[e]) for e in range(self.num_experts)]
+        return outs if return_list else torch.cat(outs)
+
+    def extra_repr(self) -> str:
+        return f"num_experts={self.num_experts}, in_features={self.in_features}, out_features={self.out_features}"
+
+
+class MoE_Torch(nn.Module):
+    """Eager torch MoE layer: linear router, top-k with softmax over the selected logits, per-expert MLPs,
+    gate-weighted sum.  Used as the on-device reference of the kernels."""
+
+    experts_cls = Experts_Torch
+
+    def __init__(self, num_experts: int, num_experts_per_tok: int, hidden_size: int, intermediate_size: int, activation_function: Callable, is_glu: bool, add_bias: bool, std: float) -> None:
+        super().__init__()
+        self.num_experts, self.top_k = num_experts, num_experts_per_tok
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.is_glu = is_glu
+        self.gate = nn.Linear(in_features=hidden_size, out_features=num_experts, bias=False)
+        self.c_fc = self.experts_cls(num_experts, hidden_size, 2 * intermediate_size if is_glu else intermediate_size, add_bias=add_bias, std=std)
+        self.act = activation_function
+        self.c_proj = self.experts_cls(num_experts, intermediate_size, hidden_size, add_bias=add_bias, std=std)
+
+    def forward(self, hidden_states: torch.Tensor):
+        shape = hidden_states.shape
+        flat = hidden_states.view(-1, self.hidden_size)
+        router_logits, router_weights, selected_experts = self._compute_routing_weights(flat)
+        out = self._compute_experts(flat, router_weights, selected_experts)
+        return out.view(shape), router_logits
+
+    def _get_topk(self, x: torch.Tensor):
+        return x.max(dim=-1, keepdim=True) if self.top_k == 1 else x.topk(self.top_k, dim=-1)
+
+    def _compute_routing_weights(self, hidden_states: torch.Tensor):
+        router_logits = self.gate(hidden_states)
+        top_vals, selected_experts = self._get_topk(router_logits)
+        router_weights = F.softmax(top_vals.float(), dim=-1).type_as(hidden_states)
+        return router_logits, router_weights, selected_experts
+
+    def _compute_experts(self, hidden_states: torch.Tensor, router_weights: torch.Tensor, selected_experts: torch.Tensor) -> torch.Tensor:
+        T = hidden_states.shape[0]
+        flat_experts = selected_experts.flatten()
+        frequency = flat_experts.bincount(minlength=self.num_experts)
+        order = flat_experts.argsort(stable=True)
+        token_of_row = order // self.top_k
+        rows = self.c_fc(hidden_states[token_of_row], frequency, return_list=True)
+        rows = [self.act(r) for r in rows]
+        rows = self.c_proj(rows, frequency, return_list=False)
+        rows = rows * router_weights.flatten()[order].unsqueeze(-1)
+        return torch.zeros(T, self.hidden_size, dtype=rows.dtype, device=rows.device).index_add(0, token_of_row, rows)
+
+
+class Experts_B200(Experts_Torch):
+    """Expert projection evaluated by the grouped-GEMM operator; the bias, if any, is not applied (the
+    reference's scatter module ignores it as well)."""
+
+    def forward(self, inputs, k, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets, gates=None, grouped_in=False, grouped_out=False):
+        return scattered_experts(inputs, self.weight.permute(0, 2, 1), k, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets, gates, grouped_in, grouped_out)
+
+
+_SWIGLU_CALLABLES = (swiglu_unchunked_torch, swiglu_unchunked_cute)
+
+
+def is_swiglu_callable(fn) -> bool:
+    if fn in _SWIGLU_CALLABLES:
+        return True
+    return getattr(fn, "__name__", "") in ("swiglu_unchunked_torch", "swiglu_unchunked_cute")
+
+
+class MoE_B200(MoE_Torch):
+    """MoE layer on the sm_100a kernels.  Same constructor, parameters and `state_dict` keys as `MoE_Torch`."""
+
+    experts_cls = Experts_B200
+
+    def _compute_experts(self, hidden_states: torch.Tensor, router_weights: torch.Tensor, selected_experts: torch.Tensor) -> torch.Tensor:
+        if self.is_glu and is_swiglu_callable(self.act):
+            return fused_swiglu_experts(hidden_states, self.c_fc.weight, self.c_proj.weight, router_weights, selected_experts)
+        with torch.no_grad():
+            sorted_expert_idxs, sorted_scattered_idxs, expert_offsets, _, _, _ = route(selected_experts.flatten(), self.num_experts, self.top_k, True, False)
+        h = self.c_fc(hidden_states, self.top_k, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets, grouped_out=True)
+        h = self.act(h)
+        return self.c_proj(h, 1, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets, grouped_in=True, gates=router_weights)
+
+
+# drop-in names of the reference
+Experts_Triton = Experts_B200
+MoE_Triton = MoE_B200

@@ -267,8 +267,8 @@ def experts_with_grads(x, w_fc, w_proj, router_weights, selected_experts, grad_o
     """
     x = x.detach().clone().requires_grad_(True)
     rw = router_weights.detach().clone().requires_grad_(True)
-    w1 = w_fc.detach().clone().requires_grad_(True)
-    w2 = w_proj.detach().clone().requires_grad_(True)
+    w1 = w_fc.detach().requires_grad_(True)  # detach() shares storage: no copy of the (large) weights
+    w2 = w_proj.detach().requires_grad_(True)
     y = experts_torch_style(x, w1, w2, rw, selected_experts, act=act)
     y.backward(grad_out)
     return dict(y=y.detach(), dx=x.grad, d_router_weights=rw.grad, d_w_fc=w1.grad, d_w_proj=w2.grad)

@@ -1,0 +1,141 @@
+"""The MoE layer (fused and generic paths) against the CPU oracle and the golden fixtures: output and all
+gradients (input, both expert weights, router weights, gate weight)."""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import kernel_hyperdrive_b200 as kh
+from kernel_hyperdrive_b200 import _lib, synthetic
+from oracle import moe_oracle as orc
+
+from conftest import GOLDEN
+from helpers import make_case, oracle_experts, rel_l2, to_dev, tolerance
+
+pytestmark = pytest.mark.gpu
+
+W = synthetic.WORKLOADS
+SMALL = {
+    "tiny": W["tiny"],
+    "c1": W["c1"],
+    "ragged_k1": synthetic.MoEWorkload("ragged", 6, 1, 40, 24, 19, dtype="fp32", routing="normal_logits"),
+    "c2_small": synthetic.scaled(W["c2"], hidden=512, intermediate=1024, tokens=1024),
+    "c3_small": synthetic.scaled(W["c3"], hidden=256, intermediate=384, tokens=512, shared_experts=0),
+    "c4_small": synthetic.scaled(W["c4"], hidden=256, intermediate=128, tokens=1024),
+    "c5_small": synthetic.scaled(W["c5"], hidden=512, intermediate=256, tokens=768),
+    "odd": synthetic.MoEWorkload("odd", 5, 3, 136, 200, 333, routing="normal_logits"),
+}
+
+
+@pytest.fixture(autouse=True)
+def _engine_reset():
+    yield
+    _lib.set_engine(_lib.ENGINE_AUTO)
+    _lib.check_status(torch.device("cuda"))
+
+
+def run_fused(case_dev):
+    x = case_dev["x"].clone().requires_grad_(True)
+    w1 = case_dev["w_fc"].clone().requires_grad_(True)
+    w2 = case_dev["w_proj"].clone().requires_grad_(True)
+    rw = case_dev["rw"].clone().requires_grad_(True)
+    y = kh.fused_swiglu_experts(x, w1, w2, rw, case_dev["sel"])
+    y.backward(case_dev["g"])
+    return dict(y=y.detach(), dx=x.grad, d_w_fc=w1.grad, d_w_proj=w2.grad, d_router_weights=rw.grad)
+
+
+def check(got, ref, tol, what):
+    for key in ("y", "dx", "d_w_fc", "d_w_proj", "d_router_weights"):
+        assert torch.isfinite(got[key]).all(), (what, key)
+        err = rel_l2(got[key], ref[key])
+        assert err < tol, (what, key, err)
+
+
+@pytest.mark.parametrize("name", list(SMALL))
+@pytest.mark.parametrize("engine,dtype", [("simt", torch.float32), ("simt", torch.bfloat16), ("umma", torch.bfloat16), ("umma", torch.float16)])
+def test_fused_experts_match_oracle(name, engine, dtype):
+    w = SMALL[name]
+    _lib.set_engine(_lib.ENGINE_SIMT if engine == "simt" else _lib.ENGINE_UMMA)
+    case = make_case(w, seed=1, dtype=dtype)
+    ref = oracle_experts(case)
+    got = run_fused(to_dev(case, dtype))
+    check(got, ref, tolerance(dtype), (name, engine, dtype))
+
+
+@pytest.mark.parametrize("name", ["tiny", "c1", "ragged"])
+def test_layer_matches_golden_fp32(name):
+    """Whole layer in fp32 against the reference module's own outputs (router included): 1e-5."""
+    gold = dict(np.load(os.path.join(GOLDEN, f"{name}.npz")))
+    w, seed = {"tiny": (W["tiny"], 0), "c1": (W["c1"], 0), "ragged": (synthetic.MoEWorkload("ragged", 6, 1, 40, 24, 19, dtype="fp32"), 3)}[name]
+    wt = synthetic.make_weights(w, seed)
+    x, g = synthetic.make_tokens(w, seed)
+    m = kh.MoE_Triton(w.num_experts, w.top_k, w.hidden, w.intermediate, kh.swiglu_unchunked_torch, True, False, w.weight_std).cuda()
+    m.load_state_dict({"gate.weight": wt["gate"], "c_fc.weight": wt["w_fc"], "c_proj.weight": wt["w_proj"]})
+    xr = x.cuda().requires_grad_(True)
+    y, logits = m(xr)
+    y.backward(g.cuda())
+    _, _, sel = m._compute_routing_weights(x.cuda())
+    assert np.array_equal(sel.cpu().numpy(), gold["selected_experts"])
+    sub = lambda t: t.detach().flatten()[::97].cpu().numpy()
+    assert rel_l2(y, gold["y"]) < 1e-5 and rel_l2(logits, gold["logits"]) < 1e-5
+    assert rel_l2(xr.grad, gold["dx"]) < 1e-5
+    assert rel_l2(m.gate.weight.grad, gold["d_gate"]) < 1e-4
+    assert rel_l2(sub(m.c_fc.weight.grad), gold["d_w_fc_sub"]) < 1e-5
+    assert rel_l2(sub(m.c_proj.weight.grad), gold["d_w_proj_sub"]) < 1e-5
+    assert abs(m.c_fc.weight.grad.double().norm().item() - gold["d_w_fc_norm"]) < 1e-5 * gold["d_w_fc_norm"]
+    # externally supplied routing through the module seam
+    xr2 = x.cuda().requires_grad_(True)
+    rw = torch.from_numpy(gold["ext_router_weights"]).cuda().requires_grad_(True)
+    m.zero_grad()
+    y2 = m._compute_experts(xr2, rw, torch.from_numpy(gold["ext_selected_experts"]).cuda())
+    y2.backward(g.cuda())
+    assert rel_l2(y2, gold["ext_y"]) < 1e-5 and rel_l2(xr2.grad, gold["ext_dx"]) < 1e-5
+    assert rel_l2(rw.grad, gold["ext_d_router_weights"]) < 1e-5
+    assert rel_l2(sub(m.c_fc.weight.grad), gold["ext_d_w_fc_sub"]) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("act_name,is_glu", [("glu", True), ("gelu", False), ("swiglu", True)])
+def test_generic_path_matches_eager_module(dtype, act_name, is_glu):
+    """Any activation callable: same operator sequence as the reference's scatter module; compared with the
+    eager torch module on the same device and weights (the reference's own test strategy, many tokens)."""
+    act = {"glu": torch.nn.GLU(), "gelu": lambda t: torch.nn.functional.gelu(t, approximate="tanh"), "swiglu": lambda t: kh.swiglu_unchunked_torch(t)}[act_name]
+    torch.manual_seed(42)
+    E, k, H, I, T = 8, 2, 256, 512, 200
+    ref_m = kh.MoE_Torch(E, k, H, I, act, is_glu, False, 0.02).cuda().to(dtype)
+    our_m = kh.MoE_Triton(E, k, H, I, act, is_glu, False, 0.02).cuda().to(dtype)
+    our_m.load_state_dict(ref_m.state_dict())
+    x = torch.randn(4, T // 4, H, device="cuda", dtype=dtype)
+    g = torch.randn_like(x)
+    outs = []
+    for m in (ref_m, our_m):
+        xr = x.clone().requires_grad_(True)
+        y, logits = m(xr)
+        y.backward(g)
+        outs.append((y.detach(), xr.grad, m.c_fc.weight.grad, m.c_proj.weight.grad, m.gate.weight.grad))
+    tol = 1e-5 if dtype == torch.float32 else 1.5e-2  # both sides round to bf16 here
+    for a, b, what in zip(outs[1], outs[0], ("y", "dx", "d_w_fc", "d_w_proj", "d_gate")):
+        assert rel_l2(a, b) < (tol if what != "d_gate" else 20 * tol), (what, rel_l2(a, b))
+
+
+def test_drop_in_shapes_and_state_dict():
+    m = kh.MoE_Triton(8, 2, 256, 512, kh.swiglu_unchunked_torch, True, False, 0.02).cuda().bfloat16()
+    x = torch.randn(2, 3, 5, 256, device="cuda", dtype=torch.bfloat16)
+    y, logits = m(x)
+    assert y.shape == x.shape and logits.shape == (30, 8) and y.dtype == torch.bfloat16
+    t = kh.MoE_Torch(8, 2, 256, 512, kh.swiglu_unchunked_torch, True, False, 0.02).cuda().bfloat16()
+    t.load_state_dict(m.state_dict())
+    y2, _ = t(x)
+    assert rel_l2(y, y2) < 1.5e-2
+
+
+def test_weight_grads_of_empty_experts_are_zero():
+    w = synthetic.MoEWorkload("e", 16, 2, 128, 128, 64, routing="normal_logits")
+    case = make_case(w, seed=5, dtype=torch.bfloat16)
+    case["sel"] = case["sel"] % 5  # experts 5.. receive nothing
+    got = run_fused(to_dev(case, torch.bfloat16))
+    assert (got["d_w_fc"][5:] == 0).all() and (got["d_w_proj"][5:] == 0).all()
+    ref = oracle_experts(case)
+    check(got, ref, 1e-2, "empty experts")
