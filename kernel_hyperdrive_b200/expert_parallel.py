@@ -1,0 +1,223 @@
+"""Expert-parallel MoE layer: experts sharded over the ranks of one NVSwitch box, tokens stay with their rank.
+
+Not in the reference (it has no collective anywhere); built on the reference's seam
+`_compute_experts(hidden_states, router_weights, selected_experts)`
+(cute_kernels/kernels/scattermoe/torch_implementation.py:135-137).
+
+Per forward pass on rank r (R ranks, E experts, E/R experts per rank, T local tokens, k slots):
+  1. route locally: stable sort of the flat expert ids -> rows ordered by (owning rank, expert), counts (E)
+  2. counts all-to-all (int32 (R, E/R), equal splits) -> how many rows every source sends to each local expert
+  3. dispatch gather: send[n, :] = x[token(n), :] in sorted order (one HBM pass)
+  4. rows all-to-all with variable splits (NCCL over NVLink); received rows land in local HBM
+  5. local experts on the received rows: the fused SwiGLU expert path with k = 1 and unit gates
+  6. rows all-to-all back (same splits reversed)
+  7. un-sort to (token, slot) order and gate-weighted sum over the k slots at the source rank
+Backward mirrors it: autograd replays steps 7..1 with the all-to-alls swapped, so a pass moves four row
+payloads in total.  The gate gradient d<gate> = <unweighted expert output, upstream gradient> is formed at
+the source rank in step 7's backward, so no extra payload travels for it.
+
+The one host synchronisation per pass is the read of the split sizes (NCCL wants them as host integers).
+
+Row operations (gather, combine, routing sort) are injected: the default runs this package's CUDA kernels;
+the CPU test-suite passes torch-indexing doubles to exercise the exchange logic over gloo.
+"""
+
+from __future__ import annotations
+
+from typing import Callable
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+import torch.nn.functional as F
+
+
+class CudaRowOps:
+    """Row operations on this package's kernels."""
+
+    @staticmethod
+    def route(flat_ids: torch.Tensor, num_experts: int, k: int):
+        from .scattermoe import route
+
+        se, ss, _, counts, _, _ = route(flat_ids, num_experts, k, True, False)
+        return ss, counts
+
+    @staticmethod
+    def gather(x: torch.Tensor, idx: torch.Tensor, fan_out: int) -> torch.Tensor:
+        from .ops import group
+
+        out = torch.empty(idx.numel(), x.size(1), dtype=x.dtype, device=x.device)
+        group(x, idx, out, None, fan_out)
+        return out
+
+    @staticmethod
+    def combine(expanded: torch.Tensor, gates: torch.Tensor | None, k: int) -> torch.Tensor:
+        from .ops import combine
+
+        out = torch.empty(expanded.size(0) // k, expanded.size(1), dtype=expanded.dtype, device=expanded.device)
+        combine(expanded, gates, out, k)
+        return out
+
+
+class _AllToAllRows(torch.autograd.Function):
+    """Variable-split row exchange; the backward is the same exchange with the splits swapped."""
+
+    @staticmethod
+    def forward(ctx, rows, send_splits, recv_splits, group):
+        ctx.splits = (send_splits, recv_splits)
+        ctx.group = group
+        out = torch.empty(sum(recv_splits), rows.size(1), dtype=rows.dtype, device=rows.device)
+        dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=recv_splits, input_split_sizes=send_splits, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        send_splits, recv_splits = ctx.splits
+        out = torch.empty(sum(send_splits), grad.size(1), dtype=grad.dtype, device=grad.device)
+        dist.all_to_all_single(out, grad.contiguous(), output_split_sizes=send_splits, input_split_sizes=recv_splits, group=ctx.group)
+        return out, None, None, None
+
+
+class _DispatchGather(torch.autograd.Function):
+    """send[n, :] = x[ss[n] // k, :].  Backward: un-sort the row gradients and sum the k slots of a token."""
+
+    @staticmethod
+    def forward(ctx, x, ss, inv, k, ops):
+        ctx.save_for_backward(inv)
+        ctx.k, ctx.ops = k, ops
+        return ops.gather(x, ss, k)
+
+    @staticmethod
+    def backward(ctx, grad):
+        (inv,) = ctx.saved_tensors
+        expanded = ctx.ops.gather(grad.contiguous(), inv, 1)
+        return ctx.ops.combine(expanded, None, ctx.k), None, None, None, None
+
+
+class _UnsortCombine(torch.autograd.Function):
+    """y[t, :] = sum_j gates[t, j] * rows[inv[t*k + j], :] with gradients for the rows and the gates."""
+
+    @staticmethod
+    def forward(ctx, rows, gates, ss, inv, ops):
+        k = gates.size(1)
+        expanded = ops.gather(rows, inv, 1)  # (token, slot) order
+        ctx.save_for_backward(expanded, gates, ss)
+        ctx.ops = ops
+        return ops.combine(expanded, gates.contiguous(), k)
+
+    @staticmethod
+    def backward(ctx, grad):
+        expanded, gates, ss = ctx.saved_tensors
+        T, k = gates.shape
+        grad = grad.contiguous()
+        d_gates = torch.bmm(expanded.view(T, k, -1), grad.unsqueeze(2)).squeeze(-1).to(gates.dtype)
+        # gradient of row n (sorted order) = gates[ss[n]] * grad[ss[n] // k]
+        d_rows = ctx.ops.gather(grad, ss, k) * gates.flatten()[ss].unsqueeze(-1)
+        return d_rows, d_gates, None, None, None
+
+
+def exchange_counts(counts: torch.Tensor, world: int, group) -> torch.Tensor:
+    """counts: int32 (E) rows this rank sends to every expert.  Returns int32 (R, E/R): rows every source
+    rank sends to each of this rank's experts."""
+    recv = torch.empty_like(counts)
+    dist.all_to_all_single(recv, counts.contiguous(), group=group)
+    return recv.view(world, -1)
+
+
+def ep_experts(x, router_weights, selected_experts, num_experts: int, local_experts_fn: Callable, group, ops=CudaRowOps):
+    """Routed experts over an expert-parallel group.  `local_experts_fn(rows, local_expert_ids)` evaluates
+    this rank's experts on the received rows (unit gates, one expert per row) and must be differentiable."""
+    world = dist.get_world_size(group)
+    T, k = selected_experts.shape
+    e_local = num_experts // world
+    with torch.no_grad():
+        flat = selected_experts.reshape(-1)
+        ss, counts = ops.route(flat, num_experts, k)
+        inv = torch.empty_like(ss)
+        inv[ss] = torch.arange(ss.numel(), device=ss.device)
+        recv_counts = exchange_counts(counts, world, group)
+        # one host read per pass: NCCL takes the split sizes as host integers
+        host = torch.cat([counts.view(world, e_local).sum(1), recv_counts.sum(1), ]).tolist()
+        send_splits, recv_splits = [int(v) for v in host[:world]], [int(v) for v in host[world:]]
+        local_ids = torch.repeat_interleave(
+            torch.arange(e_local, device=x.device).repeat(world), recv_counts.flatten().long(), output_size=sum(recv_splits)
+        )
+    send = _DispatchGather.apply(x, ss, inv, k, ops)
+    recv = _AllToAllRows.apply(send, send_splits, recv_splits, group)
+    out_rows = local_experts_fn(recv, local_ids)
+    back = _AllToAllRows.apply(out_rows, recv_splits, send_splits, group)
+    return _UnsortCombine.apply(back, router_weights.to(x.dtype), ss, inv, ops)
+
+
+class MoE_B200_EP(nn.Module):
+    """Expert-parallel MoE layer.  The gate is replicated; rank r holds experts [r*E/R, (r+1)*E/R).
+
+    Weights are drawn expert by expert from a seed shared by all ranks, so the union of the shards equals
+    the single-GPU layer built from the same seed with `full_state_dict`-style gathering.
+    """
+
+    def __init__(self, num_experts, num_experts_per_tok, hidden_size, intermediate_size, activation_function, is_glu, add_bias, std,
+                 group=None, device=None, dtype=torch.float32, seed: int = 0, ops=CudaRowOps, local_experts_fn=None):
+        super().__init__()
+        assert is_glu, "the expert-parallel layer implements GLU experts"
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        assert num_experts % self.world == 0, "experts must divide evenly over the ranks"
+        self.num_experts, self.top_k = num_experts, num_experts_per_tok
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.e_local = num_experts // self.world
+        self.ops = ops
+        self._local_experts_fn = local_experts_fn
+        self.act = activation_function
+        gen = torch.Generator().manual_seed(seed)
+        gate = torch.randn(num_experts, hidden_size, generator=gen) / hidden_size**0.5
+        self.gate = nn.Linear(hidden_size, num_experts, bias=False, device=device, dtype=dtype)
+        fc, proj = [], []
+        for e in range(self.rank * self.e_local, (self.rank + 1) * self.e_local):
+            ge = torch.Generator().manual_seed(seed * 100003 + 17 + e)
+            fc.append(torch.randn(2 * intermediate_size, hidden_size, generator=ge) * std)
+            proj.append(torch.randn(hidden_size, intermediate_size, generator=ge) * std)
+        with torch.no_grad():
+            self.gate.weight.copy_(gate)
+        self.c_fc_weight = nn.Parameter(torch.stack(fc).to(device=device, dtype=dtype))
+        self.c_proj_weight = nn.Parameter(torch.stack(proj).to(device=device, dtype=dtype))
+
+    def local_experts(self, rows: torch.Tensor, local_ids: torch.Tensor) -> torch.Tensor:
+        if self._local_experts_fn is not None:
+            return self._local_experts_fn(rows, local_ids, self.c_fc_weight, self.c_proj_weight)
+        from .scattermoe import fused_swiglu_experts
+
+        ones = torch.ones(rows.size(0), 1, dtype=rows.dtype, device=rows.device)
+        return fused_swiglu_experts(rows, self.c_fc_weight, self.c_proj_weight, ones, local_ids.view(-1, 1))
+
+    def forward(self, hidden_states: torch.Tensor):
+        shape = hidden_states.shape
+        flat = hidden_states.view(-1, self.hidden_size)
+        router_logits = self.gate(flat)
+        vals, selected = router_logits.max(-1, keepdim=True) if self.top_k == 1 else router_logits.topk(self.top_k, dim=-1)
+        router_weights = F.softmax(vals.float(), dim=-1).type_as(flat)
+        out = self._compute_experts(flat, router_weights, selected)
+        return out.view(shape), router_logits
+
+    def _compute_experts(self, hidden_states, router_weights, selected_experts):
+        return ep_experts(hidden_states, router_weights, selected_experts, self.num_experts, self.local_experts, self.group, self.ops)
+
+    def allreduce_replicated_grads(self) -> None:
+        """Sums the gradient of the replicated gate over the ranks (tokens are data-parallel)."""
+        if self.gate.weight.grad is not None:
+            dist.all_reduce(self.gate.weight.grad, group=self.group)
+
+    def full_state_dict(self) -> dict:
+        """Gathers the expert shards into the single-GPU layer's `state_dict` layout (on every rank)."""
+        fc = [torch.empty_like(self.c_fc_weight) for _ in range(self.world)]
+        proj = [torch.empty_like(self.c_proj_weight) for _ in range(self.world)]
+        dist.all_gather(fc, self.c_fc_weight.detach().contiguous(), group=self.group)
+        dist.all_gather(proj, self.c_proj_weight.detach().contiguous(), group=self.group)
+        return {"gate.weight": self.gate.weight.detach().clone(), "c_fc.weight": torch.cat(fc), "c_proj.weight": torch.cat(proj)}
+
+    def load_full_state_dict(self, sd: dict) -> None:
+        lo, hi = self.rank * self.e_local, (self.rank + 1) * self.e_local
+        with torch.no_grad():
+            self.gate.weight.copy_(sd["gate.weight"])
+            self.c_fc_weight.copy_(sd["c_fc.weight"][lo:hi])
+            self.c_proj_weight.copy_(sd["c_proj.weight"][lo:hi])
