@@ -250,7 +250,8 @@ def run_gpu_arm(args, w):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return ms.item()
 
-    for _ in range(max(args.warmup, 3)):
+    n_warm = args.warmup if args.profile else max(args.warmup, 3)
+    for _ in range(n_warm):
         step_resident()
     _lib.check_status(dev)
 
@@ -267,9 +268,12 @@ def run_gpu_arm(args, w):
         per_kernel.setdefault(name, []).append(s.elapsed_time(e))
     clock_summary = clocks.summary()
 
-    for _ in range(2):
-        step_e2e()
-    e2e_ms = timed(step_e2e, args.steps)
+    if args.profile:
+        e2e_ms = float("nan")
+    else:
+        for _ in range(2):
+            step_e2e()
+        e2e_ms = timed(step_e2e, args.steps)
     _lib.check_status(dev)
 
     flops_step = w.flops_fwd_bwd() * world  # every rank brings T tokens
@@ -287,7 +291,7 @@ def run_gpu_arm(args, w):
     per_launch = {n: {"ms": ms, "tflops": (share[n] / 18.0) * local_flops / (ms * 1e-3) / 1e12} for n, ms in gemm_ms.items() if n in share}
 
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": n_warm,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
         "config": workload_config(w, world),
         "tokens_per_s": T * world / (ms_step * 1e-3),
@@ -303,7 +307,7 @@ def run_gpu_arm(args, w):
         },
     }
 
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and not args.profile:
         cpu_w = dict(gate=layer.gate.weight.detach().cpu(), w_fc=layer.c_fc.weight.detach().cpu(), w_proj=layer.c_proj.weight.detach().cpu())
         val, sec, sample, threads = cpu_reference_run(w, 1, 1, args.cpu_sample_tokens, weights=cpu_w)
         line["cpu_baseline"] = {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
@@ -323,6 +327,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=None, help="override tokens per GPU (profiling on a small case)")
     ap.add_argument("--cpu-sample-tokens", type=int, default=256)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile", action="store_true", help="profiling run under ncu: exactly --warmup warm-up steps, no end-to-end and CPU legs; its numbers are not benchmark values")
     args = ap.parse_args()
     w = synthetic.WORKLOADS[args.workload]
     if args.tokens:

@@ -5,12 +5,13 @@
 // accumulators of 256 columns each fill the 512 TMEM columns, so the epilogue of tile i overlaps the
 // main loop of tile i+1.
 //
-// Warp roles (320 threads):
+// Warp roles (448 threads):
 //   warp 0      TMA producer: operands that are plain 2-D tiles of a matrix (cp.async.bulk.tensor, SW128)
 //   warp 1      allocates TMEM, then one lane issues every tcgen05.mma / tcgen05.commit
 //   warps 2-5   gather producers: operands whose rows are picked by an index list (token gather) are
 //               copied with 16-byte cp.async into the same 128-byte-swizzled layout TMA would write
-//   warps 6-9   epilogue: tcgen05.ld of the accumulator, fused element-wise work, global stores
+//   warps 6-13  epilogue: tcgen05.ld of the accumulator, fused element-wise work, global stores; two warps
+//               share each TMEM lane quarter and split the tile's columns
 //
 // Shared-memory tile layout (both operands): rows of 128 bytes (64 elements), 8-row groups of 1024 bytes,
 // 16-byte chunk index XOR (row & 7).  For a K-major operand a row is one M/N index and holds 64
@@ -34,9 +35,9 @@ constexpr int BM = 128, BN = 256, BK = 64;
 constexpr int STAGES = 4;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KB
 constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KB
-constexpr int NUM_THREADS = 320;
+constexpr int EPI_WARPS = 8;                        // two warps per TMEM lane quarter, each takes half the columns
+constexpr int NUM_THREADS = (6 + EPI_WARPS) * 32;   // 448
 constexpr int GATHER_THREADS = 128;
-constexpr int GATHER_LAG = 2;  // a gather thread signals stage n once it has issued stage n + GATHER_LAG
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
 
 struct UmmaParams {
@@ -132,12 +133,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+// Arrives on the barrier once every cp.async this thread issued before has landed; the arrival is one
+// of the barrier's expected arrivals (noinc), so the issuing thread never waits for its own copies.
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -284,7 +284,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&tmem_full_bar[a]), 1);
-            mbar_init(smem_u32(&tmem_empty_bar[a]), 128);
+            mbar_init(smem_u32(&tmem_empty_bar[a]), EPI_WARPS * 32);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -423,31 +423,37 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             const int esz = 2;
             int stage = 0;
             uint32_t phase = 0;
-            int issued = 0;          // k steps issued so far (all tiles)
-            int sig_stage = 0;       // next stage to signal
             Tile ti;
             bool ok = true;
-            for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
-                decode_tile(p, tb, t, ti);
-                int src_r[8];
-                if (!p.wfam) {
-                    // K-major gather of operand A: 128 rows, fixed per tile
+            if (!p.wfam) {
+                // K-major gather of operand A: the 128 source rows are fixed per tile; the next tile's rows are
+                // fetched while the current tile streams so that the index latency stays off the critical path
+                int src_r[8], src_n[8];
+                auto load_rows = [&](int t, int (&dst)[8]) {
+                    Tile tn;
+                    if (t < ntiles) {
+                        decode_tile(p, tb, t, tn);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        int r = rbase + 16 * i, src = -1;
-                        if (r < ti.rows_valid) src = p.a_map ? p.a_map[ti.row0 + r] : ti.row0 + r;
-                        src_r[i] = src;
+                        for (int i = 0; i < 8; ++i) {
+                            int r = rbase + 16 * i, src = -1;
+                            if (r < tn.rows_valid) src = p.a_map ? p.a_map[tn.row0 + r] : tn.row0 + r;
+                            dst[i] = src;
+                        }
                     }
-                }
-                for (int ks = 0; ks < ti.ksteps; ++ks) {
-                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 204)) {
-                        ok = false;
-                        break;
-                    }
-                    const int k0 = ks * BK;
-                    if (!p.wfam) {
+                };
+                load_rows(blockIdx.x, src_n);
+                for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
+                    decode_tile(p, tb, t, ti);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) src_r[i] = src_n[i];
+                    load_rows(t + gridDim.x, src_n);
+                    for (int ks = 0; ks < ti.ksteps; ++ks) {
+                        if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 204)) {
+                            ok = false;
+                            break;
+                        }
                         const uint32_t sa = smem_u32(smem_a + stage * A_STAGE_BYTES) + rbase * 128 + swz;
-                        const int kcol = k0 + chunk * 8;
+                        const int kcol = ks * BK + chunk * 8;
                         const bool kin = kcol < p.K;
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
@@ -456,21 +462,46 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                             const uint8_t* gp = (const uint8_t*)p.a_ptr + (v ? ((int64_t)src * p.a_ld + kcol) * esz : 0);
                             cp_async_16(sa + i * 2048, gp, v ? 16u : 0u);
                         }
-                    } else {
-                        // MN-major gather: 64 token rows per stage, 4 per thread
-                        int srcs_a[4], srcs_b[4];
+                        cp_async_arrive_noinc(smem_u32(&full_bar[stage]));
+                        if (++stage == STAGES) {
+                            stage = 0;
+                            phase ^= 1;
+                        }
+                    }
+                }
+            } else {
+                // MN-major gather: 64 token rows per stage, 4 per thread; the row indices of step ks + 1 are
+                // requested before the copies of step ks are issued
+                const bool ga = !p.a_tma, gb = !p.b_tma;
+                auto load_idx = [&](const Tile& tt, int ks, int (&ia)[4], int (&ib)[4]) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        int r = ks * BK + rbase + 16 * i;
+                        int sa_ = -1, sb_ = -1;
+                        if (r < tt.rows_valid) {
+                            if (ga) sa_ = p.a_map ? p.a_map[tt.row0 + r] : tt.row0 + r;
+                            if (gb) sb_ = p.b_map ? p.b_map[tt.row0 + r] : tt.row0 + r;
+                        }
+                        ia[i] = sa_;
+                        ib[i] = sb_;
+                    }
+                };
+                for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
+                    decode_tile(p, tb, t, ti);
+                    int cur_a[4], cur_b[4], nxt_a[4], nxt_b[4];
+                    if (ti.ksteps > 0) load_idx(ti, 0, nxt_a, nxt_b);
+                    for (int ks = 0; ks < ti.ksteps; ++ks) {
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
-                            int r = k0 + rbase + 16 * i;
-                            int sa_ = -1, sb_ = -1;
-                            if (r < ti.rows_valid) {
-                                sa_ = p.a_map ? p.a_map[ti.row0 + r] : ti.row0 + r;
-                                sb_ = p.b_map ? p.b_map[ti.row0 + r] : ti.row0 + r;
-                            }
-                            srcs_a[i] = sa_;
-                            srcs_b[i] = sb_;
+                            cur_a[i] = nxt_a[i];
+                            cur_b[i] = nxt_b[i];
                         }
-                        if (!p.a_tma) {
+                        if (ks + 1 < ti.ksteps) load_idx(ti, ks + 1, nxt_a, nxt_b);
+                        if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 204)) {
+                            ok = false;
+                            break;
+                        }
+                        if (ga) {
                             const uint32_t sa = smem_u32(smem_a + stage * A_STAGE_BYTES) + rbase * 128 + swz;
 #pragma unroll
                             for (int j = 0; j < BM / 64; ++j) {
@@ -478,14 +509,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                                 bool cin = col < p.Mout;
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) {
-                                    bool v = cin && srcs_a[i] >= 0;
+                                    bool v = cin && cur_a[i] >= 0;
                                     const uint8_t* gp =
-                                        (const uint8_t*)p.a_ptr + (v ? ((int64_t)srcs_a[i] * p.a_ld + col) * esz : 0);
+                                        (const uint8_t*)p.a_ptr + (v ? ((int64_t)cur_a[i] * p.a_ld + col) * esz : 0);
                                     cp_async_16(sa + j * 8192 + i * 2048, gp, v ? 16u : 0u);
                                 }
                             }
                         }
-                        if (!p.b_tma) {
+                        if (gb) {
                             const uint32_t sb = smem_u32(smem_b + stage * B_STAGE_BYTES) + rbase * 128 + swz;
 #pragma unroll
                             for (int j = 0; j < BN / 64; ++j) {
@@ -493,36 +524,19 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                                 bool cin = col < p.N;
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) {
-                                    bool v = cin && srcs_b[i] >= 0;
+                                    bool v = cin && cur_b[i] >= 0;
                                     const uint8_t* gp =
-                                        (const uint8_t*)p.b_ptr + (v ? ((int64_t)srcs_b[i] * p.b_ld + col) * esz : 0);
+                                        (const uint8_t*)p.b_ptr + (v ? ((int64_t)cur_b[i] * p.b_ld + col) * esz : 0);
                                     cp_async_16(sb + j * 8192 + i * 2048, gp, v ? 16u : 0u);
                                 }
                             }
                         }
+                        cp_async_arrive_noinc(smem_u32(&full_bar[stage]));
+                        if (++stage == STAGES) {
+                            stage = 0;
+                            phase ^= 1;
+                        }
                     }
-                    cp_async_commit();
-                    ++issued;
-                    if (issued > GATHER_LAG) {
-                        cp_async_wait<GATHER_LAG>();
-                        fence_proxy_async();
-                        mbar_arrive(smem_u32(&full_bar[sig_stage]));
-                        if (++sig_stage == STAGES) sig_stage = 0;
-                    }
-                    if (++stage == STAGES) {
-                        stage = 0;
-                        phase ^= 1;
-                    }
-                }
-            }
-            // drain: signal the stages still in flight
-            cp_async_wait<0>();
-            fence_proxy_async();
-            if (ok) {
-                int pending = issued < GATHER_LAG ? issued : GATHER_LAG;
-                for (int i = 0; i < pending; ++i) {
-                    mbar_arrive(smem_u32(&full_bar[sig_stage]));
-                    if (++sig_stage == STAGES) sig_stage = 0;
                 }
             }
         }
@@ -530,6 +544,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         // ---------------- epilogue ----------------
         const int q = warp & 3;               // TMEM lane quarter this warp may read
         const int r = q * 32 + lane;          // row of the tile this thread owns
+        const int half = (warp - 6) >> 2;     // which half of the tile's columns this warp handles
         const int is_f16 = p.is_f16;
         int acc = 0;
         uint32_t acc_phase = 0;
@@ -564,7 +579,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     orow = (uint8_t*)p.out + (dst * p.ldo + n0) * 2;
                 }
 #pragma unroll 1
-                for (int c = 0; c < BN; c += 32) {
+                for (int c = half * (BN / 2); c < (half + 1) * (BN / 2); c += 32) {
                     uint32_t v[32];
                     if (have_acc) {
                         tc_ld32(taddr + c, v);
@@ -596,7 +611,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 uint8_t* hrow = (uint8_t*)p.out + (prow * p.ldo + n0) * 2;
                 uint8_t* arow = (uint8_t*)p.out2 + (prow * (int64_t)I + n0) * 2;
 #pragma unroll 1
-                for (int c = 0; c < 128; c += 32) {
+                for (int c = half * 64; c < (half + 1) * 64; c += 32) {
                     uint32_t u[32], gt[32];
                     tc_ld32(taddr + c, u);
                     tc_ld32(taddr + 128 + c, gt);
@@ -635,7 +650,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 uint8_t* agrow = (uint8_t*)p.out2 + (prow * (int64_t)I + n0) * 2;
                 float dot = 0.f;
 #pragma unroll 1
-                for (int c = 0; c < BN; c += 32) {
+                for (int c = half * (BN / 2); c < (half + 1) * (BN / 2); c += 32) {
                     uint32_t u[32];
                     tc_ld32(taddr + c, u);
                     tc_wait_ld();
