@@ -154,8 +154,17 @@ int b200moe_swiglu_unchunked_backward(const void* x, int64_t ldx, const void* dy
  * come from b200moe_route.  m_cap = rows of the padded grouped buffers.
  * ------------------------------------------------------------------------------------------------ */
 
+/* Rows of a (T, width) tensor copied into the padded grouped order: out[p, :] = src[row_map[p], :], zeros where
+ * row_map[p] < 0; out has `rows` rows (the padded row count).  Replaces the `group` calls that materialise the
+ * grouped input and the grouped upstream gradient (SMT/ops.py:213-233); the GEMM kernels then read the result
+ * with TMA.  The kernels below also accept row_token themselves (gather fused into the operand load); the
+ * layer path pre-gathers because one 16-byte-per-thread HBM pass is cheaper than a gathered operand load. */
+int b200moe_gather_rows(const void* src, int64_t lds, const int32_t* row_map, void* out, int64_t ldo, int64_t rows,
+                        int width, int dtype, b200moe_stream_t stream);
+
 /* Up projection with the token gather on the input rows and SwiGLU in the epilogue:
  * h[p, :] = x[row_token[p], :] @ w_fc[e(p)]^T  (Mcap, 2I), a[p, :] = h[p, :I] * silu(h[p, I:])  (Mcap, I).
+ * row_token == NULL: x already holds the padded grouped rows (m_cap rows, see b200moe_gather_rows).
  * Replaces scatter2scatter for c_fc plus the activation call (SMT/__init__.py:83-91). */
 int b200moe_up_forward(const void* x, int64_t ldx, const void* w_fc, const int64_t* expert_offsets,
                        const int32_t* row_token, void* h, void* a, int64_t T, int H, int I, int E,
@@ -176,6 +185,7 @@ int b200moe_down_forward(const void* a, const void* w_proj, const int64_t* exper
  *   d_gates[row_slot[p]] = <act[p, :], u[p, :]>          (fp32, M entries, overwritten)
  *   dh[p, :] = SwiGLU backward of h[p, :] for upstream g*u[p, :]   (Mcap, 2I)
  *   ag[p, :] = g * act[p, :]                                        (Mcap, I)
+ * row_token == NULL: grad_out already holds the padded grouped rows (m_cap rows).
  * Replaces, for c_proj: the d_gates bmm, group(coeff=gates), scatter2scatter (SMT/ops.py:204-256) and the
  * activation backward between the two projections
  * (cute_kernels/kernels/swiglu_unchunked/triton_implementation/kernels_backward.py:13-48). */

@@ -75,6 +75,7 @@ def _declare(lib):
         "b200moe_scatter2scatter": (i32, [vp, i64, vp, i64, i64, i64, vp, vp, vp, i64, i64, i32, i32, i32, i32, i32, i32, i32, vp, i64, vp, vp]),
         "b200moe_group_bwd_W": (i32, [vp, i64, vp, i64, vp, vp, i64, i64, i64, i64, i32, i32, i32, i32, vp, vp]),
         "b200moe_group": (i32, [vp, i64, vp, vp, i64, vp, i32, i64, i32, i32, vp]),
+        "b200moe_gather_rows": (i32, [vp, i64, vp, vp, i64, i64, i32, i32, vp]),
         "b200moe_combine": (i32, [vp, i64, vp, vp, i64, i64, i32, i32, i32, vp]),
         "b200moe_swiglu_unchunked_forward": (i32, [vp, i64, vp, i64, i64, i32, i32, vp]),
         "b200moe_swiglu_unchunked_backward": (i32, [vp, i64, vp, i64, vp, i64, i64, i32, i32, vp]),

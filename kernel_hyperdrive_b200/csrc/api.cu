@@ -227,8 +227,7 @@ extern "C" int b200moe_up_forward(const void* x, int64_t ldx, const void* w_fc, 
     cudaStream_t stream = (cudaStream_t)stream_;
     REQUIRE_COMMON("up_forward");
     if (m_cap == 0) return B200MOE_OK;
-    B200MOE_REQUIRE(x && w_fc && expert_offsets && row_token && h && a && T >= 0, B200MOE_ERR_ARG,
-                    "up_forward: NULL pointer");
+    B200MOE_REQUIRE(x && w_fc && expert_offsets && h && a && T >= 0, B200MOE_ERR_ARG, "up_forward: NULL pointer");
     RowGemm g{};
     g.A = x;
     g.lda = ldx;
@@ -296,8 +295,8 @@ extern "C" int b200moe_down_dgrad(const void* grad_out, int64_t ldg, const void*
     cudaStream_t stream = (cudaStream_t)stream_;
     REQUIRE_COMMON("down_dgrad");
     if (m_cap == 0 || M == 0) return B200MOE_OK;
-    B200MOE_REQUIRE(grad_out && w_proj && expert_offsets && row_token && row_slot && h && dh && ag && d_gates,
-                    B200MOE_ERR_ARG, "down_dgrad: NULL pointer");
+    B200MOE_REQUIRE(grad_out && w_proj && expert_offsets && row_slot && h && dh && ag && d_gates, B200MOE_ERR_ARG,
+                    "down_dgrad: NULL pointer");
     RowGemm g{};
     g.A = grad_out;
     g.lda = ldg;

@@ -41,6 +41,26 @@ __global__ void group_kernel(const T* __restrict__ A, int64_t lda, const int64_t
     }
 }
 
+// ---- gather into the padded grouped order -----------------------------------------------------------
+template <typename T, int V>
+__global__ void gather_rows_kernel(const T* __restrict__ src, int64_t lds, const int32_t* __restrict__ row_map,
+                                   T* __restrict__ out, int64_t ldo, int64_t rows, int width) {
+    int64_t p = blockIdx.x;
+    if (p >= rows) return;
+    int r = row_map[p];
+    T* dst = out + p * ldo;
+    if (r < 0) {  // filler row: zeros
+        Pack<T, V> z;
+#pragma unroll
+        for (int i = 0; i < V; ++i) z.v[i] = Elem<T>::from_f(0.f);
+        for (int col = threadIdx.x * V; col < width; col += blockDim.x * V) *reinterpret_cast<Pack<T, V>*>(dst + col) = z;
+        return;
+    }
+    const T* s = src + (int64_t)r * lds;
+    for (int col = threadIdx.x * V; col < width; col += blockDim.x * V)
+        *reinterpret_cast<Pack<T, V>*>(dst + col) = *reinterpret_cast<const Pack<T, V>*>(s + col);
+}
+
 // ---- combine -------------------------------------------------------------------------------------
 template <typename T, int V>
 __global__ void combine_kernel(const T* __restrict__ in, int64_t ldi, const T* __restrict__ gates,
@@ -243,6 +263,28 @@ extern "C" int b200moe_group(const void* A, int64_t lda, const int64_t* idx, voi
         }
         count_launch();
         return check_launch("group");
+    });
+}
+
+extern "C" int b200moe_gather_rows(const void* src, int64_t lds, const int32_t* row_map, void* out, int64_t ldo,
+                                   int64_t rows, int width, int dtype, b200moe_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    B200MOE_REQUIRE(rows >= 0 && width >= 0, B200MOE_ERR_ARG, "gather_rows: bad sizes");
+    if (rows == 0 || width == 0) return B200MOE_OK;
+    B200MOE_REQUIRE(src && row_map && out, B200MOE_ERR_ARG, "gather_rows: NULL pointer");
+    return dispatch_dtype(dtype, [&](auto tag) {
+        using T = decltype(tag);
+        constexpr int V = vec_elems<T>();
+        bool vec = width % V == 0 && lds % V == 0 && ldo % V == 0 && aligned16(src) && aligned16(out);
+        if (vec) {
+            gather_rows_kernel<T, V><<<(unsigned)rows, row_threads(width, V), 0, stream>>>((const T*)src, lds, row_map, (T*)out,
+                                                                                        ldo, rows, width);
+        } else {
+            gather_rows_kernel<T, 1><<<(unsigned)rows, row_threads(width, 1), 0, stream>>>((const T*)src, lds, row_map, (T*)out,
+                                                                                        ldo, rows, width);
+        }
+        count_launch();
+        return check_launch("gather_rows");
     });
 }
 

@@ -23,6 +23,7 @@
 // out.  Nothing here uses cluster multicast.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -75,6 +76,7 @@ struct UmmaParams {
     uint32_t idesc;
     int is_f16;
     int full_count;  // arrivals per full barrier
+    int dbg;
 };
 
 // ---- PTX wrappers --------------------------------------------------------------------------------
@@ -616,7 +618,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     tc_ld32(taddr + c, u);
                     tc_ld32(taddr + 128 + c, gt);
                     tc_wait_ld();
-                    if (row_ok) {
+                    if (row_ok && !(p.dbg & 4)) {
 #pragma unroll
                         for (int qd = 0; qd < 4; ++qd) {
                             if (n0 + c + qd * 8 < I) {
@@ -627,10 +629,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                                     hg[i] = pack2(__uint_as_float(gt[qd * 8 + 2 * i]), __uint_as_float(gt[qd * 8 + 2 * i + 1]), is_f16);
                                     // the activation sees the values as stored (rounded to the tensor type)
                                     float2 fu = unpack2(hu[i], is_f16), fg = unpack2(hg[i], is_f16);
+                                    if (p.dbg & 2) av[i] = hu[i] ^ hg[i]; else
                                     av[i] = pack2(fu.x * fg.x * sigmoidf_stable(fg.x), fu.y * fg.y * sigmoidf_stable(fg.y), is_f16);
                                 }
+                                if (!(p.dbg & 1)) {
                                 *reinterpret_cast<uint4*>(hrow + (c + qd * 8) * 2) = make_uint4(hu[0], hu[1], hu[2], hu[3]);
                                 *reinterpret_cast<uint4*>(hrow + ((int64_t)I + c + qd * 8) * 2) = make_uint4(hg[0], hg[1], hg[2], hg[3]);
+                                }
+                                if (!(p.dbg & 8))
                                 *reinterpret_cast<uint4*>(arow + (c + qd * 8) * 2) = make_uint4(av[0], av[1], av[2], av[3]);
                             }
                         }
@@ -826,6 +832,7 @@ int umma_row_gemm(const RowGemm& g, int dtype, int32_t* status, cudaStream_t str
     p.status = status;
     p.idesc = make_idesc(0, p.b_mn, p.is_f16);
     p.full_count = 1 + (p.a_tma ? 0 : GATHER_THREADS);
+    { const char* d = getenv("B200MOE_DBG"); p.dbg = d ? atoi(d) : 0; }
 
     CUtensorMap ma{}, mb{};
     int rc;

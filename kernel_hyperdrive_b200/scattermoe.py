@@ -174,8 +174,17 @@ def _launch(name: str, fn, *args) -> None:
 
 
 
+@b200_op("gather_rows", mutates_args={"out"})
+def _gather_rows(src: torch.Tensor, row_map: torch.Tensor, out: torch.Tensor) -> None:
+    """out[p, :] = src[row_map[p], :], zeros where row_map[p] < 0 (rows of the padded grouped order)."""
+    check(
+        lib().b200moe_gather_rows(ptr(src), src.stride(0), ptr(row_map), ptr(out), out.stride(0), out.size(0), src.size(1), dtype_code(src), stream_ptr(src.device)),
+        "gather_rows",
+    )
+
+
 @b200_op("up_forward", mutates_args={"h", "a"})
-def _up_forward(x: torch.Tensor, w_fc: torch.Tensor, expert_offsets: torch.Tensor, row_token: torch.Tensor, h: torch.Tensor, a: torch.Tensor) -> None:
+def _up_forward(x: torch.Tensor, w_fc: torch.Tensor, expert_offsets: torch.Tensor, row_token: torch.Tensor | None, h: torch.Tensor, a: torch.Tensor) -> None:
     E, I2, H = w_fc.shape
     check(
         lib().b200moe_up_forward(ptr(x), x.stride(0), ptr(w_fc), ptr(expert_offsets), ptr(row_token), ptr(h), ptr(a), x.size(0), H, I2 // 2, E, h.size(0), dtype_code(x), ptr(status_word(x.device)), stream_ptr(x.device)),
@@ -193,7 +202,7 @@ def _down_forward(a: torch.Tensor, w_proj: torch.Tensor, expert_offsets: torch.T
 
 
 @b200_op("down_dgrad", mutates_args={"dh", "ag", "d_gates"})
-def _down_dgrad(grad_out: torch.Tensor, w_proj: torch.Tensor, expert_offsets: torch.Tensor, row_token: torch.Tensor, row_slot: torch.Tensor, gates: torch.Tensor | None, h: torch.Tensor, dh: torch.Tensor, ag: torch.Tensor, d_gates: torch.Tensor) -> None:
+def _down_dgrad(grad_out: torch.Tensor, w_proj: torch.Tensor, expert_offsets: torch.Tensor, row_token: torch.Tensor | None, row_slot: torch.Tensor, gates: torch.Tensor | None, h: torch.Tensor, dh: torch.Tensor, ag: torch.Tensor, d_gates: torch.Tensor) -> None:
     E, H, I = w_proj.shape
     check(
         lib().b200moe_down_dgrad(
@@ -247,7 +256,11 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
         cap = row_token.numel()
         h = torch.empty(cap, I2, device=x.device, dtype=x.dtype)
         a = torch.empty(cap, I, device=x.device, dtype=x.dtype)
-        _launch("up_forward", _up_forward, x, w_fc, offsets, row_token, h, a)
+        # rows of x in the padded grouped order: one HBM pass, after which every operand is a plain TMA tile
+        x_rows = torch.empty(cap, H, device=x.device, dtype=x.dtype)
+        _gather_rows(x, row_token, x_rows)
+        _launch("up_forward", _up_forward, x_rows, w_fc, offsets, None, h, a)
+        del x_rows  # re-gathered in the backward pass: cheaper than keeping k copies of every token alive
         y_expanded = torch.empty(M, H, device=x.device, dtype=x.dtype)
         _launch("down_forward", _down_forward, a, w_proj, offsets, row_slot, gates, y_expanded)
         if k == 1:
@@ -274,16 +287,21 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
         dh = torch.empty(cap, I2, device=x.device, dtype=x.dtype)
         ag = torch.empty(cap, I, device=x.device, dtype=x.dtype)
         d_gates = torch.empty(M, device=x.device, dtype=torch.float32)
-        _launch("down_dgrad", _down_dgrad, grad_y, w_proj, offsets, row_token, row_slot, gates, h, dh, ag, d_gates)
+        g_rows = torch.empty(cap, H, device=x.device, dtype=x.dtype)
+        _gather_rows(grad_y, row_token, g_rows)
+        _launch("down_dgrad", _down_dgrad, g_rows, w_proj, offsets, None, row_slot, gates, h, dh, ag, d_gates)
 
         d_w_proj = d_w_fc = d_x = d_rw = None
         if need_w2:
             d_w_proj = torch.empty_like(w_proj)
-            _launch("down_wgrad", _wgrad, grad_y, row_token, ag, None, offsets, d_w_proj, cap)
+            _launch("down_wgrad", _wgrad, g_rows, None, ag, None, offsets, d_w_proj, cap)
         del ag
         if need_w1:
             d_w_fc = torch.empty_like(w_fc)
-            _launch("up_wgrad", _wgrad, dh, None, x, row_token, offsets, d_w_fc, cap)
+            x_rows = g_rows  # the gathered gradient rows are dead now: reuse the buffer
+            _gather_rows(x, row_token, x_rows)
+            _launch("up_wgrad", _wgrad, dh, None, x_rows, None, offsets, d_w_fc, cap)
+        del g_rows
         if need_x:
             dx_expanded = torch.empty(M, H, device=x.device, dtype=x.dtype)
             _launch("up_dgrad", _up_dgrad, dh, w_fc, offsets, row_slot, dx_expanded)
