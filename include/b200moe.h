@@ -97,6 +97,30 @@ int b200moe_route(const int64_t* expert_ids, int64_t M, int E, int k, int64_t* s
                   int32_t* row_token, int32_t* row_slot, int64_t m_cap, void* workspace,
                   int64_t workspace_bytes, int32_t* status, b200moe_stream_t stream);
 
+/* b200moe_route for callers that are not allowed to allocate device memory.  It has no counterpart in the
+ * reference.  Some hosts hand this library a device whose memory is already spoken for: a serving process or
+ * a training framework that reserved one arena at start-up and treats any later cudaMalloc as a fault, or a
+ * caller inside a latency-critical section that cannot afford the device-wide synchronisation an allocation
+ * may imply.  Such a caller has nowhere to take the routing workspace from, so this variant keeps the
+ * workspace inside the library: a fixed array of b200moe_route_static_scratch_bytes() = 262144 bytes of
+ * device memory that is part of the library image (each GPU that loads the library carries it until the
+ * process ends).  Inputs and outputs are still the caller's buffers, with the meaning they have in
+ * b200moe_route.
+ *   - Sizes whose workspace (b200moe_route_workspace_bytes(M, E)) exceeds the array are refused with
+ *     B200MOE_ERR_UNSUPPORTED and a message naming both numbers; nothing is launched.  For example
+ *     E = 8 fits up to about 33 million rows, E = 256 up to about 1 million, E = 512 up to about 0.5 million.
+ *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress) with that device
+ *     current and remembers it; make that first call before starting any stream capture.
+ *   - The call never calls cudaMalloc, cudaFree or any allocating library routine.
+ *   - All calls on one device share the array.  Each call overwrites every word it later reads, so the previous
+ *     call's contents do no harm, but two calls that overlap on the GPU (different streams, no ordering
+ *     between them) race on it: serialise them. */
+int64_t b200moe_route_static_scratch_bytes(void);
+int b200moe_route_static(const int64_t* expert_ids, int64_t M, int E, int k, int64_t* sorted_expert_idxs,
+                         int64_t* sorted_scattered_idxs, int64_t* expert_offsets, int32_t* counts,
+                         int32_t* row_token, int32_t* row_slot, int64_t m_cap, int32_t* status,
+                         b200moe_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------------
  * The reference's four operators, same argument meaning (grouped order WITHOUT padding)
  * ------------------------------------------------------------------------------------------------ */

@@ -71,6 +71,8 @@ def _declare(lib):
         "b200moe_padded_rows_cap": (i64, [i64, i32]),
         "b200moe_route_workspace_bytes": (i64, [i64, i32]),
         "b200moe_route": (i32, [vp, i64, i32, i32, vp, vp, vp, vp, vp, vp, i64, vp, i64, vp, vp]),
+        "b200moe_route_static_scratch_bytes": (i64, []),
+        "b200moe_route_static": (i32, [vp, i64, i32, i32, vp, vp, vp, vp, vp, vp, i64, vp, vp]),
         "b200moe_scatter2scatter_workspace_bytes": (i64, [i64, i32]),
         "b200moe_scatter2scatter": (i32, [vp, i64, vp, i64, i64, i64, vp, vp, vp, i64, i64, i32, i32, i32, i32, i32, i32, i32, vp, i64, vp, vp]),
         "b200moe_group_bwd_W": (i32, [vp, i64, vp, i64, vp, vp, i64, i64, i64, i64, i32, i32, i32, i32, vp, vp]),

@@ -1,6 +1,8 @@
 // Routing kernels: histogram of expert ids, stable counting sort by expert, inclusive offsets and the
 // row maps of the padded grouped order.  Integer work, bit-exact against torch.sort(stable=True),
 // bincount and cumsum.  HBM-bound (8 bytes read per id, 16-24 bytes written per routed row).
+#include <mutex>
+
 #include "common.cuh"
 
 namespace b200moe {
@@ -268,4 +270,58 @@ extern "C" int b200moe_route(const int64_t* expert_ids, int64_t M, int E, int k,
         count_launch();
     }
     return check_launch("route");
+}
+
+// ---- routing for callers that cannot allocate ------------------------------------------------------
+// Scratch of b200moe_route_static: lives in the library image, so every GPU that loads the library holds
+// these bytes until the process exits.  In host code the array's name is only a stand-in; the device
+// address comes from cudaGetSymbolAddress, looked up once per device below.
+constexpr int64_t kStaticRouteScratchBytes = 256 * 1024;
+static __device__ __align__(256) unsigned char g_route_static_scratch[kStaticRouteScratchBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_route_static_mutex;
+void* g_route_static_ptr[kMaxDevices] = {nullptr};
+}  // namespace
+
+extern "C" int64_t b200moe_route_static_scratch_bytes(void) { return kStaticRouteScratchBytes; }
+
+extern "C" int b200moe_route_static(const int64_t* expert_ids, int64_t M, int E, int k, int64_t* sorted_expert_idxs,
+                                    int64_t* sorted_scattered_idxs, int64_t* expert_offsets, int32_t* counts,
+                                    int32_t* row_token, int32_t* row_slot, int64_t m_cap, int32_t* status,
+                                    b200moe_stream_t stream) {
+    B200MOE_REQUIRE(E > 0 && E <= kMaxExperts, B200MOE_ERR_UNSUPPORTED, "route_static: E=%d outside [1, %d]", E, kMaxExperts);
+    B200MOE_REQUIRE(M >= 0, B200MOE_ERR_ARG, "route_static: negative M");
+    int64_t need = b200moe_route_workspace_bytes(M, E);
+    B200MOE_REQUIRE(need <= kStaticRouteScratchBytes, B200MOE_ERR_UNSUPPORTED,
+                    "route_static: M=%lld rows with E=%d experts need %lld bytes of scratch but the built-in array holds %lld; "
+                    "use b200moe_route with a caller-owned workspace for this size",
+                    (long long)M, E, (long long)need, (long long)kStaticRouteScratchBytes);
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        cudaGetLastError();
+        set_error_detail("route_static: cannot identify the current device");
+        return B200MOE_ERR_LAUNCH;
+    }
+    void* scratch = nullptr;
+    {
+        // set-up, once per device, with that device current (first call on the device)
+        std::lock_guard<std::mutex> lock(g_route_static_mutex);
+        if (g_route_static_ptr[dev] == nullptr) {
+            void* p = nullptr;
+            cudaError_t err = cudaGetSymbolAddress(&p, g_route_static_scratch);
+            if (err != cudaSuccess || p == nullptr) {
+                cudaGetLastError();
+                set_error_detail("route_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(err));
+                return B200MOE_ERR_LAUNCH;
+            }
+            g_route_static_ptr[dev] = p;
+        }
+        scratch = g_route_static_ptr[dev];
+    }
+    // Every scratch word the kernels read is written earlier in the same call (per-block histograms, then
+    // the scans), so nothing needs clearing between calls.
+    return b200moe_route(expert_ids, M, E, k, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets, counts, row_token,
+                         row_slot, m_cap, scratch, kStaticRouteScratchBytes, status, stream);
 }
