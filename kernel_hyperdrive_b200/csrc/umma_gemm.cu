@@ -23,7 +23,6 @@
 // out.  Nothing here uses cluster multicast.
 #include <cuda.h>
 
-#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -33,12 +32,16 @@ namespace b200moe {
 namespace {
 
 constexpr int BM = 128, BN = 256, BK = 64;
-constexpr int STAGES = 4;
+#ifndef B200MOE_STAGES
+#define B200MOE_STAGES 4
+#endif
+constexpr int STAGES = B200MOE_STAGES;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KB
 constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KB
 constexpr int EPI_WARPS = 8;                        // two warps per TMEM lane quarter, each takes half the columns
 constexpr int NUM_THREADS = (6 + EPI_WARPS) * 32;   // 448
 constexpr int GATHER_THREADS = 128;
+constexpr int STG_BYTES = 32 * 32 * 2;  // epilogue staging: 32 rows x 32 columns of 16-bit elements, 64-byte swizzle
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
 
 struct UmmaParams {
@@ -76,7 +79,7 @@ struct UmmaParams {
     uint32_t idesc;
     int is_f16;
     int full_count;  // arrivals per full barrier
-    int dbg;
+    int o3d;         // output tensor map is 3-D (expert, row, column): weight gradients
 };
 
 // ---- PTX wrappers --------------------------------------------------------------------------------
@@ -140,6 +143,26 @@ __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint3
 __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
+
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"((uint64_t)map), "r"(src),
+                 "r"(c0), "r"(c1)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"((uint64_t)map),
+                 "r"(src), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+// 1 / (1 + exp(-x)) with the fast exponential and division; exp overflow gives 1 / inf = 0, never NaN
+__device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -257,12 +280,14 @@ __device__ __forceinline__ void decode_tile(const UmmaParams& p, const Tables& t
 template <int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     umma_grouped_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a,
-                        const __grid_constant__ CUtensorMap tmap_b) {
+                        const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_o,
+                        const __grid_constant__ CUtensorMap tmap_o2, const __grid_constant__ CUtensorMap tmap_o3) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* smem_a = smem;
     uint8_t* smem_b = smem + STAGES * A_STAGE_BYTES;
-    uint64_t* bars = (uint64_t*)(smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES));
+    uint8_t* smem_stg = smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);  // one 2 KB output box per epilogue warp
+    uint64_t* bars = (uint64_t*)(smem_stg + EPI_WARPS * STG_BYTES);
     uint64_t* full_bar = bars;
     uint64_t* empty_bar = bars + STAGES;
     uint64_t* tmem_full_bar = bars + 2 * STAGES;
@@ -548,6 +573,30 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const int r = q * 32 + lane;          // row of the tile this thread owns
         const int half = (warp - 6) >> 2;     // which half of the tile's columns this warp handles
         const int is_f16 = p.is_f16;
+        // Outputs that are whole rows of a row-major matrix leave through shared memory: the warp writes its
+        // 32 x 32 box (64-byte rows, 64-byte swizzle, conflict-free) and one lane hands it to TMA, which
+        // stores full sectors.  The box is reused for every output, so the lane first waits until the
+        // previous store has finished reading it.
+        const uint32_t stg = smem_u32(smem_stg + (warp - 6) * STG_BYTES);
+        const uint32_t stg_row = stg + lane * 64;
+        const uint32_t stg_swz = (uint32_t)((lane >> 1) & 3);
+        auto stage_store = [&](const CUtensorMap* map, int c0, int c1, int c2, const uint32_t (&pk)[16]) {
+            if (lane == 0) bulk_wait_read0();
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                st_shared_v4(stg_row + ((j ^ stg_swz) << 4), pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                if (p.o3d) {
+                    tma_store_3d(map, stg, c0, c1, c2);
+                } else {
+                    tma_store_2d(map, stg, c0, c1);
+                }
+                bulk_commit();
+            }
+        };
         int acc = 0;
         uint32_t acc_phase = 0;
         Tile ti;
@@ -559,133 +608,129 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             const bool have_acc = ti.ksteps > 0;
 
             if (EPI == EPI_STORE) {
-                bool row_ok;
-                int64_t dst;
-                float sc = 1.f;
-                uint8_t* orow;
-                int n0;
-                if (p.wfam) {
-                    int m = ti.mb * BM + r;
-                    row_ok = m < p.Mout;
-                    dst = m;
-                    n0 = ti.nb * BN;
-                    orow = (uint8_t*)p.out + ((int64_t)ti.e * p.d_se + dst * p.ldo + n0) * 2;
+                const int n0 = ti.nb * BN;
+                // whole-row output (weight gradients; grouped rows when this warp's 32 rows are all real)
+                const bool via_tma = p.wfam || (p.o_map == nullptr && p.scale == nullptr && q * 32 + 32 <= ti.rows_valid);
+                if (via_tma) {
+                    const int row_c = p.wfam ? ti.mb * BM + q * 32 : ti.row0 + q * 32;
+#pragma unroll 1
+                    for (int c = half * (BN / 2); c < (half + 1) * (BN / 2); c += 32) {
+                        if (n0 + c >= p.N) break;
+                        uint32_t v[32], pk[16];
+                        if (have_acc) {
+                            tc_ld32(taddr + c, v);
+                            tc_wait_ld();
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] = 0u;
+                        }
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) pk[i] = pack2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]), is_f16);
+                        stage_store(&tmap_o, n0 + c, row_c, ti.e, pk);
+                    }
                 } else {
-                    row_ok = r < ti.rows_valid;
+                    bool row_ok = r < ti.rows_valid;
                     int d = -1;
                     if (row_ok) d = p.o_map ? p.o_map[ti.row0 + r] : ti.row0 + r;
                     row_ok = d >= 0;
-                    dst = d;
+                    const int64_t dst = d;
+                    float sc = 1.f;
                     if (row_ok && p.scale) sc = load_scalar(p.scale, dst, is_f16);
-                    n0 = ti.nb * BN;
-                    orow = (uint8_t*)p.out + (dst * p.ldo + n0) * 2;
-                }
+                    uint8_t* orow = (uint8_t*)p.out + (dst * p.ldo + n0) * 2;
 #pragma unroll 1
-                for (int c = half * (BN / 2); c < (half + 1) * (BN / 2); c += 32) {
-                    uint32_t v[32];
-                    if (have_acc) {
-                        tc_ld32(taddr + c, v);
-                        tc_wait_ld();
-                    } else {
+                    for (int c = half * (BN / 2); c < (half + 1) * (BN / 2); c += 32) {
+                        uint32_t v[32];
+                        if (have_acc) {
+                            tc_ld32(taddr + c, v);
+                            tc_wait_ld();
+                        } else {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = 0u;
-                    }
-                    if (row_ok) {
+                            for (int i = 0; i < 32; ++i) v[i] = 0u;
+                        }
+                        if (row_ok) {
 #pragma unroll
-                        for (int qd = 0; qd < 4; ++qd) {
-                            if (n0 + c + qd * 8 < p.N) {
-                                uint4 o;
-                                o.x = pack2(__uint_as_float(v[qd * 8 + 0]) * sc, __uint_as_float(v[qd * 8 + 1]) * sc, is_f16);
-                                o.y = pack2(__uint_as_float(v[qd * 8 + 2]) * sc, __uint_as_float(v[qd * 8 + 3]) * sc, is_f16);
-                                o.z = pack2(__uint_as_float(v[qd * 8 + 4]) * sc, __uint_as_float(v[qd * 8 + 5]) * sc, is_f16);
-                                o.w = pack2(__uint_as_float(v[qd * 8 + 6]) * sc, __uint_as_float(v[qd * 8 + 7]) * sc, is_f16);
-                                *reinterpret_cast<uint4*>(orow + (c + qd * 8) * 2) = o;
+                            for (int qd = 0; qd < 4; ++qd) {
+                                if (n0 + c + qd * 8 < p.N) {
+                                    uint4 o;
+                                    o.x = pack2(__uint_as_float(v[qd * 8 + 0]) * sc, __uint_as_float(v[qd * 8 + 1]) * sc, is_f16);
+                                    o.y = pack2(__uint_as_float(v[qd * 8 + 2]) * sc, __uint_as_float(v[qd * 8 + 3]) * sc, is_f16);
+                                    o.z = pack2(__uint_as_float(v[qd * 8 + 4]) * sc, __uint_as_float(v[qd * 8 + 5]) * sc, is_f16);
+                                    o.w = pack2(__uint_as_float(v[qd * 8 + 6]) * sc, __uint_as_float(v[qd * 8 + 7]) * sc, is_f16);
+                                    *reinterpret_cast<uint4*>(orow + (c + qd * 8) * 2) = o;
+                                }
                             }
                         }
                     }
                 }
             } else if (EPI == EPI_SWIGLU) {
-                // accumulator columns [0,128) = up, [128,256) = gate, for output columns nb*128 .. +128 of each half
+                // accumulator columns [0,128) = up, [128,256) = gate, for output columns nb*128 .. +128 of each half;
+                // the layout is the padded grouped order, so all 128 rows of the tile are written (fillers get zeros)
                 const int I = p.swiglu_half;
-                const bool row_ok = r < ti.rows_valid;
-                const int64_t prow = ti.row0 + r;
                 const int n0 = ti.nb * 128;
-                uint8_t* hrow = (uint8_t*)p.out + (prow * p.ldo + n0) * 2;
-                uint8_t* arow = (uint8_t*)p.out2 + (prow * (int64_t)I + n0) * 2;
+                const int row_c = ti.row0 + q * 32;
 #pragma unroll 1
                 for (int c = half * 64; c < (half + 1) * 64; c += 32) {
-                    uint32_t u[32], gt[32];
+                    if (n0 + c >= I) break;
+                    uint32_t u[32], gt[32], hu[16], hg[16], av[16];
                     tc_ld32(taddr + c, u);
                     tc_ld32(taddr + 128 + c, gt);
                     tc_wait_ld();
-                    if (row_ok && !(p.dbg & 4)) {
 #pragma unroll
-                        for (int qd = 0; qd < 4; ++qd) {
-                            if (n0 + c + qd * 8 < I) {
-                                uint32_t hu[4], hg[4], av[4];
-#pragma unroll
-                                for (int i = 0; i < 4; ++i) {
-                                    hu[i] = pack2(__uint_as_float(u[qd * 8 + 2 * i]), __uint_as_float(u[qd * 8 + 2 * i + 1]), is_f16);
-                                    hg[i] = pack2(__uint_as_float(gt[qd * 8 + 2 * i]), __uint_as_float(gt[qd * 8 + 2 * i + 1]), is_f16);
-                                    // the activation sees the values as stored (rounded to the tensor type)
-                                    float2 fu = unpack2(hu[i], is_f16), fg = unpack2(hg[i], is_f16);
-                                    if (p.dbg & 2) av[i] = hu[i] ^ hg[i]; else
-                                    av[i] = pack2(fu.x * fg.x * sigmoidf_stable(fg.x), fu.y * fg.y * sigmoidf_stable(fg.y), is_f16);
-                                }
-                                if (!(p.dbg & 1)) {
-                                *reinterpret_cast<uint4*>(hrow + (c + qd * 8) * 2) = make_uint4(hu[0], hu[1], hu[2], hu[3]);
-                                *reinterpret_cast<uint4*>(hrow + ((int64_t)I + c + qd * 8) * 2) = make_uint4(hg[0], hg[1], hg[2], hg[3]);
-                                }
-                                if (!(p.dbg & 8))
-                                *reinterpret_cast<uint4*>(arow + (c + qd * 8) * 2) = make_uint4(av[0], av[1], av[2], av[3]);
-                            }
-                        }
+                    for (int i = 0; i < 16; ++i) {
+                        hu[i] = pack2(__uint_as_float(u[2 * i]), __uint_as_float(u[2 * i + 1]), is_f16);
+                        hg[i] = pack2(__uint_as_float(gt[2 * i]), __uint_as_float(gt[2 * i + 1]), is_f16);
+                        // the activation sees the values as stored (rounded to the tensor type)
+                        float2 fu = unpack2(hu[i], is_f16), fg = unpack2(hg[i], is_f16);
+                        av[i] = pack2(fu.x * fg.x * sigmoid_fast(fg.x), fu.y * fg.y * sigmoid_fast(fg.y), is_f16);
                     }
+                    stage_store(&tmap_o, n0 + c, row_c, 0, hu);    // up half of h
+                    stage_store(&tmap_o3, n0 + c, row_c, 0, hg);   // gate half of h (its own map: columns clip at I)
+                    stage_store(&tmap_o2, n0 + c, row_c, 0, av);   // activation
                 }
             } else {  // EPI_DGRAD_DOWN
                 const int I = p.N;
-                const bool row_ok = r < ti.rows_valid;
                 const int64_t prow = ti.row0 + r;
                 const int n0 = ti.nb * BN;
-                int slot = -1;
-                if (row_ok) slot = p.g_map[prow];
+                const int row_c = ti.row0 + q * 32;
+                const int slot = p.g_map[prow];
                 float g = 0.f;
                 if (slot >= 0) g = p.scale ? load_scalar(p.scale, slot, is_f16) : 1.f;
                 const uint8_t* hrow = (const uint8_t*)p.h + (prow * 2 * (int64_t)I + n0) * 2;
-                uint8_t* dhrow = (uint8_t*)p.out + (prow * 2 * (int64_t)I + n0) * 2;
-                uint8_t* agrow = (uint8_t*)p.out2 + (prow * (int64_t)I + n0) * 2;
                 float dot = 0.f;
 #pragma unroll 1
                 for (int c = half * (BN / 2); c < (half + 1) * (BN / 2); c += 32) {
-                    uint32_t u[32];
+                    if (n0 + c >= I) break;
+                    // the pre-activation values of this row: requested before the accumulator is read
+                    uint4 hu4[4], hg4[4];
+#pragma unroll
+                    for (int qd = 0; qd < 4; ++qd) {
+                        bool in = n0 + c + qd * 8 < I;
+                        hu4[qd] = in ? *reinterpret_cast<const uint4*>(hrow + (c + qd * 8) * 2) : make_uint4(0, 0, 0, 0);
+                        hg4[qd] = in ? *reinterpret_cast<const uint4*>(hrow + ((int64_t)I + c + qd * 8) * 2) : make_uint4(0, 0, 0, 0);
+                    }
+                    uint32_t u[32], du[16], dg[16], ag[16];
                     tc_ld32(taddr + c, u);
                     tc_wait_ld();
-                    if (row_ok) {
 #pragma unroll
-                        for (int qd = 0; qd < 4; ++qd) {
-                            if (n0 + c + qd * 8 < I) {
-                                uint4 hu = *reinterpret_cast<const uint4*>(hrow + (c + qd * 8) * 2);
-                                uint4 hg = *reinterpret_cast<const uint4*>(hrow + ((int64_t)I + c + qd * 8) * 2);
-                                const uint32_t hua[4] = {hu.x, hu.y, hu.z, hu.w}, hga[4] = {hg.x, hg.y, hg.z, hg.w};
-                                uint32_t du[4], dg[4], ag[4];
+                    for (int qd = 0; qd < 4; ++qd) {
+                        const uint32_t hua[4] = {hu4[qd].x, hu4[qd].y, hu4[qd].z, hu4[qd].w};
+                        const uint32_t hga[4] = {hg4[qd].x, hg4[qd].y, hg4[qd].z, hg4[qd].w};
 #pragma unroll
-                                for (int i = 0; i < 4; ++i) {
-                                    float2 up = unpack2(hua[i], is_f16), gt = unpack2(hga[i], is_f16);
-                                    float u0 = __uint_as_float(u[qd * 8 + 2 * i]), u1 = __uint_as_float(u[qd * 8 + 2 * i + 1]);
-                                    float s0 = sigmoidf_stable(gt.x), s1 = sigmoidf_stable(gt.y);
-                                    float a0 = round_elem(up.x * gt.x * s0, is_f16), a1 = round_elem(up.y * gt.y * s1, is_f16);
-                                    dot += a0 * u0 + a1 * u1;
-                                    float d0 = round_elem(g * u0, is_f16), d1 = round_elem(g * u1, is_f16);
-                                    du[i] = pack2(d0 * gt.x * s0, d1 * gt.y * s1, is_f16);
-                                    dg[i] = pack2(d0 * up.x * (s0 + gt.x * s0 * (1.f - s0)), d1 * up.y * (s1 + gt.y * s1 * (1.f - s1)), is_f16);
-                                    ag[i] = pack2(g * a0, g * a1, is_f16);
-                                }
-                                *reinterpret_cast<uint4*>(dhrow + (c + qd * 8) * 2) = make_uint4(du[0], du[1], du[2], du[3]);
-                                *reinterpret_cast<uint4*>(dhrow + ((int64_t)I + c + qd * 8) * 2) = make_uint4(dg[0], dg[1], dg[2], dg[3]);
-                                *reinterpret_cast<uint4*>(agrow + (c + qd * 8) * 2) = make_uint4(ag[0], ag[1], ag[2], ag[3]);
-                            }
+                        for (int i = 0; i < 4; ++i) {
+                            float2 up = unpack2(hua[i], is_f16), gt = unpack2(hga[i], is_f16);
+                            float u0 = __uint_as_float(u[qd * 8 + 2 * i]), u1 = __uint_as_float(u[qd * 8 + 2 * i + 1]);
+                            float s0 = sigmoid_fast(gt.x), s1 = sigmoid_fast(gt.y);
+                            float a0 = round_elem(up.x * gt.x * s0, is_f16), a1 = round_elem(up.y * gt.y * s1, is_f16);
+                            dot += a0 * u0 + a1 * u1;
+                            float d0 = round_elem(g * u0, is_f16), d1 = round_elem(g * u1, is_f16);
+                            du[qd * 4 + i] = pack2(d0 * gt.x * s0, d1 * gt.y * s1, is_f16);
+                            dg[qd * 4 + i] = pack2(d0 * up.x * (s0 + gt.x * s0 * (1.f - s0)), d1 * up.y * (s1 + gt.y * s1 * (1.f - s1)), is_f16);
+                            ag[qd * 4 + i] = pack2(g * a0, g * a1, is_f16);
                         }
                     }
+                    stage_store(&tmap_o, n0 + c, row_c, 0, du);    // up half of dh
+                    stage_store(&tmap_o3, n0 + c, row_c, 0, dg);   // gate half of dh
+                    stage_store(&tmap_o2, n0 + c, row_c, 0, ag);   // gate-scaled activation
                 }
                 if (slot >= 0) atomicAdd(p.d_gates + slot, dot);
             }
@@ -696,6 +741,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 acc_phase ^= 1;
             }
         }
+        if (lane == 0) bulk_wait0();  // every TMA store issued by this warp has been written
     }
 
     // ---------------- teardown ----------------
@@ -711,7 +757,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     }
 }
 
-constexpr int SMEM_BYTES = 1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 128 + (int)sizeof(Tables) + 64;
+constexpr int SMEM_BYTES = 1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + EPI_WARPS * STG_BYTES + 128 + (int)sizeof(Tables) + 64;
 
 // ---- host side -----------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -729,6 +775,24 @@ EncodeTiledFn encode_fn() {
             fn = (EncodeTiledFn)p;
     });
     return fn;
+}
+
+// Output box of the epilogue: 32 columns x 32 rows (x 1 expert), 64-byte swizzle.  rank 2: [rows][cols] with row
+// stride ld; rank 3: [experts][rows][cols] with expert stride se, so that a tile never spills into the next expert.
+int make_store_map(CUtensorMap* map, const void* base, int64_t experts, int64_t rows, int64_t cols, int64_t ld, int64_t se,
+                   int is_f16) {
+    EncodeTiledFn fn = encode_fn();
+    B200MOE_REQUIRE(fn != nullptr, B200MOE_ERR_DRIVER, "cuTensorMapEncodeTiled not available from the driver");
+    int rank = experts > 0 ? 3 : 2;
+    cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)(experts > 0 ? experts : 1)};
+    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)se * 2};
+    cuuint32_t box[3] = {32u, 32u, 1u};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult rc = fn(map, is_f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, (void*)base, dims,
+                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                     CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    B200MOE_REQUIRE(rc == CUDA_SUCCESS, B200MOE_ERR_DRIVER, "cuTensorMapEncodeTiled (store map) failed with %d", (int)rc);
+    return B200MOE_OK;
 }
 
 // 2-D row-major matrix [rows][cols] with row stride ld (elements), box of 64 columns x box_rows rows.
@@ -765,14 +829,15 @@ uint32_t make_idesc(int a_mn, int b_mn, int is_f16) {
 }
 
 template <int EPI>
-int launch(const UmmaParams& p, const CUtensorMap& ma, const CUtensorMap& mb, cudaStream_t stream) {
+int launch(const UmmaParams& p, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mo2,
+           const CUtensorMap& mo3, cudaStream_t stream) {
     auto kern = umma_grouped_kernel<EPI>;
     cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (err != cudaSuccess) {
         set_error_detail("cudaFuncSetAttribute(smem=%d): %s", SMEM_BYTES, cudaGetErrorString(err));
         return B200MOE_ERR_LAUNCH;
     }
-    kern<<<sm_count(), NUM_THREADS, SMEM_BYTES, stream>>>(p, ma, mb);
+    kern<<<sm_count(), NUM_THREADS, SMEM_BYTES, stream>>>(p, ma, mb, mo, mo2, mo3);
     count_launch();
     return check_launch("umma_grouped_kernel");
 }
@@ -832,7 +897,6 @@ int umma_row_gemm(const RowGemm& g, int dtype, int32_t* status, cudaStream_t str
     p.status = status;
     p.idesc = make_idesc(0, p.b_mn, p.is_f16);
     p.full_count = 1 + (p.a_tma ? 0 : GATHER_THREADS);
-    { const char* d = getenv("B200MOE_DBG"); p.dbg = d ? atoi(d) : 0; }
 
     CUtensorMap ma{}, mb{};
     int rc;
@@ -850,16 +914,39 @@ int umma_row_gemm(const RowGemm& g, int dtype, int32_t* status, cudaStream_t str
     if (rc) return rc;
     if (!p.a_tma) ma = mb;  // unused, but the parameter must hold a valid descriptor
 
+    CUtensorMap mo = mb, mo2 = mb, mo3 = mb;  // placeholders when an output does not go through TMA
+    p.o3d = 0;
     if (g.epi == EPI_SWIGLU) {
+        B200MOE_REQUIRE(g.padded && g.o_map == nullptr, B200MOE_ERR_ARG, "SwiGLU epilogue needs the padded grouped order");
         p.swiglu_half = g.N / 2;
         p.N = g.N;
         p.nb_count = (p.swiglu_half + 127) / 128;
-        return launch<EPI_SWIGLU>(p, ma, mb, stream);
+        // the two halves of h get a map each so that a box at the end of the up half is clipped at column I
+        rc = make_store_map(&mo, g.out, 0, g.rows_cap, g.N / 2, g.ldo, 0, p.is_f16);
+        if (rc) return rc;
+        rc = make_store_map(&mo3, (const uint8_t*)g.out + (int64_t)(g.N / 2) * 2, 0, g.rows_cap, g.N / 2, g.ldo, 0, p.is_f16);
+        if (rc) return rc;
+        rc = make_store_map(&mo2, g.out2, 0, g.rows_cap, g.N / 2, g.N / 2, 0, p.is_f16);
+        if (rc) return rc;
+        return launch<EPI_SWIGLU>(p, ma, mb, mo, mo2, mo3, stream);
     }
     p.N = g.N;
     p.nb_count = (g.N + BN - 1) / BN;
-    if (g.epi == EPI_DGRAD_DOWN) return launch<EPI_DGRAD_DOWN>(p, ma, mb, stream);
-    return launch<EPI_STORE>(p, ma, mb, stream);
+    if (g.epi == EPI_DGRAD_DOWN) {
+        B200MOE_REQUIRE(g.padded && g.o_map == nullptr, B200MOE_ERR_ARG, "dgrad epilogue needs the padded grouped order");
+        rc = make_store_map(&mo, g.out, 0, g.rows_cap, g.N, 2 * (int64_t)g.N, 0, p.is_f16);
+        if (rc) return rc;
+        rc = make_store_map(&mo3, (const uint8_t*)g.out + (int64_t)g.N * 2, 0, g.rows_cap, g.N, 2 * (int64_t)g.N, 0, p.is_f16);
+        if (rc) return rc;
+        rc = make_store_map(&mo2, g.out2, 0, g.rows_cap, g.N, g.N, 0, p.is_f16);
+        if (rc) return rc;
+        return launch<EPI_DGRAD_DOWN>(p, ma, mb, mo, mo2, mo3, stream);
+    }
+    if (g.o_map == nullptr && g.scale == nullptr) {
+        rc = make_store_map(&mo, g.out, 0, g.rows_cap, g.N, g.ldo, 0, p.is_f16);
+        if (rc) return rc;
+    }
+    return launch<EPI_STORE>(p, ma, mb, mo, mo2, mo3, stream);
 }
 
 int umma_w_gemm(const WGemm& g, int dtype, int32_t* status, cudaStream_t stream) {
@@ -908,7 +995,11 @@ int umma_w_gemm(const WGemm& g, int dtype, int32_t* status, cudaStream_t stream)
     } else if (have) {
         mb = ma;
     }
-    return launch<EPI_STORE>(p, ma, mb, stream);
+    CUtensorMap mo{};
+    p.o3d = 1;
+    rc = make_store_map(&mo, g.DW, g.E, g.Mout, g.Nout, g.d_sm, g.d_se, p.is_f16);
+    if (rc) return rc;
+    return launch<EPI_STORE>(p, ma, mb, mo, mo, mo, stream);
 }
 
 }  // namespace b200moe
