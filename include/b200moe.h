@@ -49,6 +49,7 @@ extern "C" {
 #define B200MOE_ENGINE_AUTO 0 /* fp32 -> SIMT, bf16/fp16 -> tcgen05 when the shape allows, else SIMT */
 #define B200MOE_ENGINE_SIMT 1 /* CUDA-core kernels for every dtype (exact fp32 math, cross-checks)   */
 #define B200MOE_ENGINE_UMMA 2 /* tcgen05 only; shapes it cannot take return B200MOE_ERR_LAYOUT       */
+#define B200MOE_ENGINE_UMMA_1CTA 3 /* like UMMA, but never the two-CTA (cta_group::2) kernels     */
 
 typedef void* b200moe_stream_t; /* cudaStream_t */
 

@@ -46,7 +46,7 @@ int pick_engine(const G& g, int dtype, F&& supported, const char* what) {
     int eng = current_engine();
     if (eng == B200MOE_ENGINE_SIMT) return 0;
     bool ok = dtype != B200MOE_F32 && supported(g, dtype);
-    if (eng == B200MOE_ENGINE_UMMA) {
+    if (eng == B200MOE_ENGINE_UMMA || eng == B200MOE_ENGINE_UMMA_1CTA) {
         if (!ok) {
             set_error_detail("%s: shape/dtype not handled by the tcgen05 engine", what);
             return B200MOE_ERR_LAYOUT;
@@ -103,7 +103,7 @@ extern "C" const char* b200moe_error_string(int code) {
 extern "C" const char* b200moe_last_error_detail(void) { return g_detail; }
 
 extern "C" int b200moe_set_engine(int engine) {
-    if (engine < B200MOE_ENGINE_AUTO || engine > B200MOE_ENGINE_UMMA) return B200MOE_ERR_ARG;
+    if (engine < B200MOE_ENGINE_AUTO || engine > B200MOE_ENGINE_UMMA_1CTA) return B200MOE_ERR_ARG;
     return g_engine.exchange(engine);
 }
 

@@ -1,0 +1,374 @@
+// Two-CTA variant of the tensor-core engine: a cluster of two CTAs (two SMs) works on one 256 x 256 output
+// tile with tcgen05.mma.cta_group::2 (M = 256, N = 256, K = 16).
+//
+// Each CTA stages its own 128 rows of operand A and HALF of operand B (128 of the 256 B rows), so a CTA
+// moves 32 KB per 64-deep k step instead of 48 KB: one third less L2 -> shared-memory traffic and
+// shared-memory read bandwidth per FLOP than the one-CTA kernel, and six pipeline stages fit instead of four.
+// The accumulator of a CTA's 128 rows lives in that CTA's tensor memory; each CTA runs its own epilogue.
+//
+// Protocol (rank 0 of the pair is the leader):
+//   * both CTAs' producer lanes wait on their OWN empty barrier, then issue their TMA loads with the
+//     completion bytes counted on the LEADER's full barrier (the leader arms it with the bytes of both CTAs);
+//   * the leader's MMA lane waits on its full barrier, issues the MMAs, and commits to the empty barrier of
+//     BOTH CTAs (one commit per barrier; no multicast) and, at the end of a tile, to both tmem_full barriers;
+//   * every epilogue warp of both CTAs arrives on the LEADER's tmem_empty barrier when it has drained its part
+//     of the accumulator.
+// All operands must be plain TMA tiles (the layer path gathers rows beforehand).  No load uses cluster
+// multicast.  Every wait is bounded like in the one-CTA kernel; a cluster barrier at the end keeps either CTA
+// from exiting while its peer may still signal into its shared memory.
+#include "umma_common.cuh"
+
+namespace b200moe {
+namespace umma {
+
+namespace {
+
+constexpr int STAGES2 = 6;
+constexpr int B_HALF_BYTES = (BN / 2) * BK * 2;  // 16 KB
+constexpr int NUM_THREADS2 = (2 + EPI_WARPS) * 32;  // 320: TMA warp, MMA warp, 8 epilogue warps
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA tile load of one CTA of the pair; `bar` is a shared::cluster address (the leader's full barrier).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+
+// Tile list of the pair kernels.  Family R: a cluster tile is two consecutive 128-row blocks of one expert
+// (the second may not exist when the expert has an odd number of blocks: that CTA then idles through the tile);
+// tile_prefix counts cluster tiles.  Family W: output blocks of 256 x 256, CTA `rank` owns rows 128*rank..+127.
+__device__ __forceinline__ int total_tiles2(const UmmaParams& p, const Tables& tb) {
+    return p.wfam ? p.E * ((p.mb_count + 1) / 2) * p.nb_count : tb.tile_prefix[p.E] * p.nb_count;
+}
+
+__device__ __forceinline__ void decode_tile2(const UmmaParams& p, const Tables& tb, int t, int rank, Tile& ti) {
+    if (p.wfam) {
+        const int mb2 = (p.mb_count + 1) / 2;
+        int per_e = mb2 * p.nb_count;
+        ti.e = t / per_e;
+        int local = t - ti.e * per_e;
+        int pair;
+        if (mb2 <= p.nb_count) {
+            pair = local % mb2;
+            ti.nb = local / mb2;
+        } else {
+            ti.nb = local % p.nb_count;
+            pair = local / p.nb_count;
+        }
+        ti.mb = 2 * pair + rank;
+        ti.row0 = tb.seg_start[ti.e];
+        ti.rows_valid = tb.seg_cnt[ti.e];
+        ti.ksteps = (ti.rows_valid + BK - 1) / BK;
+    } else {
+        int lo = 0, hi = p.E - 1;
+        while (lo < hi) {
+            int mid = (lo + hi + 1) >> 1;
+            if (tb.tile_prefix[mid] * p.nb_count <= t) {
+                lo = mid;
+            } else {
+                hi = mid - 1;
+            }
+        }
+        ti.e = lo;
+        int pairs_e = tb.tile_prefix[lo + 1] - tb.tile_prefix[lo];
+        int local = t - tb.tile_prefix[lo] * p.nb_count;
+        ti.nb = local / pairs_e;
+        int pair = local - ti.nb * pairs_e;
+        int blk = 2 * pair + rank;
+        ti.mb = blk;
+        ti.row0 = tb.seg_start[lo] + blk * BM;
+        int cover = p.padded ? (tb.seg_cnt[lo] + kPadRows - 1) / kPadRows * kPadRows : tb.seg_cnt[lo];
+        int left = cover - blk * BM;
+        ti.rows_valid = left <= 0 ? 0 : (left < BM ? left : BM);
+        ti.ksteps = (p.K + BK - 1) / BK;
+    }
+}
+
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
+    umma2_grouped_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a,
+                         const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_o,
+                         const __grid_constant__ CUtensorMap tmap_o2, const __grid_constant__ CUtensorMap tmap_o3) {
+    extern __shared__ uint8_t smem_raw[];
+    // identical layout in both CTAs of the pair: the peer's buffers and barriers sit at the same offsets
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + STAGES2 * A_STAGE_BYTES;
+    uint8_t* smem_stg = smem + STAGES2 * (A_STAGE_BYTES + B_HALF_BYTES);
+    uint64_t* bars = (uint64_t*)(smem_stg + EPI_WARPS * STG_BYTES);
+    uint64_t* full_bar = bars;                       // used in the leader only
+    uint64_t* empty_bar = bars + STAGES2;            // one set per CTA
+    uint64_t* tmem_full_bar = bars + 2 * STAGES2;    // one set per CTA
+    uint64_t* tmem_empty_bar = bars + 2 * STAGES2 + 2;  // used in the leader only
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES2 + 4);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    Tables& tb = *(Tables*)(tmem_slot + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int cluster_id = blockIdx.x >> 1, nclusters = gridDim.x >> 1;
+
+    for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
+        int64_t prev = e ? p.offsets[e - 1] : 0;
+        tb.seg_cnt[e] = (int)(p.offsets[e] - prev);
+    }
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < STAGES2; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&tmem_full_bar[a]), 1);
+            mbar_init(smem_u32(&tmem_empty_bar[a]), 2 * EPI_WARPS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int start = 0, tiles = 0;
+        for (int e = 0; e < p.E; ++e) {
+            int cnt = tb.seg_cnt[e];
+            int cover = p.padded ? (cnt + kPadRows - 1) / kPadRows * kPadRows : cnt;
+            tb.seg_start[e] = start;
+            tb.tile_prefix[e] = tiles;
+            start += cover;
+            tiles += ((cover + BM - 1) / BM + 1) / 2;
+        }
+        tb.tile_prefix[p.E] = tiles;
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    cluster_sync_all();  // barriers of both CTAs are initialised and visible before anyone signals the peer
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int ntiles = total_tiles2(p, tb);
+
+    if (warp == 0) {
+        // ---------------- TMA producer (one lane per CTA) ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            Tile ti;
+            bool ok = true;
+            for (int t = cluster_id; t < ntiles && ok; t += nclusters) {
+                decode_tile2(p, tb, t, rank, ti);
+                for (int ks = 0; ks < ti.ksteps; ++ks) {
+                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 211)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t lead_full = map_to_cta(smem_u32(&full_bar[stage]), 0);
+                    if (rank == 0) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * (A_STAGE_BYTES + B_HALF_BYTES));
+                    const uint32_t sa = smem_u32(smem_a + stage * A_STAGE_BYTES);
+                    const uint32_t sb = smem_u32(smem_b + stage * B_HALF_BYTES);
+                    const int k0 = ks * BK;
+                    if (p.wfam) {
+                        int krow = ti.row0 + k0;
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) tma_load_2d_pair(sa + j * 8192, &tmap_a, lead_full, ti.mb * BM + j * 64, krow);
+#pragma unroll
+                        for (int j = 0; j < 2; ++j)
+                            tma_load_2d_pair(sb + j * 8192, &tmap_b, lead_full, ti.nb * BN + (int)rank * 128 + j * 64, krow);
+                    } else {
+                        tma_load_2d_pair(sa, &tmap_a, lead_full, k0, ti.row0);  // box 64 x 128: this CTA's rows
+                        if (p.b_mn) {
+                            int krow = ti.e * p.b_rows_per_expert + k0;
+#pragma unroll
+                            for (int j = 0; j < 2; ++j)
+                                tma_load_2d_pair(sb + j * 8192, &tmap_b, lead_full, ti.nb * BN + (int)rank * 128 + j * 64, krow);
+                        } else {
+                            int r0;
+                            if (EPI == EPI_SWIGLU) {
+                                // leader: 128 "up" rows, peer: the matching 128 "gate" rows
+                                r0 = ti.e * p.b_rows_per_expert + ti.nb * 128 + (int)rank * p.swiglu_half;
+                            } else {
+                                r0 = ti.e * p.b_rows_per_expert + ti.nb * BN + (int)rank * 128;
+                            }
+                            tma_load_2d_pair(sb, &tmap_b, lead_full, k0, r0);  // box 64 x 128
+                        }
+                    }
+                    if (++stage == STAGES2) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (leader CTA only) ----------------
+        if (lane == 0 && rank == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            Tile ti;
+            bool ok = true;
+            const uint32_t a_step = p.a_mn ? 128u : 2u;
+            const uint32_t b_step = p.b_mn ? 128u : 2u;
+            for (int t = cluster_id; t < ntiles && ok; t += nclusters) {
+                decode_tile2(p, tb, t, 0, ti);
+                if (!mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1, abort_flag, p.status, 212)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int ks = 0; ks < ti.ksteps; ++ks) {
+                    if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, 213)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    uint64_t adesc = make_desc(smem_u32(smem_a + stage * A_STAGE_BYTES), p.a_mn);
+                    uint64_t bdesc = make_desc(smem_u32(smem_b + stage * B_HALF_BYTES), p.b_mn);
+#pragma unroll
+                    for (int j = 0; j < BK / 16; ++j) {
+                        tc_mma_pair(d_tmem, adesc + (uint64_t)(j * a_step), bdesc + (uint64_t)(j * b_step), p.idesc,
+                                    (ks | j) ? 1u : 0u);
+                    }
+                    // the stage is free in both CTAs once these MMAs have read it
+                    const uint32_t eb = smem_u32(&empty_bar[stage]);
+                    tc_commit_pair(eb);
+                    tc_commit_pair(map_to_cta(eb, 1));
+                    if (++stage == STAGES2) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (!ok) break;
+                const uint32_t fb = smem_u32(&tmem_full_bar[acc]);
+                tc_commit_pair(fb);
+                tc_commit_pair(map_to_cta(fb, 1));
+                if (++acc == 2) {
+                    acc = 0;
+                    acc_phase ^= 1;
+                }
+            }
+        }
+    } else {
+        // ---------------- epilogue (both CTAs, each on its own 128 rows) ----------------
+        const int q = warp & 3;
+        const int half = (warp - 2) >> 2;
+        const uint32_t stg = smem_u32(smem_stg + (warp - 2) * STG_BYTES);
+        const uint32_t stg_row = stg + lane * 64;
+        const uint32_t stg_swz = (uint32_t)((lane >> 1) & 3);
+        auto stage_store = [&](const CUtensorMap* map, int c0, int c1, int c2, const uint32_t (&pk)[16]) {
+            if (lane == 0) bulk_wait_read0();
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                st_shared_v4(stg_row + ((j ^ stg_swz) << 4), pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                if (p.o3d) {
+                    tma_store_3d(map, stg, c0, c1, c2);
+                } else {
+                    tma_store_2d(map, stg, c0, c1);
+                }
+                bulk_commit();
+            }
+        };
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        Tile ti;
+        for (int t = cluster_id; t < ntiles; t += nclusters) {
+            decode_tile2(p, tb, t, rank, ti);
+            if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status, 215)) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+            // a CTA whose half of the cluster tile does not exist (odd number of row blocks) has nothing to write
+            const bool live = p.wfam || ti.rows_valid > 0;
+            if (live) epilogue_tile<EPI>(p, ti, taddr, q, half, lane, &tmap_o, &tmap_o2, &tmap_o3, stage_store);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));
+            if (++acc == 2) {
+                acc = 0;
+                acc_phase ^= 1;
+            }
+        }
+        if (lane == 0) bulk_wait0();
+    }
+
+    // ---------------- teardown ----------------
+    if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    }
+    __syncwarp();
+    tc_fence_before();
+    cluster_sync_all();  // neither CTA leaves (or frees tensor memory) while the other may still signal it
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
+constexpr int SMEM_BYTES2 =
+    1024 + STAGES2 * (A_STAGE_BYTES + B_HALF_BYTES) + EPI_WARPS * STG_BYTES + 128 + (int)sizeof(Tables) + 64;
+
+template <int EPI>
+int launch2(const UmmaParams& p, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mo2,
+            const CUtensorMap& mo3, cudaStream_t stream) {
+    auto kern = umma2_grouped_kernel<EPI>;
+    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES2);
+    if (err != cudaSuccess) {
+        set_error_detail("cudaFuncSetAttribute(smem=%d): %s", SMEM_BYTES2, cudaGetErrorString(err));
+        return B200MOE_ERR_LAUNCH;
+    }
+    int grid = sm_count() & ~1;  // whole pairs
+    kern<<<grid, NUM_THREADS2, SMEM_BYTES2, stream>>>(p, ma, mb, mo, mo2, mo3);
+    count_launch();
+    return check_launch("umma2_grouped_kernel");
+}
+
+}  // namespace
+
+int launch_2cta(int epi, const UmmaParams& p, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo,
+                const CUtensorMap& mo2, const CUtensorMap& mo3, cudaStream_t stream) {
+    switch (epi) {
+        case EPI_STORE:
+            return launch2<EPI_STORE>(p, ma, mb, mo, mo2, mo3, stream);
+        case EPI_SWIGLU:
+            return launch2<EPI_SWIGLU>(p, ma, mb, mo, mo2, mo3, stream);
+        case EPI_DGRAD_DOWN:
+            return launch2<EPI_DGRAD_DOWN>(p, ma, mb, mo, mo2, mo3, stream);
+        default:
+            set_error_detail("unknown epilogue %d", epi);
+            return B200MOE_ERR_ARG;
+    }
+}
+
+}  // namespace umma
+}  // namespace b200moe

@@ -21,260 +21,116 @@
 // Every wait on an mbarrier is bounded: after about two seconds the waiting thread raises a CTA-wide
 // abort flag, writes a code to the status word and every role leaves its loop; TMEM is freed on the way
 // out.  Nothing here uses cluster multicast.
-#include <cuda.h>
-
 #include <mutex>
 
-#include "common.cuh"
+#include "umma_common.cuh"
 
 namespace b200moe {
 
+namespace umma {
+
+namespace {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+}  // namespace
+
+// Output box of the epilogue: 32 columns x 32 rows (x 1 expert), 64-byte swizzle.  rank 2: [rows][cols] with row
+// stride ld; rank 3: [experts][rows][cols] with expert stride se, so that a tile never spills into the next expert.
+int make_store_map(CUtensorMap* map, const void* base, int64_t experts, int64_t rows, int64_t cols, int64_t ld, int64_t se,
+                   int is_f16) {
+    EncodeTiledFn fn = encode_fn();
+    B200MOE_REQUIRE(fn != nullptr, B200MOE_ERR_DRIVER, "cuTensorMapEncodeTiled not available from the driver");
+    int rank = experts > 0 ? 3 : 2;
+    cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)(experts > 0 ? experts : 1)};
+    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)se * 2};
+    cuuint32_t box[3] = {32u, 32u, 1u};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult rc = fn(map, is_f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, (void*)base, dims,
+                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                     CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    B200MOE_REQUIRE(rc == CUDA_SUCCESS, B200MOE_ERR_DRIVER, "cuTensorMapEncodeTiled (store map) failed with %d", (int)rc);
+    return B200MOE_OK;
+}
+
+// 2-D row-major matrix [rows][cols] with row stride ld (elements), box of 64 columns x box_rows rows.
+int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows, int is_f16) {
+    EncodeTiledFn fn = encode_fn();
+    B200MOE_REQUIRE(fn != nullptr, B200MOE_ERR_DRIVER, "cuTensorMapEncodeTiled not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult rc = fn(map, is_f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims,
+                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    B200MOE_REQUIRE(rc == CUDA_SUCCESS, B200MOE_ERR_DRIVER, "cuTensorMapEncodeTiled failed with %d (rows=%lld cols=%lld ld=%lld)",
+                    (int)rc, (long long)rows, (long long)cols, (long long)ld);
+    return B200MOE_OK;
+}
+
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (!cached[dev]) cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev);
+    return cached[dev] > 0 ? cached[dev] : 148;
+}
+
+
+uint32_t make_idesc(int a_mn, int b_mn, int is_f16, int m) {
+    uint32_t fmt = is_f16 ? 0u : 1u;
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) | ((uint32_t)(BN >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+
+}  // namespace umma
+
+using namespace umma;
+
 namespace {
 
-constexpr int BM = 128, BN = 256, BK = 64;
+bool aligned16(const void* p) { return p != nullptr && ((uintptr_t)p & 15) == 0; }
+
+// The two-CTA kernels take over whenever every operand is a TMA tile, unless the one-CTA engine is forced.
+bool use_pair_kernels(const UmmaParams& p) { return p.a_tma && p.b_tma && current_engine() != B200MOE_ENGINE_UMMA_1CTA; }
+
+template <int EPI>
+int launch(const UmmaParams& p, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mo2,
+           const CUtensorMap& mo3, cudaStream_t stream);
+
+template <int EPI>
+int launch_any(UmmaParams& p, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mo2,
+               const CUtensorMap& mo3, cudaStream_t stream) {
+    if (use_pair_kernels(p)) {
+        p.idesc = make_idesc(p.a_mn, p.b_mn, p.is_f16, 2 * BM);
+        return launch_2cta(EPI, p, ma, mb, mo, mo2, mo3, stream);
+    }
+    return launch<EPI>(p, ma, mb, mo, mo2, mo3, stream);
+}
+
 #ifndef B200MOE_STAGES
 #define B200MOE_STAGES 4
 #endif
 constexpr int STAGES = B200MOE_STAGES;
-constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KB
-constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KB
-constexpr int EPI_WARPS = 8;                        // two warps per TMEM lane quarter, each takes half the columns
+constexpr int B_STAGE_BYTES = BN * BK * 2;          // 32 KB
 constexpr int NUM_THREADS = (6 + EPI_WARPS) * 32;   // 448
 constexpr int GATHER_THREADS = 128;
-constexpr int STG_BYTES = 32 * 32 * 2;  // epilogue staging: 32 rows x 32 columns of 16-bit elements, 64-byte swizzle
-constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
-
-struct UmmaParams {
-    int wfam;    // 0: family R (row tiles), 1: family W (per-expert weight gradient)
-    int E, padded;
-    const int64_t* offsets;
-    int K;          // R: reduction extent
-    int N;          // columns of the output (R: N, W: Nout)
-    int Mout;       // W: rows of the output
-    int nb_count;   // column blocks
-    int mb_count;   // W: row blocks
-    int swiglu_half;  // EPI_SWIGLU: I (columns of one half); tiles cover 128 columns of each half
-    // operand A (R: activations; W: P)
-    int a_tma, a_mn;
-    const void* a_ptr;
-    int64_t a_ld;
-    const int32_t* a_map;
-    // operand B (R: weights; W: Q)
-    int b_tma, b_mn;
-    const void* b_ptr;
-    int64_t b_ld;
-    const int32_t* b_map;
-    int b_rows_per_expert;  // R: rows of the 2-D weight matrix one expert owns
-    // epilogue
-    void* out;
-    int64_t ldo;
-    const int32_t* o_map;
-    const void* scale;
-    void* out2;
-    const void* h;
-    float* d_gates;
-    const int32_t* g_map;
-    int64_t d_se;
-    int32_t* status;
-    uint32_t idesc;
-    int is_f16;
-    int full_count;  // arrivals per full barrier
-    int o3d;         // output tensor map is 3-D (expert, row, column): weight gradients
-};
-
-// ---- PTX wrappers --------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok;
-}
-
-// Bounded wait.  Returns false when the CTA is aborting (this thread or another one gave up).
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
-                                            int code) {
-    long long t0 = clock64();
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 32; ++i)
-            if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-            *abort_flag = 1;
-            if (status) atomicCAS(status, 0, code);
-            return false;
-        }
-    }
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
-                                          int code) {
-    if (mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, abort_flag, status, code);
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(c0), "r"(c1)
-        : "memory");
-}
-
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-// Arrives on the barrier once every cp.async this thread issued before has landed; the arrival is one
-// of the barrier's expected arrivals (noinc), so the issuing thread never waits for its own copies.
-__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
-    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"((uint64_t)map), "r"(src),
-                 "r"(c0), "r"(c1)
-                 : "memory");
-}
-__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
-    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"((uint64_t)map),
-                 "r"(src), "r"(c0), "r"(c1), "r"(c2)
-                 : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
-// 1 / (1 + exp(-x)) with the fast exponential and division; exp overflow gives 1 / inf = 0, never NaN
-__device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                       uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
-        : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor, 128-byte swizzle, version 1 (sm_100).
-// K-major: 8-row groups 1024 B apart (SBO); LBO unused.  MN-major: 8-k groups 1024 B apart (SBO), 64-wide
-// blocks along M/N 8192 B apart (LBO).
-__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, int mn_major) {
-    uint32_t lo = ((smem_addr >> 4) & 0x3FFFu) | ((mn_major ? (8192u >> 4) : 1u) << 16);
-    uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
-    return ((uint64_t)hi << 32) | lo;
-}
-
-// ---- element helpers (bf16 / fp16 chosen at run time, uniform per launch) --------------------------
-__device__ __forceinline__ uint32_t pack2(float a, float b, int is_f16) {
-    if (is_f16) {
-        __half2 v = __floats2half2_rn(a, b);
-        return *reinterpret_cast<uint32_t*>(&v);
-    }
-    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
-__device__ __forceinline__ float2 unpack2(uint32_t u, int is_f16) {
-    if (is_f16) return __half22float2(*reinterpret_cast<__half2*>(&u));
-    return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u));
-}
-__device__ __forceinline__ float load_scalar(const void* p, int64_t i, int is_f16) {
-    if (is_f16) return __half2float(((const __half*)p)[i]);
-    return __bfloat162float(((const __nv_bfloat16*)p)[i]);
-}
-__device__ __forceinline__ float round_elem(float v, int is_f16) {
-    if (is_f16) return __half2float(__float2half_rn(v));
-    return __bfloat162float(__float2bfloat16_rn(v));
-}
-
-// ---- tile bookkeeping ----------------------------------------------------------------------------
-struct Tables {
-    int seg_start[kMaxExperts];    // first layout row of the expert's segment
-    int seg_cnt[kMaxExperts];      // rows the expert really has
-    int tile_prefix[kMaxExperts + 1];  // R: row tiles before the expert
-};
-
-struct Tile {
-    int e, row0, rows_valid, nb, mb, ksteps;
-};
-
-__device__ __forceinline__ int total_tiles(const UmmaParams& p, const Tables& tb) {
-    return p.wfam ? p.E * p.mb_count * p.nb_count : tb.tile_prefix[p.E] * p.nb_count;
-}
-
-__device__ __forceinline__ void decode_tile(const UmmaParams& p, const Tables& tb, int t, Tile& ti) {
-    if (p.wfam) {
-        int per_e = p.mb_count * p.nb_count;
-        ti.e = t / per_e;
-        int local = t - ti.e * per_e;
-        if (p.mb_count <= p.nb_count) {  // walk the shorter side fastest: its operand panel stays L2-resident
-            ti.mb = local % p.mb_count;
-            ti.nb = local / p.mb_count;
-        } else {
-            ti.nb = local % p.nb_count;
-            ti.mb = local / p.nb_count;
-        }
-        ti.row0 = tb.seg_start[ti.e];
-        ti.rows_valid = tb.seg_cnt[ti.e];
-        ti.ksteps = (ti.rows_valid + BK - 1) / BK;
-    } else {
-        int lo = 0, hi = p.E - 1;  // last e with tile_prefix[e] * nb <= t
-        while (lo < hi) {
-            int mid = (lo + hi + 1) >> 1;
-            if (tb.tile_prefix[mid] * p.nb_count <= t) {
-                lo = mid;
-            } else {
-                hi = mid - 1;
-            }
-        }
-        ti.e = lo;
-        int mt_e = tb.tile_prefix[lo + 1] - tb.tile_prefix[lo];
-        int local = t - tb.tile_prefix[lo] * p.nb_count;
-        ti.nb = local / mt_e;  // all row tiles of one column block first: the weight panel is shared
-        int mt = local - ti.nb * mt_e;
-        ti.mb = mt;
-        ti.row0 = tb.seg_start[lo] + mt * BM;
-        int cover = p.padded ? (tb.seg_cnt[lo] + kPadRows - 1) / kPadRows * kPadRows : tb.seg_cnt[lo];
-        ti.rows_valid = min(BM, cover - mt * BM);
-        ti.ksteps = (p.K + BK - 1) / BK;
-    }
-}
 
 // ---- the kernel ----------------------------------------------------------------------------------
 template <int EPI>
@@ -570,9 +426,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     } else {
         // ---------------- epilogue ----------------
         const int q = warp & 3;               // TMEM lane quarter this warp may read
-        const int r = q * 32 + lane;          // row of the tile this thread owns
         const int half = (warp - 6) >> 2;     // which half of the tile's columns this warp handles
-        const int is_f16 = p.is_f16;
         // Outputs that are whole rows of a row-major matrix leave through shared memory: the warp writes its
         // 32 x 32 box (64-byte rows, 64-byte swizzle, conflict-free) and one lane hands it to TMA, which
         // stores full sectors.  The box is reused for every output, so the lane first waits until the
@@ -605,135 +459,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status, 205)) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
-            const bool have_acc = ti.ksteps > 0;
-
-            if (EPI == EPI_STORE) {
-                const int n0 = ti.nb * BN;
-                // whole-row output (weight gradients; grouped rows when this warp's 32 rows are all real)
-                const bool via_tma = p.wfam || (p.o_map == nullptr && p.scale == nullptr && q * 32 + 32 <= ti.rows_valid);
-                if (via_tma) {
-                    const int row_c = p.wfam ? ti.mb * BM + q * 32 : ti.row0 + q * 32;
-#pragma unroll 1
-                    for (int c = half * (BN / 2); c < (half + 1) * (BN / 2); c += 32) {
-                        if (n0 + c >= p.N) break;
-                        uint32_t v[32], pk[16];
-                        if (have_acc) {
-                            tc_ld32(taddr + c, v);
-                            tc_wait_ld();
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) v[i] = 0u;
-                        }
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) pk[i] = pack2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]), is_f16);
-                        stage_store(&tmap_o, n0 + c, row_c, ti.e, pk);
-                    }
-                } else {
-                    bool row_ok = r < ti.rows_valid;
-                    int d = -1;
-                    if (row_ok) d = p.o_map ? p.o_map[ti.row0 + r] : ti.row0 + r;
-                    row_ok = d >= 0;
-                    const int64_t dst = d;
-                    float sc = 1.f;
-                    if (row_ok && p.scale) sc = load_scalar(p.scale, dst, is_f16);
-                    uint8_t* orow = (uint8_t*)p.out + (dst * p.ldo + n0) * 2;
-#pragma unroll 1
-                    for (int c = half * (BN / 2); c < (half + 1) * (BN / 2); c += 32) {
-                        uint32_t v[32];
-                        if (have_acc) {
-                            tc_ld32(taddr + c, v);
-                            tc_wait_ld();
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) v[i] = 0u;
-                        }
-                        if (row_ok) {
-#pragma unroll
-                            for (int qd = 0; qd < 4; ++qd) {
-                                if (n0 + c + qd * 8 < p.N) {
-                                    uint4 o;
-                                    o.x = pack2(__uint_as_float(v[qd * 8 + 0]) * sc, __uint_as_float(v[qd * 8 + 1]) * sc, is_f16);
-                                    o.y = pack2(__uint_as_float(v[qd * 8 + 2]) * sc, __uint_as_float(v[qd * 8 + 3]) * sc, is_f16);
-                                    o.z = pack2(__uint_as_float(v[qd * 8 + 4]) * sc, __uint_as_float(v[qd * 8 + 5]) * sc, is_f16);
-                                    o.w = pack2(__uint_as_float(v[qd * 8 + 6]) * sc, __uint_as_float(v[qd * 8 + 7]) * sc, is_f16);
-                                    *reinterpret_cast<uint4*>(orow + (c + qd * 8) * 2) = o;
-                                }
-                            }
-                        }
-                    }
-                }
-            } else if (EPI == EPI_SWIGLU) {
-                // accumulator columns [0,128) = up, [128,256) = gate, for output columns nb*128 .. +128 of each half;
-                // the layout is the padded grouped order, so all 128 rows of the tile are written (fillers get zeros)
-                const int I = p.swiglu_half;
-                const int n0 = ti.nb * 128;
-                const int row_c = ti.row0 + q * 32;
-#pragma unroll 1
-                for (int c = half * 64; c < (half + 1) * 64; c += 32) {
-                    if (n0 + c >= I) break;
-                    uint32_t u[32], gt[32], hu[16], hg[16], av[16];
-                    tc_ld32(taddr + c, u);
-                    tc_ld32(taddr + 128 + c, gt);
-                    tc_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        hu[i] = pack2(__uint_as_float(u[2 * i]), __uint_as_float(u[2 * i + 1]), is_f16);
-                        hg[i] = pack2(__uint_as_float(gt[2 * i]), __uint_as_float(gt[2 * i + 1]), is_f16);
-                        // the activation sees the values as stored (rounded to the tensor type)
-                        float2 fu = unpack2(hu[i], is_f16), fg = unpack2(hg[i], is_f16);
-                        av[i] = pack2(fu.x * fg.x * sigmoid_fast(fg.x), fu.y * fg.y * sigmoid_fast(fg.y), is_f16);
-                    }
-                    stage_store(&tmap_o, n0 + c, row_c, 0, hu);    // up half of h
-                    stage_store(&tmap_o3, n0 + c, row_c, 0, hg);   // gate half of h (its own map: columns clip at I)
-                    stage_store(&tmap_o2, n0 + c, row_c, 0, av);   // activation
-                }
-            } else {  // EPI_DGRAD_DOWN
-                const int I = p.N;
-                const int64_t prow = ti.row0 + r;
-                const int n0 = ti.nb * BN;
-                const int row_c = ti.row0 + q * 32;
-                const int slot = p.g_map[prow];
-                float g = 0.f;
-                if (slot >= 0) g = p.scale ? load_scalar(p.scale, slot, is_f16) : 1.f;
-                const uint8_t* hrow = (const uint8_t*)p.h + (prow * 2 * (int64_t)I + n0) * 2;
-                float dot = 0.f;
-#pragma unroll 1
-                for (int c = half * (BN / 2); c < (half + 1) * (BN / 2); c += 32) {
-                    if (n0 + c >= I) break;
-                    // the pre-activation values of this row: requested before the accumulator is read
-                    uint4 hu4[4], hg4[4];
-#pragma unroll
-                    for (int qd = 0; qd < 4; ++qd) {
-                        bool in = n0 + c + qd * 8 < I;
-                        hu4[qd] = in ? *reinterpret_cast<const uint4*>(hrow + (c + qd * 8) * 2) : make_uint4(0, 0, 0, 0);
-                        hg4[qd] = in ? *reinterpret_cast<const uint4*>(hrow + ((int64_t)I + c + qd * 8) * 2) : make_uint4(0, 0, 0, 0);
-                    }
-                    uint32_t u[32], du[16], dg[16], ag[16];
-                    tc_ld32(taddr + c, u);
-                    tc_wait_ld();
-#pragma unroll
-                    for (int qd = 0; qd < 4; ++qd) {
-                        const uint32_t hua[4] = {hu4[qd].x, hu4[qd].y, hu4[qd].z, hu4[qd].w};
-                        const uint32_t hga[4] = {hg4[qd].x, hg4[qd].y, hg4[qd].z, hg4[qd].w};
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            float2 up = unpack2(hua[i], is_f16), gt = unpack2(hga[i], is_f16);
-                            float u0 = __uint_as_float(u[qd * 8 + 2 * i]), u1 = __uint_as_float(u[qd * 8 + 2 * i + 1]);
-                            float s0 = sigmoid_fast(gt.x), s1 = sigmoid_fast(gt.y);
-                            float a0 = round_elem(up.x * gt.x * s0, is_f16), a1 = round_elem(up.y * gt.y * s1, is_f16);
-                            dot += a0 * u0 + a1 * u1;
-                            float d0 = round_elem(g * u0, is_f16), d1 = round_elem(g * u1, is_f16);
-                            du[qd * 4 + i] = pack2(d0 * gt.x * s0, d1 * gt.y * s1, is_f16);
-                            dg[qd * 4 + i] = pack2(d0 * up.x * (s0 + gt.x * s0 * (1.f - s0)), d1 * up.y * (s1 + gt.y * s1 * (1.f - s1)), is_f16);
-                            ag[qd * 4 + i] = pack2(g * a0, g * a1, is_f16);
-                        }
-                    }
-                    stage_store(&tmap_o, n0 + c, row_c, 0, du);    // up half of dh
-                    stage_store(&tmap_o3, n0 + c, row_c, 0, dg);   // gate half of dh
-                    stage_store(&tmap_o2, n0 + c, row_c, 0, ag);   // gate-scaled activation
-                }
-                if (slot >= 0) atomicAdd(p.d_gates + slot, dot);
-            }
+            epilogue_tile<EPI>(p, ti, taddr, q, half, lane, &tmap_o, &tmap_o2, &tmap_o3, stage_store);
             tc_fence_before();
             mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
             if (++acc == 2) {
@@ -749,6 +475,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         // give copies still in flight time to land before shared memory is released
         for (int i = 0; i < 64; ++i) __nanosleep(2000);
     }
+    __syncwarp();
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -758,75 +485,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 }
 
 constexpr int SMEM_BYTES = 1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + EPI_WARPS * STG_BYTES + 128 + (int)sizeof(Tables) + 64;
-
-// ---- host side -----------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    });
-    return fn;
-}
-
-// Output box of the epilogue: 32 columns x 32 rows (x 1 expert), 64-byte swizzle.  rank 2: [rows][cols] with row
-// stride ld; rank 3: [experts][rows][cols] with expert stride se, so that a tile never spills into the next expert.
-int make_store_map(CUtensorMap* map, const void* base, int64_t experts, int64_t rows, int64_t cols, int64_t ld, int64_t se,
-                   int is_f16) {
-    EncodeTiledFn fn = encode_fn();
-    B200MOE_REQUIRE(fn != nullptr, B200MOE_ERR_DRIVER, "cuTensorMapEncodeTiled not available from the driver");
-    int rank = experts > 0 ? 3 : 2;
-    cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)(experts > 0 ? experts : 1)};
-    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)se * 2};
-    cuuint32_t box[3] = {32u, 32u, 1u};
-    cuuint32_t estr[3] = {1u, 1u, 1u};
-    CUresult rc = fn(map, is_f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, (void*)base, dims,
-                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
-                     CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    B200MOE_REQUIRE(rc == CUDA_SUCCESS, B200MOE_ERR_DRIVER, "cuTensorMapEncodeTiled (store map) failed with %d", (int)rc);
-    return B200MOE_OK;
-}
-
-// 2-D row-major matrix [rows][cols] with row stride ld (elements), box of 64 columns x box_rows rows.
-int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows, int is_f16) {
-    EncodeTiledFn fn = encode_fn();
-    B200MOE_REQUIRE(fn != nullptr, B200MOE_ERR_DRIVER, "cuTensorMapEncodeTiled not available from the driver");
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1u, 1u};
-    CUresult rc = fn(map, is_f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims,
-                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    B200MOE_REQUIRE(rc == CUDA_SUCCESS, B200MOE_ERR_DRIVER, "cuTensorMapEncodeTiled failed with %d (rows=%lld cols=%lld ld=%lld)",
-                    (int)rc, (long long)rows, (long long)cols, (long long)ld);
-    return B200MOE_OK;
-}
-
-int sm_count() {
-    static int cached[64] = {0};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64) dev = 0;
-    if (!cached[dev]) cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev);
-    return cached[dev] > 0 ? cached[dev] : 148;
-}
-
-bool aligned16(const void* p) { return p != nullptr && ((uintptr_t)p & 15) == 0; }
-
-uint32_t make_idesc(int a_mn, int b_mn, int is_f16) {
-    uint32_t fmt = is_f16 ? 0u : 1u;
-    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) | ((uint32_t)(BN >> 3) << 17) |
-           ((uint32_t)(BM >> 4) << 24);
-}
 
 template <int EPI>
 int launch(const UmmaParams& p, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mo2,
@@ -895,7 +553,7 @@ int umma_row_gemm(const RowGemm& g, int dtype, int32_t* status, cudaStream_t str
     p.d_gates = g.d_gates;
     p.g_map = g.g_map;
     p.status = status;
-    p.idesc = make_idesc(0, p.b_mn, p.is_f16);
+    p.idesc = make_idesc(0, p.b_mn, p.is_f16, BM);
     p.full_count = 1 + (p.a_tma ? 0 : GATHER_THREADS);
 
     CUtensorMap ma{}, mb{};
@@ -928,7 +586,7 @@ int umma_row_gemm(const RowGemm& g, int dtype, int32_t* status, cudaStream_t str
         if (rc) return rc;
         rc = make_store_map(&mo2, g.out2, 0, g.rows_cap, g.N / 2, g.N / 2, 0, p.is_f16);
         if (rc) return rc;
-        return launch<EPI_SWIGLU>(p, ma, mb, mo, mo2, mo3, stream);
+        return launch_any<EPI_SWIGLU>(p, ma, mb, mo, mo2, mo3, stream);
     }
     p.N = g.N;
     p.nb_count = (g.N + BN - 1) / BN;
@@ -940,13 +598,13 @@ int umma_row_gemm(const RowGemm& g, int dtype, int32_t* status, cudaStream_t str
         if (rc) return rc;
         rc = make_store_map(&mo2, g.out2, 0, g.rows_cap, g.N, g.N, 0, p.is_f16);
         if (rc) return rc;
-        return launch<EPI_DGRAD_DOWN>(p, ma, mb, mo, mo2, mo3, stream);
+        return launch_any<EPI_DGRAD_DOWN>(p, ma, mb, mo, mo2, mo3, stream);
     }
     if (g.o_map == nullptr && g.scale == nullptr) {
         rc = make_store_map(&mo, g.out, 0, g.rows_cap, g.N, g.ldo, 0, p.is_f16);
         if (rc) return rc;
     }
-    return launch<EPI_STORE>(p, ma, mb, mo, mo2, mo3, stream);
+    return launch_any<EPI_STORE>(p, ma, mb, mo, mo2, mo3, stream);
 }
 
 int umma_w_gemm(const WGemm& g, int dtype, int32_t* status, cudaStream_t stream) {
@@ -977,7 +635,7 @@ int umma_w_gemm(const WGemm& g, int dtype, int32_t* status, cudaStream_t stream)
     p.ldo = g.d_sm;
     p.d_se = g.d_se;
     p.status = status;
-    p.idesc = make_idesc(1, 1, p.is_f16);
+    p.idesc = make_idesc(1, 1, p.is_f16, BM);
     p.full_count = ((p.a_tma || p.b_tma) ? 1 : 0) + ((!p.a_tma || !p.b_tma) ? GATHER_THREADS : 0);
 
     CUtensorMap ma{}, mb{};
@@ -999,7 +657,7 @@ int umma_w_gemm(const WGemm& g, int dtype, int32_t* status, cudaStream_t stream)
     p.o3d = 1;
     rc = make_store_map(&mo, g.DW, g.E, g.Mout, g.Nout, g.d_sm, g.d_se, p.is_f16);
     if (rc) return rc;
-    return launch<EPI_STORE>(p, ma, mb, mo, mo, mo, stream);
+    return launch_any<EPI_STORE>(p, ma, mb, mo, mo, mo, stream);
 }
 
 }  // namespace b200moe

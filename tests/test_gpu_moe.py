@@ -54,10 +54,10 @@ def check(got, ref, tol, what):
 
 
 @pytest.mark.parametrize("name", list(SMALL))
-@pytest.mark.parametrize("engine,dtype", [("simt", torch.float32), ("simt", torch.bfloat16), ("umma", torch.bfloat16), ("umma", torch.float16)])
+@pytest.mark.parametrize("engine,dtype", [("simt", torch.float32), ("simt", torch.bfloat16), ("umma", torch.bfloat16), ("umma", torch.float16), ("umma1", torch.bfloat16)])
 def test_fused_experts_match_oracle(name, engine, dtype):
     w = SMALL[name]
-    _lib.set_engine(_lib.ENGINE_SIMT if engine == "simt" else _lib.ENGINE_UMMA)
+    _lib.set_engine({"simt": _lib.ENGINE_SIMT, "umma": _lib.ENGINE_UMMA, "umma1": _lib.ENGINE_UMMA_1CTA}[engine])
     case = make_case(w, seed=1, dtype=dtype)
     ref = oracle_experts(case)
     got = run_fused(to_dev(case, dtype))

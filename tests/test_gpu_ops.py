@@ -16,7 +16,7 @@ from helpers import rel_l2, tolerance
 
 pytestmark = pytest.mark.gpu
 
-ENGINES = [("simt", torch.float32), ("simt", torch.bfloat16), ("umma", torch.bfloat16), ("umma", torch.float16)]
+ENGINES = [("simt", torch.float32), ("simt", torch.bfloat16), ("umma", torch.bfloat16), ("umma", torch.float16), ("umma1", torch.bfloat16)]
 
 
 @pytest.fixture(autouse=True)
@@ -27,7 +27,7 @@ def _engine_reset():
 
 
 def use_engine(name):
-    _lib.set_engine({"simt": _lib.ENGINE_SIMT, "umma": _lib.ENGINE_UMMA, "auto": _lib.ENGINE_AUTO}[name])
+    _lib.set_engine({"simt": _lib.ENGINE_SIMT, "umma": _lib.ENGINE_UMMA, "umma1": _lib.ENGINE_UMMA_1CTA, "auto": _lib.ENGINE_AUTO}[name])
 
 
 def routed(E, k, T, seed, empty_from=None):
