@@ -187,7 +187,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
             for (int t = cluster_id; t < ntiles && ok; t += nclusters) {
                 decode_tile2(p, tb, t, rank, ti);
                 for (int ks = 0; ks < ti.ksteps; ++ks) {
-                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 211)) {
+                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 211, 40)) {
                         ok = false;
                         break;
                     }
@@ -305,7 +305,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
         Tile ti;
         for (int t = cluster_id; t < ntiles; t += nclusters) {
             decode_tile2(p, tb, t, rank, ti);
-            if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status, 215)) break;
+            if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status, 215, 200)) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
             // a CTA whose half of the cluster tile does not exist (odd number of row blocks) has nothing to write

@@ -78,13 +78,18 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 }
 
 // Bounded wait.  Returns false when the CTA is aborting (this thread or another one gave up).
+// `sleep_ns` > 0 puts the thread to sleep between polls: used where the wait is long and a wake-up delay of
+// that order does not matter (epilogue warps waiting for a whole tile, producers that run stages ahead), so
+// that idle warps do not spend issue slots and power on polling.
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
-                                            int code) {
+                                                   int code, unsigned sleep_ns) {
     long long t0 = clock64();
     for (;;) {
 #pragma unroll 1
-        for (int i = 0; i < 32; ++i)
+        for (int i = 0; i < 32; ++i) {
             if (mbar_try_wait(bar, parity)) return true;
+            if (sleep_ns) __nanosleep(sleep_ns);
+        }
         if (*abort_flag) return false;
         if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
             *abort_flag = 1;
@@ -94,9 +99,9 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
     }
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
-                                          int code) {
+                                          int code, unsigned sleep_ns = 0) {
     if (mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, abort_flag, status, code);
+    return mbar_wait_slow(bar, parity, abort_flag, status, code, sleep_ns);
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {

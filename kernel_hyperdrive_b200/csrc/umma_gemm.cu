@@ -206,7 +206,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
                 decode_tile(p, tb, t, ti);
                 for (int ks = 0; ks < ti.ksteps; ++ks) {
-                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 201)) {
+                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 201, 40)) {
                         ok = false;
                         break;
                     }
@@ -331,7 +331,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     for (int i = 0; i < 8; ++i) src_r[i] = src_n[i];
                     load_rows(t + gridDim.x, src_n);
                     for (int ks = 0; ks < ti.ksteps; ++ks) {
-                        if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 204)) {
+                        if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 204, 40)) {
                             ok = false;
                             break;
                         }
@@ -380,7 +380,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                             cur_b[i] = nxt_b[i];
                         }
                         if (ks + 1 < ti.ksteps) load_idx(ti, ks + 1, nxt_a, nxt_b);
-                        if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 204)) {
+                        if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 204, 40)) {
                             ok = false;
                             break;
                         }
@@ -456,7 +456,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         Tile ti;
         for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
             decode_tile(p, tb, t, ti);
-            if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status, 205)) break;
+            if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status, 205, 200)) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
             epilogue_tile<EPI>(p, ti, taddr, q, half, lane, &tmap_o, &tmap_o2, &tmap_o3, stage_store);

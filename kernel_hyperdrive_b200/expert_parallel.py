@@ -43,11 +43,12 @@ class CudaRowOps:
         return ss, counts
 
     @staticmethod
-    def gather(x: torch.Tensor, idx: torch.Tensor, fan_out: int) -> torch.Tensor:
+    def gather(x: torch.Tensor, idx: torch.Tensor, fan_out: int, coeff: torch.Tensor | None = None) -> torch.Tensor:
+        """out[n, :] = x[idx[n] // fan_out, :] * coeff[idx[n]] (coeff optional), one pass."""
         from .ops import group
 
         out = torch.empty(idx.numel(), x.size(1), dtype=x.dtype, device=x.device)
-        group(x, idx, out, None, fan_out)
+        group(x, idx, out, coeff, fan_out)
         return out
 
     @staticmethod
@@ -112,7 +113,7 @@ class _UnsortCombine(torch.autograd.Function):
         grad = grad.contiguous()
         d_gates = torch.bmm(expanded.view(T, k, -1), grad.unsqueeze(2)).squeeze(-1).to(gates.dtype)
         # gradient of row n (sorted order) = gates[ss[n]] * grad[ss[n] // k]
-        d_rows = ctx.ops.gather(grad, ss, k) * gates.flatten()[ss].unsqueeze(-1)
+        d_rows = ctx.ops.gather(grad, ss, k, gates.reshape(-1).contiguous())
         return d_rows, d_gates, None, None, None
 
 

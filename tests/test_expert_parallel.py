@@ -23,8 +23,9 @@ class TorchRowOps:
         return ss, flat_ids.bincount(minlength=num_experts).int()
 
     @staticmethod
-    def gather(x, idx, fan_out):
-        return x[idx // fan_out]
+    def gather(x, idx, fan_out, coeff=None):
+        out = x[idx // fan_out]
+        return out if coeff is None else out * coeff[idx].unsqueeze(-1)
 
     @staticmethod
     def combine(expanded, gates, k):

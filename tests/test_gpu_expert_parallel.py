@@ -1,0 +1,59 @@
+"""Expert-parallel layer on the GPU with this package's kernels (row gather, combine, routing sort, fused experts).
+One rank over NCCL: every exchange is a self-exchange, so the whole data path (pack, all-to-all calls, local expert
+ids, un-sort, gate-weighted combine, and the backward of each) runs on the device and is compared with the
+single-GPU layer holding the same weights.  Multi-rank exchange logic is covered by the gloo tests on CPU."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+
+import kernel_hyperdrive_b200 as kh
+from kernel_hyperdrive_b200 import _lib
+from kernel_hyperdrive_b200.expert_parallel import MoE_B200_EP
+
+from helpers import rel_l2
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def single_rank_group():
+    if dist.is_initialized():
+        yield dist.group.WORLD
+        return
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(0)
+    dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+    yield dist.group.WORLD
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("dtype,E,k,H,I,T", [(torch.float32, 8, 2, 128, 256, 300), (torch.bfloat16, 8, 2, 512, 1024, 1000), (torch.bfloat16, 16, 4, 256, 384, 777)])
+def test_single_rank_expert_parallel_matches_single_gpu_layer(single_rank_group, dtype, E, k, H, I, T):
+    dev = torch.device("cuda", 0)
+    ep = MoE_B200_EP(E, k, H, I, kh.swiglu_unchunked_torch, True, False, 0.05, group=single_rank_group, device=dev, dtype=dtype, seed=2)
+    ref = kh.MoE_B200(E, k, H, I, kh.swiglu_unchunked_torch, True, False, 0.05).to(dev).to(dtype)
+    ref.load_state_dict(ep.full_state_dict())
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(T, H, generator=g).to(dev, dtype)
+    gy = torch.randn(T, H, generator=g).to(dev, dtype)
+    outs = []
+    for layer in (ref, ep):
+        xr = x.clone().requires_grad_(True)
+        y, logits = layer(xr)
+        y.backward(gy)
+        if layer is ref:
+            grads = (ref.c_fc.weight.grad, ref.c_proj.weight.grad, ref.gate.weight.grad)
+        else:
+            grads = (ep.c_fc_weight.grad, ep.c_proj_weight.grad, ep.gate.weight.grad)
+        outs.append((y.detach(), xr.grad) + grads)
+    _lib.check_status(dev)
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    for a, b, name in zip(outs[1], outs[0], ("y", "dx", "d_w_fc", "d_w_proj", "d_gate")):
+        assert rel_l2(a, b) < (tol if name != "d_gate" else 20 * tol), (name, rel_l2(a, b))
