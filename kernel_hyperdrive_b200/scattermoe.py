@@ -351,25 +351,41 @@ class Experts_Torch(nn.Module):
 
 class MoE_Torch(nn.Module):
     """Eager torch MoE layer: linear router, top-k with softmax over the selected logits, per-expert MLPs,
-    gate-weighted sum.  Used as the on-device reference of the kernels."""
+    gate-weighted sum.  Used as the on-device reference of the kernels.
+
+    The first eight arguments are the reference's.  Two optional extensions follow (the reference has neither):
+    `num_shared_experts` always-on SwiGLU experts whose output is added for every token (parameters
+    `shared_c_fc.weight (S, 2*I_s, H)`, `shared_c_proj.weight (S, H, I_s)`, created only when S > 0), and
+    `router_scoring="sigmoid"`: sigmoid of the top-k logits, normalised to sum one, instead of their softmax.
+    """
 
     experts_cls = Experts_Torch
 
-    def __init__(self, num_experts: int, num_experts_per_tok: int, hidden_size: int, intermediate_size: int, activation_function: Callable, is_glu: bool, add_bias: bool, std: float) -> None:
+    def __init__(self, num_experts: int, num_experts_per_tok: int, hidden_size: int, intermediate_size: int, activation_function: Callable, is_glu: bool, add_bias: bool, std: float,
+                 num_shared_experts: int = 0, shared_intermediate_size: int | None = None, router_scoring: str = "softmax") -> None:
         super().__init__()
+        assert router_scoring in ("softmax", "sigmoid")
         self.num_experts, self.top_k = num_experts, num_experts_per_tok
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
         self.is_glu = is_glu
+        self.router_scoring = router_scoring
+        self.num_shared_experts = num_shared_experts
         self.gate = nn.Linear(in_features=hidden_size, out_features=num_experts, bias=False)
         self.c_fc = self.experts_cls(num_experts, hidden_size, 2 * intermediate_size if is_glu else intermediate_size, add_bias=add_bias, std=std)
         self.act = activation_function
         self.c_proj = self.experts_cls(num_experts, intermediate_size, hidden_size, add_bias=add_bias, std=std)
+        if num_shared_experts > 0:
+            i_s = shared_intermediate_size or intermediate_size
+            self.shared_c_fc = Experts_Torch(num_shared_experts, hidden_size, 2 * i_s, add_bias=False, std=std)
+            self.shared_c_proj = Experts_Torch(num_shared_experts, i_s, hidden_size, add_bias=False, std=std)
 
     def forward(self, hidden_states: torch.Tensor):
         shape = hidden_states.shape
         flat = hidden_states.view(-1, self.hidden_size)
         router_logits, router_weights, selected_experts = self._compute_routing_weights(flat)
         out = self._compute_experts(flat, router_weights, selected_experts)
+        if self.num_shared_experts > 0:
+            out = out + self._compute_shared_experts(flat)
         return out.view(shape), router_logits
 
     def _get_topk(self, x: torch.Tensor):
@@ -378,7 +394,11 @@ class MoE_Torch(nn.Module):
     def _compute_routing_weights(self, hidden_states: torch.Tensor):
         router_logits = self.gate(hidden_states)
         top_vals, selected_experts = self._get_topk(router_logits)
-        router_weights = F.softmax(top_vals.float(), dim=-1).type_as(hidden_states)
+        if self.router_scoring == "sigmoid":
+            scores = torch.sigmoid(top_vals.float())
+            router_weights = (scores / scores.sum(-1, keepdim=True)).type_as(hidden_states)
+        else:
+            router_weights = F.softmax(top_vals.float(), dim=-1).type_as(hidden_states)
         return router_logits, router_weights, selected_experts
 
     def _compute_experts(self, hidden_states: torch.Tensor, router_weights: torch.Tensor, selected_experts: torch.Tensor) -> torch.Tensor:
@@ -392,6 +412,12 @@ class MoE_Torch(nn.Module):
         rows = self.c_proj(rows, frequency, return_list=False)
         rows = rows * router_weights.flatten()[order].unsqueeze(-1)
         return torch.zeros(T, self.hidden_size, dtype=rows.dtype, device=rows.device).index_add(0, token_of_row, rows)
+
+    def _compute_shared_experts(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        out = torch.zeros_like(hidden_states)
+        for s_ in range(self.num_shared_experts):
+            out = out + F.linear(swiglu_unchunked_torch(F.linear(hidden_states, self.shared_c_fc.weight[s_])), self.shared_c_proj.weight[s_])
+        return out
 
 
 class Experts_B200(Experts_Torch):
@@ -424,6 +450,13 @@ class MoE_B200(MoE_Torch):
         h = self.c_fc(hidden_states, self.top_k, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets, grouped_out=True)
         h = self.act(h)
         return self.c_proj(h, 1, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets, grouped_in=True, gates=router_weights)
+
+    def _compute_shared_experts(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        # every token visits every shared expert with weight one: the routed-expert kernels with a trivial routing
+        T, S = hidden_states.shape[0], self.num_shared_experts
+        ones = torch.ones(T, S, dtype=hidden_states.dtype, device=hidden_states.device)
+        ids = torch.arange(S, device=hidden_states.device).expand(T, S)
+        return fused_swiglu_experts(hidden_states, self.shared_c_fc.weight, self.shared_c_proj.weight, ones, ids)
 
 
 # drop-in names of the reference

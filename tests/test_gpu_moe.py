@@ -139,3 +139,55 @@ def test_weight_grads_of_empty_experts_are_zero():
     assert (got["d_w_fc"][5:] == 0).all() and (got["d_w_proj"][5:] == 0).all()
     ref = oracle_experts(case)
     check(got, ref, 1e-2, "empty experts")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_shared_experts_and_sigmoid_scoring(dtype):
+    """Extensions the benchmark configurations ask for on top of the reference layer: always-on shared experts
+    and sigmoid scoring of the selected logits.  Checked against the eager module on the device and against the
+    CPU oracle's restatement of both."""
+    torch.manual_seed(7)
+    E, k, H, I, T, S, I_s = 16, 4, 256, 384, 500, 2, 128
+    kw = dict(num_shared_experts=S, shared_intermediate_size=I_s, router_scoring="sigmoid")
+    ref_m = kh.MoE_Torch(E, k, H, I, kh.swiglu_unchunked_torch, True, False, 0.05, **kw).cuda().to(dtype)
+    our_m = kh.MoE_B200(E, k, H, I, kh.swiglu_unchunked_torch, True, False, 0.05, **kw).cuda().to(dtype)
+    our_m.load_state_dict(ref_m.state_dict())
+    assert "shared_c_fc.weight" in our_m.state_dict() and our_m.shared_c_fc.weight.shape == (S, 2 * I_s, H)
+    x = torch.randn(T, H, device="cuda", dtype=dtype)
+    g = torch.randn_like(x)
+    outs = []
+    for m in (ref_m, our_m):
+        xr = x.clone().requires_grad_(True)
+        y, _ = m(xr)
+        y.backward(g)
+        outs.append((y.detach(), xr.grad, m.c_fc.weight.grad, m.shared_c_fc.weight.grad, m.shared_c_proj.weight.grad, m.gate.weight.grad))
+    tol = 1e-5 if dtype == torch.float32 else 1.5e-2
+    for a, b, what in zip(outs[1], outs[0], ("y", "dx", "d_w_fc", "d_shared_fc", "d_shared_proj", "d_gate")):
+        assert rel_l2(a, b) < (tol if what != "d_gate" else 20 * tol), (what, rel_l2(a, b))
+    # oracle: routed part with sigmoid routing + dense shared experts
+    xf = x.cpu().float()
+    sd = {n: t.detach().cpu().float() for n, t in ref_m.state_dict().items()}
+    logits = xf @ sd["gate.weight"].t()
+    rw, sel = orc.sigmoid_routing(logits, k)
+    _, _, sel_dev = our_m._compute_routing_weights(x)
+    if torch.equal(sel, sel_dev.cpu()):  # a 16-bit gate may order near-ties differently; compare only on equal routing
+        y_ref = orc.experts_torch_style(xf, sd["c_fc.weight"], sd["c_proj.weight"], rw, sel) + orc.shared_experts(xf, sd["shared_c_fc.weight"], sd["shared_c_proj.weight"])
+        assert rel_l2(outs[1][0], y_ref) < (1e-5 if dtype == torch.float32 else 1e-2)
+
+
+@pytest.mark.parametrize("act_name", ["swiglu", "glu"])
+def test_torch_compile_fullgraph(act_name):
+    """The layer traces under torch.compile(fullgraph=True) like the reference's module in its own test
+    (tests/kernels/scattermoe_test.py:92-93): every kernel launch is one opaque custom op in the graph."""
+    act = kh.swiglu_unchunked_torch if act_name == "swiglu" else torch.nn.GLU()
+    torch.manual_seed(0)
+    m = kh.MoE_Triton(8, 2, 256, 512, act, True, False, 0.02).cuda().bfloat16()
+    x = torch.randn(64, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y0, _ = m(x)
+    y0.sum().backward()
+    g0 = x.grad.clone()
+    x.grad = None
+    mc = torch.compile(m, fullgraph=True)
+    y1, _ = mc(x)
+    y1.sum().backward()
+    assert rel_l2(y1, y0) < 1e-3 and rel_l2(x.grad, g0) < 2e-2
