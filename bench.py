@@ -38,9 +38,12 @@ METRIC = "moe_layer_fwd_bwd_tflops"
 UNIT = "TFLOP/s"
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the grouped-GEMM kernel from an ncu capture,
-# keyed by workload; None until a capture of that workload has been summarised under profiles/.
+# dram__bytes_read.sum + dram__bytes_write.sum of the six grouped-GEMM launches of one step from the ncu capture
+# summarised in profiles/umma2_grouped_kernel_c2_4096tokens.md.  That capture holds 4096 of the 16384 tokens; the
+# weight part of the traffic does not grow with the token count, so it cannot be scaled to the full workload and the
+# full-size `traffic` stays null.
 NCU_TRAFFIC_BYTES_PER_STEP = {}
+NCU_TRAFFIC_SMALL_CASE = {"c2": {"tokens": 4096, "bytes": 13.41e9, "algorithmic_bytes": 12.5e9}}
 
 
 def measured_peaks():
@@ -336,9 +339,9 @@ def run_gpu_arm(args, w):
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": 2 * x_host.numel() * x_host.element_size(), "d2h_bytes_per_step": 2 * y_host.numel() * y_host.element_size()},
         "gpu_launches": launches,
         "roofline": {
-            "bound": "tensor", "kernel": "umma_grouped_kernel (6 launches per step)", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+            "bound": "tensor", "kernel": "umma2_grouped_kernel (6 launches per step)", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
             "frac": (achieved / peak) if achieved else None, "peak_kind": f"bf16_tflops_sustained of {peak_kind}",
-            "traffic": NCU_TRAFFIC_BYTES_PER_STEP.get(w.name), "per_launch": per_launch, "gemm_ms_per_step": gemm_total_ms,
+            "traffic": NCU_TRAFFIC_BYTES_PER_STEP.get(w.name), "traffic_small_case": NCU_TRAFFIC_SMALL_CASE.get(w.name), "per_launch": per_launch, "gemm_ms_per_step": gemm_total_ms,
         },
     }
 
