@@ -197,16 +197,20 @@ def run_gpu_arm(args, w):
         dist.init_process_group("nccl", device_id=dev)
     dtype = synthetic.TORCH_DTYPES[w.dtype]
     E, k, H, I, T = w.num_experts, w.top_k, w.hidden, w.intermediate, w.tokens
+    extra = dict(num_shared_experts=w.shared_experts, router_scoring="sigmoid" if w.routing == "sigmoid" else "softmax")
 
     if world > 1:
         from kernel_hyperdrive_b200.expert_parallel import MoE_B200_EP
 
-        layer = MoE_B200_EP(E, k, H, I, kh.swiglu_unchunked_torch, True, False, w.weight_std, group=dist.group.WORLD, device=dev, dtype=dtype, seed=0)
+        layer = MoE_B200_EP(E, k, H, I, kh.swiglu_unchunked_torch, True, False, w.weight_std, group=dist.group.WORLD, device=dev, dtype=dtype, seed=0, **extra)
     else:
         torch.manual_seed(0)
-        with torch.device(dev):
-            layer = kh.MoE_B200(E, k, H, I, kh.swiglu_unchunked_torch, True, False, w.weight_std)
-        layer = layer.to(dtype)
+        torch.set_default_dtype(dtype)  # build the (large) expert tensors directly in the workload's type
+        try:
+            with torch.device(dev):
+                layer = kh.MoE_B200(E, k, H, I, kh.swiglu_unchunked_torch, True, False, w.weight_std, **extra)
+        finally:
+            torch.set_default_dtype(torch.float32)
     params = [p for p in layer.parameters()]
 
     gen = torch.Generator().manual_seed(1000 + rank)
@@ -217,11 +221,28 @@ def run_gpu_arm(args, w):
     x_dev = x_host.to(dev).requires_grad_(True)
     g_dev = g_host.to(dev)
 
+    if w.routing == "gate":
+        def forward(x):
+            return layer(x)[0]
+    else:
+        # routing supplied from outside (logits drawn per token and expert, or Zipf-distributed expert choice):
+        # enters through the layer's `_compute_experts(hidden_states, router_weights, selected_experts)` seam
+        rw_cpu, sel_cpu = synthetic.make_routing(w, x_host.float(), torch.zeros(E, 1), seed=1000 + rank)
+        rw_dev, sel_dev = rw_cpu.to(dev, dtype), sel_cpu.to(dev)
+        counts = torch.bincount(sel_cpu.flatten(), minlength=E)
+        routing_note = {"rows_min": int(counts.min()), "rows_max": int(counts.max()), "rows_mean": float(counts.float().mean()), "empty_experts": int((counts == 0).sum())}
+
+        def forward(x):
+            out = layer._compute_experts(x, rw_dev, sel_dev)
+            if w.shared_experts:
+                out = out + layer._compute_shared_experts(x)
+            return out
+
     def step_resident():
         for p in params:
             p.grad = None
         x_dev.grad = None
-        y, _ = layer(x_dev)
+        y = forward(x_dev)
         y.backward(g_dev)
         return y
 
@@ -257,7 +278,7 @@ def run_gpu_arm(args, w):
             for p in params:
                 p.grad = None
             x = x_slots[slot].detach().requires_grad_(True)
-            y, _ = layer(x)
+            y = forward(x)
             y.backward(g_slots[slot])
             ev_free[slot].record(main)
             ev_done[slot].record(main)
@@ -321,12 +342,13 @@ def run_gpu_arm(args, w):
     peaks, peak_kind = measured_peaks()
     peak = peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"])
 
-    gemm_ms = {n: sum(v) / len(v) for n, v in per_kernel.items()}
+    gemm_ms = {n: sum(v) / args.steps for n, v in per_kernel.items()}  # per step (a name can launch more than once per step)
     gemm_total_ms = sum(gemm_ms.values())
     local_flops = w.flops_fwd_bwd()
     achieved = local_flops / (gemm_total_ms * 1e-3) / 1e12 if gemm_total_ms > 0 else None
     share = {"up_forward": 4, "down_forward": 2, "down_dgrad": 2, "down_wgrad": 2, "up_wgrad": 4, "up_dgrad": 4}
     per_launch = {n: {"ms": ms, "tflops": (share[n] / 18.0) * local_flops / (ms * 1e-3) / 1e12} for n, ms in gemm_ms.items() if n in share}
+    extra_info = {} if w.routing == "gate" else {"routing": routing_note}
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": n_warm,
@@ -337,7 +359,7 @@ def run_gpu_arm(args, w):
         "frac_of_bf16_peak_sustained": value / world / peak,
         "clocks": clock_summary,
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": 2 * x_host.numel() * x_host.element_size(), "d2h_bytes_per_step": 2 * y_host.numel() * y_host.element_size()},
-        "gpu_launches": launches,
+        "gpu_launches": launches, **extra_info,
         "roofline": {
             "bound": "tensor", "kernel": "umma2_grouped_kernel (6 launches per step)", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
             "frac": (achieved / peak) if achieved else None, "peak_kind": f"bf16_tflops_sustained of {peak_kind}",
@@ -345,7 +367,7 @@ def run_gpu_arm(args, w):
         },
     }
 
-    if rank == 0 and world == 1 and not args.no_cpu_baseline and not args.profile:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and not args.profile and w.name in ("c1", "c2"):
         cpu_w = dict(gate=layer.gate.weight.detach().cpu(), w_fc=layer.c_fc.weight.detach().cpu(), w_proj=layer.c_proj.weight.detach().cpu())
         val, sec, sample, threads = cpu_reference_run(w, 1, 1, args.cpu_sample_tokens, weights=cpu_w)
         line["cpu_baseline"] = {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
@@ -370,6 +392,8 @@ def main():
     w = synthetic.WORKLOADS[args.workload]
     if args.tokens:
         w = synthetic.scaled(w, tokens=args.tokens)
+    elif w.name == "c5":
+        w = synthetic.scaled(w, tokens=w.tokens // 8)  # the configuration is stated for 8 GPUs: 131072 tokens over 8 ranks
     if args.impl == "reference":
         run_reference_arm(args, w)
     else:

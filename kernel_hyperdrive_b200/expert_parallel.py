@@ -158,9 +158,11 @@ class MoE_B200_EP(nn.Module):
     """
 
     def __init__(self, num_experts, num_experts_per_tok, hidden_size, intermediate_size, activation_function, is_glu, add_bias, std,
-                 group=None, device=None, dtype=torch.float32, seed: int = 0, ops=CudaRowOps, local_experts_fn=None):
+                 group=None, device=None, dtype=torch.float32, seed: int = 0, ops=CudaRowOps, local_experts_fn=None,
+                 num_shared_experts: int = 0, shared_intermediate_size: int | None = None, router_scoring: str = "softmax"):
         super().__init__()
         assert is_glu, "the expert-parallel layer implements GLU experts"
+        assert router_scoring in ("softmax", "sigmoid")
         self.group = group if group is not None else dist.group.WORLD
         self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
         assert num_experts % self.world == 0, "experts must divide evenly over the ranks"
@@ -170,18 +172,28 @@ class MoE_B200_EP(nn.Module):
         self.ops = ops
         self._local_experts_fn = local_experts_fn
         self.act = activation_function
-        gen = torch.Generator().manual_seed(seed)
-        gate = torch.randn(num_experts, hidden_size, generator=gen) / hidden_size**0.5
+        self.router_scoring = router_scoring
+        self.num_shared_experts = num_shared_experts
+        # every rank draws with the same per-expert seeds on the same kind of device, so shards agree across ranks
+        gen_dev = torch.device(device) if device is not None and torch.device(device).type == "cuda" else torch.device("cpu")
+
+        def draw(shape, seed_, scale):
+            g = torch.Generator(device=gen_dev).manual_seed(seed_)
+            return (torch.randn(*shape, generator=g, device=gen_dev) * scale).to(dtype)
+
         self.gate = nn.Linear(hidden_size, num_experts, bias=False, device=device, dtype=dtype)
-        fc, proj = [], []
-        for e in range(self.rank * self.e_local, (self.rank + 1) * self.e_local):
-            ge = torch.Generator().manual_seed(seed * 100003 + 17 + e)
-            fc.append(torch.randn(2 * intermediate_size, hidden_size, generator=ge) * std)
-            proj.append(torch.randn(hidden_size, intermediate_size, generator=ge) * std)
         with torch.no_grad():
-            self.gate.weight.copy_(gate)
-        self.c_fc_weight = nn.Parameter(torch.stack(fc).to(device=device, dtype=dtype))
-        self.c_proj_weight = nn.Parameter(torch.stack(proj).to(device=device, dtype=dtype))
+            self.gate.weight.copy_(draw((num_experts, hidden_size), seed * 100003 + 1, hidden_size**-0.5))
+        lo = self.rank * self.e_local
+        fc = [draw((2 * intermediate_size, hidden_size), seed * 100003 + 17 + 2 * e, std) for e in range(lo, lo + self.e_local)]
+        proj = [draw((hidden_size, intermediate_size), seed * 100003 + 18 + 2 * e, std) for e in range(lo, lo + self.e_local)]
+        self.c_fc_weight = nn.Parameter(torch.stack(fc).to(device))
+        self.c_proj_weight = nn.Parameter(torch.stack(proj).to(device))
+        del fc, proj
+        if num_shared_experts > 0:  # replicated; they see this rank's tokens only
+            i_s = shared_intermediate_size or intermediate_size
+            self.shared_c_fc_weight = nn.Parameter(torch.stack([draw((2 * i_s, hidden_size), seed * 100003 + 7 + 2 * s_, std) for s_ in range(num_shared_experts)]).to(device))
+            self.shared_c_proj_weight = nn.Parameter(torch.stack([draw((hidden_size, i_s), seed * 100003 + 8 + 2 * s_, std) for s_ in range(num_shared_experts)]).to(device))
 
     def local_experts(self, rows: torch.Tensor, local_ids: torch.Tensor) -> torch.Tensor:
         if self._local_experts_fn is not None:
@@ -196,9 +208,29 @@ class MoE_B200_EP(nn.Module):
         flat = hidden_states.view(-1, self.hidden_size)
         router_logits = self.gate(flat)
         vals, selected = router_logits.max(-1, keepdim=True) if self.top_k == 1 else router_logits.topk(self.top_k, dim=-1)
-        router_weights = F.softmax(vals.float(), dim=-1).type_as(flat)
+        if self.router_scoring == "sigmoid":
+            scores = torch.sigmoid(vals.float())
+            router_weights = (scores / scores.sum(-1, keepdim=True)).type_as(flat)
+        else:
+            router_weights = F.softmax(vals.float(), dim=-1).type_as(flat)
         out = self._compute_experts(flat, router_weights, selected)
+        if self.num_shared_experts > 0:
+            out = out + self._compute_shared_experts(flat)
         return out.view(shape), router_logits
+
+    def _compute_shared_experts(self, hidden_states):
+        from .scattermoe import fused_swiglu_experts
+
+        T, S = hidden_states.shape[0], self.num_shared_experts
+        ones = torch.ones(T, S, dtype=hidden_states.dtype, device=hidden_states.device)
+        ids = torch.arange(S, device=hidden_states.device).expand(T, S)
+        return fused_swiglu_experts(hidden_states, self.shared_c_fc_weight, self.shared_c_proj_weight, ones, ids)
+
+    def allreduce_shared_grads(self) -> None:
+        """Sums the gradients of the replicated shared experts over the ranks."""
+        for p in (getattr(self, "shared_c_fc_weight", None), getattr(self, "shared_c_proj_weight", None)):
+            if p is not None and p.grad is not None:
+                dist.all_reduce(p.grad, group=self.group)
 
     def _compute_experts(self, hidden_states, router_weights, selected_experts):
         return ep_experts(hidden_states, router_weights, selected_experts, self.num_experts, self.local_experts, self.group, self.ops)
