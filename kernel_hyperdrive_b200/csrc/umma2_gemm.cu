@@ -179,52 +179,79 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
 
     if (warp == 0) {
         // ---------------- TMA producer (one lane per CTA) ----------------
+        // A cursor walks the (tile, k step) sequence of this cluster.  (Asking L2 to prefetch the same boxes some
+        // steps ahead was measured and lost a third of the throughput: the TMA unit is busy enough with the loads.)
         if (lane == 0) {
+            struct Box {
+                const CUtensorMap* map;
+                int c0, c1;
+                uint32_t off;  // byte offset inside the stage's A (is_b == 0) or B-half (is_b == 1) buffer
+                int is_b;
+            };
+            struct Cursor {
+                int t, ks;
+                bool valid;
+                Tile ti;
+            };
+            auto settle = [&](Cursor& c) {  // moves to the next tile that has k steps (an empty expert has none)
+                for (;;) {
+                    c.valid = c.t < ntiles;
+                    if (!c.valid) return;
+                    decode_tile2(p, tb, c.t, rank, c.ti);
+                    if (c.ti.ksteps > 0) return;
+                    c.t += nclusters;
+                }
+            };
+            auto advance = [&](Cursor& c) {
+                if (++c.ks >= c.ti.ksteps) {
+                    c.ks = 0;
+                    c.t += nclusters;
+                    settle(c);
+                }
+            };
+            auto boxes_of = [&](const Cursor& c, Box (&bx)[4]) -> int {
+                const Tile& ti = c.ti;
+                const int k0 = c.ks * BK;
+                int n = 0;
+                if (p.wfam) {
+                    int krow = ti.row0 + k0;
+                    for (int j = 0; j < 2; ++j) bx[n++] = Box{&tmap_a, ti.mb * BM + j * 64, krow, (uint32_t)j * 8192u, 0};
+                    for (int j = 0; j < 2; ++j) bx[n++] = Box{&tmap_b, ti.nb * BN + (int)rank * 128 + j * 64, krow, (uint32_t)j * 8192u, 1};
+                } else {
+                    bx[n++] = Box{&tmap_a, k0, ti.row0, 0u, 0};  // box 64 x 128: this CTA's rows
+                    if (p.b_mn) {
+                        int krow = ti.e * p.b_rows_per_expert + k0;
+                        for (int j = 0; j < 2; ++j) bx[n++] = Box{&tmap_b, ti.nb * BN + (int)rank * 128 + j * 64, krow, (uint32_t)j * 8192u, 1};
+                    } else {
+                        int r0;
+                        if (EPI == EPI_SWIGLU) {
+                            // leader: 128 "up" rows, peer: the matching 128 "gate" rows
+                            r0 = ti.e * p.b_rows_per_expert + ti.nb * 128 + (int)rank * p.swiglu_half;
+                        } else {
+                            r0 = ti.e * p.b_rows_per_expert + ti.nb * BN + (int)rank * 128;
+                        }
+                        bx[n++] = Box{&tmap_b, k0, r0, 0u, 1};  // box 64 x 128
+                    }
+                }
+                return n;
+            };
             int stage = 0;
             uint32_t phase = 0;
-            Tile ti;
-            bool ok = true;
-            for (int t = cluster_id; t < ntiles && ok; t += nclusters) {
-                decode_tile2(p, tb, t, rank, ti);
-                for (int ks = 0; ks < ti.ksteps; ++ks) {
-                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 211, 40)) {
-                        ok = false;
-                        break;
-                    }
-                    const uint32_t lead_full = map_to_cta(smem_u32(&full_bar[stage]), 0);
-                    if (rank == 0) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * (A_STAGE_BYTES + B_HALF_BYTES));
-                    const uint32_t sa = smem_u32(smem_a + stage * A_STAGE_BYTES);
-                    const uint32_t sb = smem_u32(smem_b + stage * B_HALF_BYTES);
-                    const int k0 = ks * BK;
-                    if (p.wfam) {
-                        int krow = ti.row0 + k0;
-#pragma unroll
-                        for (int j = 0; j < 2; ++j) tma_load_2d_pair(sa + j * 8192, &tmap_a, lead_full, ti.mb * BM + j * 64, krow);
-#pragma unroll
-                        for (int j = 0; j < 2; ++j)
-                            tma_load_2d_pair(sb + j * 8192, &tmap_b, lead_full, ti.nb * BN + (int)rank * 128 + j * 64, krow);
-                    } else {
-                        tma_load_2d_pair(sa, &tmap_a, lead_full, k0, ti.row0);  // box 64 x 128: this CTA's rows
-                        if (p.b_mn) {
-                            int krow = ti.e * p.b_rows_per_expert + k0;
-#pragma unroll
-                            for (int j = 0; j < 2; ++j)
-                                tma_load_2d_pair(sb + j * 8192, &tmap_b, lead_full, ti.nb * BN + (int)rank * 128 + j * 64, krow);
-                        } else {
-                            int r0;
-                            if (EPI == EPI_SWIGLU) {
-                                // leader: 128 "up" rows, peer: the matching 128 "gate" rows
-                                r0 = ti.e * p.b_rows_per_expert + ti.nb * 128 + (int)rank * p.swiglu_half;
-                            } else {
-                                r0 = ti.e * p.b_rows_per_expert + ti.nb * BN + (int)rank * 128;
-                            }
-                            tma_load_2d_pair(sb, &tmap_b, lead_full, k0, r0);  // box 64 x 128
-                        }
-                    }
-                    if (++stage == STAGES2) {
-                        stage = 0;
-                        phase ^= 1;
-                    }
+            Cursor ld{cluster_id, 0, false, {}};
+            settle(ld);
+            Box bx[4];
+            while (ld.valid) {
+                if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 211, 40)) break;
+                const uint32_t lead_full = map_to_cta(smem_u32(&full_bar[stage]), 0);
+                if (rank == 0) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * (A_STAGE_BYTES + B_HALF_BYTES));
+                const uint32_t sa = smem_u32(smem_a + stage * A_STAGE_BYTES);
+                const uint32_t sb = smem_u32(smem_b + stage * B_HALF_BYTES);
+                int n = boxes_of(ld, bx);
+                for (int i = 0; i < n; ++i) tma_load_2d_pair((bx[i].is_b ? sb : sa) + bx[i].off, bx[i].map, lead_full, bx[i].c0, bx[i].c1);
+                advance(ld);
+                if (++stage == STAGES2) {
+                    stage = 0;
+                    phase ^= 1;
                 }
             }
         }
