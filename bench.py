@@ -167,11 +167,11 @@ def run_reference_arm(args, w):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(w, n_gpus):
+def workload_config(w, n_gpus, exchange="peer-memory kernels over NVLink"):
     return {
         "workload": f"{w.name}: {w.num_experts} experts top-{w.top_k}, hidden {w.hidden}, SwiGLU intermediate {w.intermediate}, {w.tokens} tokens per GPU, {w.dtype}, routing={w.routing}",
         "tokens_per_gpu": w.tokens, "num_experts": w.num_experts, "top_k": w.top_k, "hidden": w.hidden, "intermediate": w.intermediate,
-        "parallelism": "single GPU" if n_gpus == 1 else f"expert parallel ep{n_gpus} (experts sharded, NCCL all-to-all dispatch/combine)",
+        "parallelism": "single GPU" if n_gpus == 1 else f"expert parallel ep{n_gpus} (experts sharded, dispatch/combine: {exchange})",
         "l2": "inputs_exceed_l2 (expert weights and activations are GBs, L2 is 126 MB)",
     }
 
@@ -202,7 +202,8 @@ def run_gpu_arm(args, w):
     if world > 1:
         from kernel_hyperdrive_b200.expert_parallel import MoE_B200_EP
 
-        layer = MoE_B200_EP(E, k, H, I, kh.swiglu_unchunked_torch, True, False, w.weight_std, group=dist.group.WORLD, device=dev, dtype=dtype, seed=0, **extra)
+        layer = MoE_B200_EP(E, k, H, I, kh.swiglu_unchunked_torch, True, False, w.weight_std, group=dist.group.WORLD, device=dev, dtype=dtype, seed=0,
+                            exchange=args.ep_exchange, exchange_rows=(2 * T * k + 127) // 128 * 128, **extra)
     else:
         torch.manual_seed(0)
         torch.set_default_dtype(dtype)  # build the (large) expert tensors directly in the workload's type
@@ -353,7 +354,7 @@ def run_gpu_arm(args, w):
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": n_warm,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
-        "config": workload_config(w, world),
+        "config": workload_config(w, world, "peer-memory kernels over NVLink" if args.ep_exchange == "p2p" else "NCCL all-to-all"),
         "tokens_per_s": T * world / (ms_step * 1e-3),
         "frac_of_bf16_peak_burst": value / world / peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]),
         "frac_of_bf16_peak_sustained": value / world / peak,
@@ -387,6 +388,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=None, help="override tokens per GPU (profiling on a small case)")
     ap.add_argument("--cpu-sample-tokens", type=int, default=256)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ep-exchange", default="p2p", choices=["p2p", "nccl"], help="N > 1: row exchange by this package's kernels over peer memory, or NCCL all-to-all")
     ap.add_argument("--profile", action="store_true", help="profiling run under ncu: exactly --warmup warm-up steps, no end-to-end and CPU legs; its numbers are not benchmark values")
     args = ap.parse_args()
     w = synthetic.WORKLOADS[args.workload]

@@ -235,6 +235,28 @@ int b200moe_up_dgrad(const void* dh, const void* w_fc, const int64_t* expert_off
                      void* dx_expanded, int64_t ldd, int64_t M, int H, int I, int E, int64_t m_cap, int dtype,
                      int32_t* status, b200moe_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * Expert-parallel row exchange over peer memory (no counterpart in the reference, which has no collective).
+ * peer_ptrs is a HOST array of R device pointers: entry d is rank d's exchange buffer (cap_rows x width), mapped
+ * into this process (CUDA IPC / symmetric memory).  start (R+1) and base (R) are device int32 arrays: the rows
+ * of this rank's expert-sorted order bound for rank d are [start[d], start[d+1]) and land in d's buffer from row
+ * base[d] on.  The caller orders the ranks (buffers free before, data complete after) around each call.
+ * ------------------------------------------------------------------------------------------------ */
+
+/* Token dispatch: peer d's buffer row base[d] + n - start[d] = src[idx[n] / fan_out, :] * coeff[idx[n]]
+ * (idx NULL: n itself; coeff NULL: 1) for n in [0, M).  Fuses the dispatch gather (SMT/ops.py:227-233 applied to the
+ * send side) with the transfer.  Rows that would fall outside cap_rows set status word 301 and are skipped. */
+int b200moe_ep_push_rows(const void* src, int64_t lds, const int64_t* idx, int fan_out, const void* coeff,
+                         const void* const* peer_ptrs, const int32_t* start, const int32_t* base, int R, int64_t M,
+                         int width, int64_t cap_rows, int dtype, int32_t* status, b200moe_stream_t stream);
+
+/* Return path: out[t, :] = sum_j gates[t, j] * row(inv[t*k + j]) read straight from the owning peer's buffer, where
+ * row(n) sits at base[d] + n - start[d] of rank d's buffer; expanded (T*k x width, may be NULL) receives the
+ * unweighted rows.  Fuses the transfer with the un-sort and the gate-weighted combine (SMT/ops.py:160-164). */
+int b200moe_ep_pull_combine(const void* const* peer_ptrs, const int64_t* inv, const int32_t* start,
+                            const int32_t* base, int R, const void* gates, void* out, int64_t ldo, void* expanded,
+                            int64_t T, int k, int width, int dtype, b200moe_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -17,7 +17,7 @@ import torch
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libb200moe.so")
-SOURCES = ["api.cu", "routing.cu", "rowops.cu", "simt_gemm.cu", "umma_gemm.cu", "umma2_gemm.cu"]
+SOURCES = ["api.cu", "routing.cu", "rowops.cu", "simt_gemm.cu", "umma_gemm.cu", "umma2_gemm.cu", "ep.cu"]
 HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(PKG_DIR, "..", "include", "b200moe.h")]
 
 F32, BF16, F16 = 0, 1, 2
@@ -85,6 +85,8 @@ def _declare(lib):
         "b200moe_down_forward": (i32, [vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, i64, i32, vp, vp]),
         "b200moe_down_dgrad": (i32, [vp, i64, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i64, i32, vp, vp]),
         "b200moe_wgrad": (i32, [vp, i64, vp, vp, i64, vp, vp, vp, i32, i32, i32, i64, i32, vp, vp]),
+        "b200moe_ep_push_rows": (i32, [vp, i64, vp, i32, vp, vp, vp, vp, i32, i64, i32, i64, i32, vp, vp]),
+        "b200moe_ep_pull_combine": (i32, [vp, vp, vp, vp, i32, vp, vp, i64, vp, i64, i32, i32, i32, vp]),
         "b200moe_up_dgrad": (i32, [vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, i64, i32, vp, vp]),
     }
     for name, (res, args) in sig.items():

@@ -1,0 +1,170 @@
+// Expert-parallel row exchange over peer memory (NVLink / NVSwitch): the token dispatch writes rows straight into
+// the destination rank's receive buffer, the return path reads rows straight from the expert rank's output buffer
+// and folds the gate-weighted sum over the k slots into the same pass.  Plain peer loads and stores of 16 bytes;
+// no multimem, no TMA on peer memory.  Ordering between ranks (buffer free / data complete) is the caller's job
+// (a barrier over the symmetric-memory signal pads before and after each kernel).
+//
+// Row placement.  Rank r sorts its routed rows by global expert, so the rows for destination rank d are the
+// contiguous range [start[d], start[d+1]) of its sorted order, already ordered by d's local expert.  In d's buffer
+// the rows of source rank r follow those of ranks 0..r-1: row n of the sorted order lands at base[d] + n - start[d].
+#include "common.cuh"
+
+namespace b200moe {
+namespace {
+
+constexpr int kMaxRanks = 64;
+
+struct PeerTable {
+    void* ptr[kMaxRanks];
+};
+
+template <typename T, int V>
+struct alignas(sizeof(T) * V) Pack {
+    T v[V];
+};
+
+__device__ __forceinline__ int find_dest(const int32_t* __restrict__ start, int R, int n) {
+    int d = 0;
+    while (d + 1 < R && n >= start[d + 1]) ++d;
+    return d;
+}
+
+template <typename T, int V>
+__global__ void ep_push_kernel(const T* __restrict__ src, int64_t lds, const int64_t* __restrict__ idx, int fan_out,
+                               const T* __restrict__ coeff, PeerTable peers, const int32_t* __restrict__ start,
+                               const int32_t* __restrict__ base, int R, int64_t M, int width, int64_t cap_rows,
+                               int32_t* status) {
+    int64_t n = blockIdx.x;
+    if (n >= M) return;
+    int d = find_dest(start, R, (int)n);
+    int64_t pos = (int64_t)base[d] + (n - start[d]);
+    if (pos < 0 || pos >= cap_rows) {  // would overrun the peer's buffer: record and skip
+        if (threadIdx.x == 0 && status) atomicCAS(status, 0, 301);
+        return;
+    }
+    int64_t s = idx ? idx[n] : n;
+    const T* row = src + (s / fan_out) * lds;
+    T* dst = (T*)peers.ptr[d] + pos * (int64_t)width;
+    float c = coeff ? Elem<T>::to_f(coeff[s]) : 1.f;
+    for (int col = threadIdx.x * V; col < width; col += blockDim.x * V) {
+        Pack<T, V> p = *reinterpret_cast<const Pack<T, V>*>(row + col);
+        if (coeff) {
+#pragma unroll
+            for (int i = 0; i < V; ++i) p.v[i] = Elem<T>::from_f(Elem<T>::to_f(p.v[i]) * c);
+        }
+        *reinterpret_cast<Pack<T, V>*>(dst + col) = p;
+    }
+}
+
+template <typename T, int V>
+__global__ void ep_pull_combine_kernel(PeerTable peers, const int64_t* __restrict__ inv, const int32_t* __restrict__ start,
+                                       const int32_t* __restrict__ base, int R, const T* __restrict__ gates,
+                                       T* __restrict__ out, int64_t ldo, T* __restrict__ expanded, int64_t Tn, int k,
+                                       int width) {
+    int64_t t = blockIdx.x;
+    if (t >= Tn) return;
+    __shared__ const T* rows[64];
+    if (threadIdx.x < k) {
+        int64_t n = inv[t * k + threadIdx.x];
+        int d = find_dest(start, R, (int)n);
+        rows[threadIdx.x] = (const T*)peers.ptr[d] + ((int64_t)base[d] + (n - start[d])) * (int64_t)width;
+    }
+    __syncthreads();
+    for (int col = threadIdx.x * V; col < width; col += blockDim.x * V) {
+        float acc[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = 0.f;
+        for (int j = 0; j < k; ++j) {
+            Pack<T, V> p = *reinterpret_cast<const Pack<T, V>*>(rows[j] + col);
+            float g = gates ? Elem<T>::to_f(gates[t * k + j]) : 1.f;
+#pragma unroll
+            for (int i = 0; i < V; ++i) acc[i] += g * Elem<T>::to_f(p.v[i]);
+            if (expanded) *reinterpret_cast<Pack<T, V>*>(expanded + (t * k + j) * (int64_t)width + col) = p;
+        }
+        Pack<T, V> o;
+#pragma unroll
+        for (int i = 0; i < V; ++i) o.v[i] = Elem<T>::from_f(acc[i]);
+        *reinterpret_cast<Pack<T, V>*>(out + t * ldo + col) = o;
+    }
+}
+
+int fill_peers(PeerTable& tab, const void* const* peer_ptrs, int R, const char* what) {
+    B200MOE_REQUIRE(R >= 1 && R <= kMaxRanks && peer_ptrs, B200MOE_ERR_ARG, "%s: bad rank count or NULL peer table", what);
+    for (int i = 0; i < R; ++i) {
+        B200MOE_REQUIRE(peer_ptrs[i] != nullptr && ((uintptr_t)peer_ptrs[i] & 15) == 0, B200MOE_ERR_ARG,
+                        "%s: peer buffer %d is NULL or not 16-byte aligned", what, i);
+        tab.ptr[i] = const_cast<void*>(peer_ptrs[i]);
+    }
+    return B200MOE_OK;
+}
+
+int row_threads(int width, int vec) {
+    int t = (width / vec + 31) / 32 * 32;
+    return t < 64 ? 64 : (t > 256 ? 256 : t);
+}
+
+}  // namespace
+}  // namespace b200moe
+
+using namespace b200moe;
+
+extern "C" int b200moe_ep_push_rows(const void* src, int64_t lds, const int64_t* idx, int fan_out, const void* coeff,
+                                    const void* const* peer_ptrs, const int32_t* start, const int32_t* base, int R,
+                                    int64_t M, int width, int64_t cap_rows, int dtype, int32_t* status,
+                                    b200moe_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    B200MOE_REQUIRE(M >= 0 && width > 0 && fan_out > 0 && cap_rows >= 0, B200MOE_ERR_ARG, "ep_push_rows: bad sizes");
+    if (M == 0) return B200MOE_OK;
+    B200MOE_REQUIRE(src && start && base, B200MOE_ERR_ARG, "ep_push_rows: NULL pointer");
+    PeerTable tab{};
+    int rc = fill_peers(tab, peer_ptrs, R, "ep_push_rows");
+    if (rc) return rc;
+    B200MOE_REQUIRE(dtype == B200MOE_BF16 || dtype == B200MOE_F16 || dtype == B200MOE_F32, B200MOE_ERR_DTYPE, "ep_push_rows: dtype");
+    int esz = dtype == B200MOE_F32 ? 4 : 2, V = 16 / esz;
+    B200MOE_REQUIRE(width % V == 0 && lds % V == 0 && ((uintptr_t)src & 15) == 0, B200MOE_ERR_LAYOUT,
+                    "ep_push_rows: rows must be 16-byte aligned and a multiple of 16 bytes wide");
+    int threads = row_threads(width, V);
+    if (dtype == B200MOE_F32) {
+        ep_push_kernel<float, 4><<<(unsigned)M, threads, 0, stream>>>((const float*)src, lds, idx, fan_out, (const float*)coeff, tab,
+                                                                   start, base, R, M, width, cap_rows, status);
+    } else if (dtype == B200MOE_BF16) {
+        ep_push_kernel<__nv_bfloat16, 8><<<(unsigned)M, threads, 0, stream>>>((const __nv_bfloat16*)src, lds, idx, fan_out,
+                                                                           (const __nv_bfloat16*)coeff, tab, start, base, R, M,
+                                                                           width, cap_rows, status);
+    } else {
+        ep_push_kernel<__half, 8><<<(unsigned)M, threads, 0, stream>>>((const __half*)src, lds, idx, fan_out, (const __half*)coeff,
+                                                                    tab, start, base, R, M, width, cap_rows, status);
+    }
+    count_launch();
+    return check_launch("ep_push_rows");
+}
+
+extern "C" int b200moe_ep_pull_combine(const void* const* peer_ptrs, const int64_t* inv, const int32_t* start,
+                                       const int32_t* base, int R, const void* gates, void* out, int64_t ldo,
+                                       void* expanded, int64_t T_, int k, int width, int dtype,
+                                       b200moe_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    B200MOE_REQUIRE(T_ >= 0 && width > 0 && k > 0 && k <= 64, B200MOE_ERR_ARG, "ep_pull_combine: bad sizes (k <= 64)");
+    if (T_ == 0) return B200MOE_OK;
+    B200MOE_REQUIRE(inv && start && base && out, B200MOE_ERR_ARG, "ep_pull_combine: NULL pointer");
+    PeerTable tab{};
+    int rc = fill_peers(tab, peer_ptrs, R, "ep_pull_combine");
+    if (rc) return rc;
+    B200MOE_REQUIRE(dtype == B200MOE_BF16 || dtype == B200MOE_F16 || dtype == B200MOE_F32, B200MOE_ERR_DTYPE, "ep_pull_combine: dtype");
+    int esz = dtype == B200MOE_F32 ? 4 : 2, V = 16 / esz;
+    B200MOE_REQUIRE(width % V == 0 && ldo % V == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)expanded & 15) == 0,
+                    B200MOE_ERR_LAYOUT, "ep_pull_combine: rows must be 16-byte aligned and a multiple of 16 bytes wide");
+    int threads = row_threads(width, V);
+    if (dtype == B200MOE_F32) {
+        ep_pull_combine_kernel<float, 4><<<(unsigned)T_, threads, 0, stream>>>(tab, inv, start, base, R, (const float*)gates, (float*)out,
+                                                                            ldo, (float*)expanded, T_, k, width);
+    } else if (dtype == B200MOE_BF16) {
+        ep_pull_combine_kernel<__nv_bfloat16, 8><<<(unsigned)T_, threads, 0, stream>>>(
+            tab, inv, start, base, R, (const __nv_bfloat16*)gates, (__nv_bfloat16*)out, ldo, (__nv_bfloat16*)expanded, T_, k, width);
+    } else {
+        ep_pull_combine_kernel<__half, 8><<<(unsigned)T_, threads, 0, stream>>>(tab, inv, start, base, R, (const __half*)gates,
+                                                                             (__half*)out, ldo, (__half*)expanded, T_, k, width);
+    }
+    count_launch();
+    return check_launch("ep_pull_combine");
+}

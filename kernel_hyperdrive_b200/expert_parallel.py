@@ -150,6 +150,152 @@ def ep_experts(x, router_weights, selected_experts, num_experts: int, local_expe
     return _UnsortCombine.apply(back, router_weights.to(x.dtype), ss, inv, ops)
 
 
+# --------------------------------------------------------------------------------------------------
+# exchange over peer memory: this package's kernels store to / load from the peers' buffers directly
+# --------------------------------------------------------------------------------------------------
+
+
+class PeerExchange:
+    """Four symmetric (cap_rows, H) buffers per rank, mapped into every rank of the group:
+    "x" (dispatched tokens), "y" (expert outputs), "dy" (dispatched output gradients), "dx" (input gradients of the
+    received rows).  `barrier()` orders the ranks on the current stream through the symmetric-memory signal pads."""
+
+    def __init__(self, group, cap_rows: int, width: int, dtype: torch.dtype, device: torch.device):
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm
+
+        self.group, self.cap_rows, self.width = group, cap_rows, width
+        self.world = dist.get_world_size(group)
+        self.bufs, self.peer_ptrs, self._handles = {}, {}, {}
+        for name in ("x", "y", "dy", "dx"):
+            t = symm.empty(cap_rows, width, dtype=dtype, device=device)
+            hdl = symm.rendezvous(t, group)
+            self.bufs[name], self._handles[name] = t, hdl
+            self.peer_ptrs[name] = (ctypes.c_void_p * self.world)(*[int(p) for p in hdl.buffer_ptrs])
+        self._barrier_handle = self._handles["x"]
+
+    def barrier(self) -> None:
+        self._barrier_handle.barrier(channel=0)
+
+
+class _Plan:
+    """Where this rank's sorted rows go: computed once per pass from the all-gathered expert counts."""
+
+    __slots__ = ("ss", "inv", "start", "base", "m_recv", "local_ids", "k")
+
+
+def _make_plan(selected_experts, num_experts: int, world: int, rank: int, group, ops) -> "_Plan":
+    T, k = selected_experts.shape
+    e_local = num_experts // world
+    plan = _Plan()
+    plan.k = k
+    ss, counts = ops.route(selected_experts.reshape(-1), num_experts, k)
+    plan.ss = ss
+    plan.inv = torch.empty_like(ss)
+    plan.inv[ss] = torch.arange(ss.numel(), device=ss.device)
+    counts_all = torch.empty(world, num_experts, dtype=counts.dtype, device=counts.device)
+    dist.all_gather_into_tensor(counts_all, counts.contiguous(), group=group)
+    to_rank = counts_all.view(world, world, e_local).sum(-1)  # [source, destination]
+    zero = torch.zeros(1, dtype=torch.int64, device=ss.device)
+    plan.start = torch.cat([zero, to_rank[rank].cumsum(0)]).to(torch.int32)
+    plan.base = (to_rank.cumsum(0) - to_rank)[rank].to(torch.int32)  # rows of lower-ranked sources in each destination
+    recv_counts = counts_all[:, rank * e_local : (rank + 1) * e_local]
+    plan.m_recv = int(recv_counts.sum().item())  # the one host read of the pass: sizes the local expert tensors
+    plan.local_ids = torch.repeat_interleave(
+        torch.arange(e_local, device=ss.device).repeat(world), recv_counts.reshape(-1).long(), output_size=plan.m_recv
+    )
+    return plan
+
+
+def _push(xc: PeerExchange, name: str, src, idx, fan_out: int, coeff, plan: "_Plan") -> None:
+    from ._lib import check, dtype_code, lib, ptr, status_word, stream_ptr
+
+    M = plan.ss.numel()
+    check(
+        lib().b200moe_ep_push_rows(ptr(src), src.stride(0), ptr(idx), fan_out, ptr(coeff), xc.peer_ptrs[name], ptr(plan.start), ptr(plan.base),
+                                   xc.world, M, src.size(1), xc.cap_rows, dtype_code(src), ptr(status_word(src.device)), stream_ptr(src.device)),
+        "ep_push_rows",
+    )
+
+
+def _pull(xc: PeerExchange, name: str, gates, out, expanded, plan: "_Plan") -> None:
+    from ._lib import check, dtype_code, lib, ptr, stream_ptr
+
+    check(
+        lib().b200moe_ep_pull_combine(xc.peer_ptrs[name], ptr(plan.inv), ptr(plan.start), ptr(plan.base), xc.world, ptr(gates), ptr(out), out.stride(0),
+                                      ptr(expanded), out.size(0), plan.k, out.size(1), dtype_code(out), stream_ptr(out.device)),
+        "ep_pull_combine",
+    )
+
+
+class _PeerDispatch(torch.autograd.Function):
+    """Forward: every rank stores its routed rows into the owners' "x" buffers.  Backward: the owners publish the
+    input gradients of the rows they received in "dx"; the source pulls them and sums the k slots of a token."""
+
+    @staticmethod
+    def forward(ctx, x, xc, plan):
+        ctx.xc, ctx.plan, ctx.shape = xc, plan, x.shape
+        xc.barrier()  # nobody still reads last pass's rows
+        _push(xc, "x", x.contiguous(), plan.ss, plan.k, None, plan)
+        xc.barrier()  # all rows have landed
+        return xc.bufs["x"][: plan.m_recv]
+
+    @staticmethod
+    def backward(ctx, grad_recv):
+        xc, plan = ctx.xc, ctx.plan
+        xc.bufs["dx"][: plan.m_recv].copy_(grad_recv)
+        xc.barrier()
+        dx = torch.empty(ctx.shape, dtype=grad_recv.dtype, device=grad_recv.device)
+        _pull(xc, "dx", None, dx, None, plan)
+        xc.barrier()
+        return dx, None, None
+
+
+class _PeerCombine(torch.autograd.Function):
+    """Forward: the owners publish their output rows in "y"; the source pulls the k rows of each token and forms the
+    gate-weighted sum.  Backward: gate gradients locally, gate-scaled output gradients stored into the owners' "dy"."""
+
+    @staticmethod
+    def forward(ctx, out_rows, gates, xc, plan):
+        T, k = gates.shape
+        xc.bufs["y"][: plan.m_recv].copy_(out_rows)
+        xc.barrier()
+        y = torch.empty(T, out_rows.size(1), dtype=out_rows.dtype, device=out_rows.device)
+        expanded = torch.empty(T * k, out_rows.size(1), dtype=out_rows.dtype, device=out_rows.device)
+        gates = gates.contiguous()
+        _pull(xc, "y", gates, y, expanded, plan)
+        xc.barrier()
+        ctx.save_for_backward(expanded, gates)
+        ctx.xc, ctx.plan = xc, plan
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        expanded, gates = ctx.saved_tensors
+        xc, plan = ctx.xc, ctx.plan
+        T, k = gates.shape
+        grad_y = grad_y.contiguous()
+        d_gates = torch.bmm(expanded.view(T, k, -1), grad_y.unsqueeze(2)).squeeze(-1).to(gates.dtype)
+        xc.barrier()
+        _push(xc, "dy", grad_y, plan.ss, k, gates.reshape(-1), plan)
+        xc.barrier()
+        return xc.bufs["dy"][: plan.m_recv], d_gates, None, None
+
+
+def ep_experts_p2p(x, router_weights, selected_experts, num_experts: int, local_experts_fn: Callable, xc: PeerExchange, ops=CudaRowOps):
+    """Routed experts over an expert-parallel group with the row exchange done by this package's kernels on peer
+    memory (see PeerExchange).  Same contract as `ep_experts`."""
+    world, rank = xc.world, dist.get_rank(xc.group)
+    with torch.no_grad():
+        plan = _make_plan(selected_experts, num_experts, world, rank, xc.group, ops)
+    if plan.m_recv > xc.cap_rows:
+        raise RuntimeError(f"expert-parallel exchange buffer too small: {plan.m_recv} rows arrive, capacity {xc.cap_rows}")
+    recv = _PeerDispatch.apply(x, xc, plan)
+    out_rows = local_experts_fn(recv, plan.local_ids)
+    return _PeerCombine.apply(out_rows, router_weights.to(x.dtype), xc, plan)
+
+
 class MoE_B200_EP(nn.Module):
     """Expert-parallel MoE layer.  The gate is replicated; rank r holds experts [r*E/R, (r+1)*E/R).
 
@@ -159,7 +305,8 @@ class MoE_B200_EP(nn.Module):
 
     def __init__(self, num_experts, num_experts_per_tok, hidden_size, intermediate_size, activation_function, is_glu, add_bias, std,
                  group=None, device=None, dtype=torch.float32, seed: int = 0, ops=CudaRowOps, local_experts_fn=None,
-                 num_shared_experts: int = 0, shared_intermediate_size: int | None = None, router_scoring: str = "softmax"):
+                 num_shared_experts: int = 0, shared_intermediate_size: int | None = None, router_scoring: str = "softmax",
+                 exchange: str = "nccl", exchange_rows: int | None = None):
         super().__init__()
         assert is_glu, "the expert-parallel layer implements GLU experts"
         assert router_scoring in ("softmax", "sigmoid")
@@ -174,6 +321,9 @@ class MoE_B200_EP(nn.Module):
         self.act = activation_function
         self.router_scoring = router_scoring
         self.num_shared_experts = num_shared_experts
+        assert exchange in ("nccl", "p2p")
+        # "p2p": rows move by this package's kernels over peer memory; exchange_rows = capacity of each buffer in rows
+        self.exchange = PeerExchange(self.group, exchange_rows, hidden_size, dtype, torch.device(device)) if exchange == "p2p" else None
         # every rank draws with the same per-expert seeds on the same kind of device, so shards agree across ranks
         gen_dev = torch.device(device) if device is not None and torch.device(device).type == "cuda" else torch.device("cpu")
 
@@ -233,6 +383,8 @@ class MoE_B200_EP(nn.Module):
                 dist.all_reduce(p.grad, group=self.group)
 
     def _compute_experts(self, hidden_states, router_weights, selected_experts):
+        if self.exchange is not None:
+            return ep_experts_p2p(hidden_states, router_weights, selected_experts, self.num_experts, self.local_experts, self.exchange, self.ops)
         return ep_experts(hidden_states, router_weights, selected_experts, self.num_experts, self.local_experts, self.group, self.ops)
 
     def allreduce_replicated_grads(self) -> None:

@@ -1,5 +1,6 @@
 """Expert-parallel layer on the GPU with this package's kernels (row gather, combine, routing sort, fused experts).
-One rank over NCCL: every exchange is a self-exchange, so the whole data path (pack, all-to-all calls, local expert
+One rank over NCCL, with the row exchange done either by NCCL all-to-all or by this package's peer-memory kernels
+(symmetric memory; the peer table then holds the rank's own buffer): every exchange is a self-exchange, so the whole data path (pack, all-to-all calls, local expert
 ids, un-sort, gate-weighted combine, and the backward of each) runs on the device and is compared with the
 single-GPU layer holding the same weights.  Multi-rank exchange logic is covered by the gloo tests on CPU."""
 
@@ -34,10 +35,12 @@ def single_rank_group():
     dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("exchange", ["nccl", "p2p"])
 @pytest.mark.parametrize("dtype,E,k,H,I,T", [(torch.float32, 8, 2, 128, 256, 300), (torch.bfloat16, 8, 2, 512, 1024, 1000), (torch.bfloat16, 16, 4, 256, 384, 777)])
-def test_single_rank_expert_parallel_matches_single_gpu_layer(single_rank_group, dtype, E, k, H, I, T):
+def test_single_rank_expert_parallel_matches_single_gpu_layer(single_rank_group, exchange, dtype, E, k, H, I, T):
     dev = torch.device("cuda", 0)
-    ep = MoE_B200_EP(E, k, H, I, kh.swiglu_unchunked_torch, True, False, 0.05, group=single_rank_group, device=dev, dtype=dtype, seed=2)
+    ep = MoE_B200_EP(E, k, H, I, kh.swiglu_unchunked_torch, True, False, 0.05, group=single_rank_group, device=dev, dtype=dtype, seed=2,
+                     exchange=exchange, exchange_rows=(T * k + 127) // 128 * 128)
     ref = kh.MoE_B200(E, k, H, I, kh.swiglu_unchunked_torch, True, False, 0.05).to(dev).to(dtype)
     ref.load_state_dict(ep.full_state_dict())
     g = torch.Generator().manual_seed(3)
