@@ -203,7 +203,7 @@ def run_gpu_arm(args, w):
         from kernel_hyperdrive_b200.expert_parallel import MoE_B200_EP
 
         layer = MoE_B200_EP(E, k, H, I, kh.swiglu_unchunked_torch, True, False, w.weight_std, group=dist.group.WORLD, device=dev, dtype=dtype, seed=0,
-                            exchange=args.ep_exchange, exchange_rows=(2 * T * k + 127) // 128 * 128, **extra)
+                            exchange=args.ep_exchange, exchange_rows=((world if w.routing == "zipf" else 2) * T * k + 127) // 128 * 128, **extra)
     else:
         torch.manual_seed(0)
         torch.set_default_dtype(dtype)  # build the (large) expert tensors directly in the workload's type

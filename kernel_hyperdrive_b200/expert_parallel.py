@@ -174,6 +174,7 @@ class PeerExchange:
             self.bufs[name], self._handles[name] = t, hdl
             self.peer_ptrs[name] = (ctypes.c_void_p * self.world)(*[int(p) for p in hdl.buffer_ptrs])
         self._barrier_handle = self._handles["x"]
+        self.backward_reads_pending = False
 
     def barrier(self) -> None:
         self._barrier_handle.barrier(channel=0)
@@ -236,7 +237,13 @@ class _PeerDispatch(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, xc, plan):
         ctx.xc, ctx.plan, ctx.shape = xc, plan, x.shape
-        xc.barrier()  # nobody still reads last pass's rows
+        # Normally no barrier before the push: every rank finished reading its "x" rows of the previous pass before
+        # it reached that pass's "y written" barrier (forward reads) and "dx written" barrier (the backward reads them
+        # again for the weight gradient), and this rank has passed both.  If the previous pass may still run a backward
+        # that never reached the "dx written" barrier (its input needed no gradient), order the ranks explicitly.
+        if xc.backward_reads_pending:
+            xc.barrier()
+        xc.backward_reads_pending = torch.is_grad_enabled()
         _push(xc, "x", x.contiguous(), plan.ss, plan.k, None, plan)
         xc.barrier()  # all rows have landed
         return xc.bufs["x"][: plan.m_recv]
@@ -244,11 +251,14 @@ class _PeerDispatch(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_recv):
         xc, plan = ctx.xc, ctx.plan
-        xc.bufs["dx"][: plan.m_recv].copy_(grad_recv)
-        xc.barrier()
+        buf = xc.bufs["dx"][: plan.m_recv]
+        if grad_recv.data_ptr() != buf.data_ptr():  # the fused kernels normally wrote it in place already
+            buf.copy_(grad_recv)
+        xc.barrier()  # every rank's "dx" rows are written
+        xc.backward_reads_pending = False
         dx = torch.empty(ctx.shape, dtype=grad_recv.dtype, device=grad_recv.device)
         _pull(xc, "dx", None, dx, None, plan)
-        xc.barrier()
+        # the next write into "dx" comes after the next pass's barriers, which no rank passes before it finished this pull
         return dx, None, None
 
 
@@ -259,13 +269,14 @@ class _PeerCombine(torch.autograd.Function):
     @staticmethod
     def forward(ctx, out_rows, gates, xc, plan):
         T, k = gates.shape
-        xc.bufs["y"][: plan.m_recv].copy_(out_rows)
-        xc.barrier()
+        buf = xc.bufs["y"][: plan.m_recv]
+        if out_rows.data_ptr() != buf.data_ptr():
+            buf.copy_(out_rows)
+        xc.barrier()  # every rank's "y" rows are written
         y = torch.empty(T, out_rows.size(1), dtype=out_rows.dtype, device=out_rows.device)
         expanded = torch.empty(T * k, out_rows.size(1), dtype=out_rows.dtype, device=out_rows.device)
         gates = gates.contiguous()
         _pull(xc, "y", gates, y, expanded, plan)
-        xc.barrier()
         ctx.save_for_backward(expanded, gates)
         ctx.xc, ctx.plan = xc, plan
         return y
@@ -277,9 +288,8 @@ class _PeerCombine(torch.autograd.Function):
         T, k = gates.shape
         grad_y = grad_y.contiguous()
         d_gates = torch.bmm(expanded.view(T, k, -1), grad_y.unsqueeze(2)).squeeze(-1).to(gates.dtype)
-        xc.barrier()
         _push(xc, "dy", grad_y, plan.ss, k, gates.reshape(-1), plan)
-        xc.barrier()
+        xc.barrier()  # all gradient rows have landed
         return xc.bufs["dy"][: plan.m_recv], d_gates, None, None
 
 
@@ -351,7 +361,10 @@ class MoE_B200_EP(nn.Module):
         from .scattermoe import fused_swiglu_experts
 
         ones = torch.ones(rows.size(0), 1, dtype=rows.dtype, device=rows.device)
-        return fused_swiglu_experts(rows, self.c_fc_weight, self.c_proj_weight, ones, local_ids.view(-1, 1))
+        y_out = dx_out = None
+        if self.exchange is not None:  # the kernels write straight into the buffers the other ranks read
+            y_out, dx_out = self.exchange.bufs["y"], self.exchange.bufs["dx"]
+        return fused_swiglu_experts(rows, self.c_fc_weight, self.c_proj_weight, ones, local_ids.view(-1, 1), y_out, dx_out)
 
     def forward(self, hidden_states: torch.Tensor):
         shape = hidden_states.shape

@@ -240,7 +240,11 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, x, w_fc, w_proj, router_weights, selected_experts):
+    def forward(ctx, x, w_fc, w_proj, router_weights, selected_experts, out_bufs=None):
+        # out_bufs = (y_out, dx_out), k == 1 only: caller-owned (rows >= T, H) buffers that receive the output / the
+        # input gradient directly, e.g. exchange buffers other ranks read from.  Passed as a tuple so that autograd
+        # does not see them as inputs.
+        y_out, dx_out = out_bufs if out_bufs is not None else (None, None)
         T, H = x.shape
         E, I2, _ = w_fc.shape
         I = I2 // 2
@@ -261,7 +265,7 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
         _gather_rows(x, row_token, x_rows)
         _launch("up_forward", _up_forward, x_rows, w_fc, offsets, None, h, a)
         del x_rows  # re-gathered in the backward pass: cheaper than keeping k copies of every token alive
-        y_expanded = torch.empty(M, H, device=x.device, dtype=x.dtype)
+        y_expanded = y_out[:M] if (k == 1 and y_out is not None) else torch.empty(M, H, device=x.device, dtype=x.dtype)
         _launch("down_forward", _down_forward, a, w_proj, offsets, row_slot, gates, y_expanded)
         if k == 1:
             y = y_expanded
@@ -271,6 +275,7 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
         ctx.save_for_backward(x, w_fc, w_proj, gates, offsets, row_token, row_slot, h)
         ctx.k = k
         ctx.rw_dtype = router_weights.dtype
+        ctx.dx_out = dx_out if k == 1 else None
         return y
 
     @staticmethod
@@ -303,7 +308,7 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
             _launch("up_wgrad", _wgrad, dh, None, x_rows, None, offsets, d_w_fc, cap)
         del g_rows
         if need_x:
-            dx_expanded = torch.empty(M, H, device=x.device, dtype=x.dtype)
+            dx_expanded = ctx.dx_out[:M] if ctx.dx_out is not None else torch.empty(M, H, device=x.device, dtype=x.dtype)
             _launch("up_dgrad", _up_dgrad, dh, w_fc, offsets, row_slot, dx_expanded)
             if k == 1:
                 d_x = dx_expanded
@@ -312,11 +317,12 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
                 combine(dx_expanded, None, d_x, k)
         if need_g:
             d_rw = d_gates.view(T, k).to(ctx.rw_dtype)
-        return d_x, d_w_fc, d_w_proj, d_rw, None
+        return d_x, d_w_fc, d_w_proj, d_rw, None, None
 
 
-def fused_swiglu_experts(x, w_fc, w_proj, router_weights, selected_experts):
-    return _FusedSwiGLUExperts.apply(x, w_fc, w_proj, router_weights, selected_experts)
+def fused_swiglu_experts(x, w_fc, w_proj, router_weights, selected_experts, y_out=None, dx_out=None):
+    out_bufs = (y_out, dx_out) if (y_out is not None or dx_out is not None) else None
+    return _FusedSwiGLUExperts.apply(x, w_fc, w_proj, router_weights, selected_experts, out_bufs)
 
 
 # --------------------------------------------------------------------------------------------------
