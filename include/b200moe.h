@@ -50,6 +50,10 @@ extern "C" {
 #define B200MOE_ENGINE_SIMT 1 /* CUDA-core kernels for every dtype (exact fp32 math, cross-checks)   */
 #define B200MOE_ENGINE_UMMA 2 /* tcgen05 only; shapes it cannot take return B200MOE_ERR_LAYOUT       */
 #define B200MOE_ENGINE_UMMA_1CTA 3 /* like UMMA, but never the two-CTA (cta_group::2) kernels     */
+#define B200MOE_ENGINE_UMMA_GATHER4 4 /* like UMMA, and operands whose rows are picked by a row map are fetched by
+                                       * TMA row gather (tile::gather4) inside the two-CTA kernel instead of by the
+                                       * cp.async gather warps of the one-CTA kernel; measured about 3x slower, kept
+                                       * for comparison */
 
 typedef void* b200moe_stream_t; /* cudaStream_t */
 

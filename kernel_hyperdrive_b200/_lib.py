@@ -21,7 +21,7 @@ SOURCES = ["api.cu", "routing.cu", "rowops.cu", "simt_gemm.cu", "umma_gemm.cu", 
 HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(PKG_DIR, "..", "include", "b200moe.h")]
 
 F32, BF16, F16 = 0, 1, 2
-ENGINE_AUTO, ENGINE_SIMT, ENGINE_UMMA, ENGINE_UMMA_1CTA = 0, 1, 2, 3
+ENGINE_AUTO, ENGINE_SIMT, ENGINE_UMMA, ENGINE_UMMA_1CTA, ENGINE_UMMA_GATHER4 = 0, 1, 2, 3, 4
 DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
 
 _lock = threading.Lock()

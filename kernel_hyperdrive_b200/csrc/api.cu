@@ -46,7 +46,7 @@ int pick_engine(const G& g, int dtype, F&& supported, const char* what) {
     int eng = current_engine();
     if (eng == B200MOE_ENGINE_SIMT) return 0;
     bool ok = dtype != B200MOE_F32 && supported(g, dtype);
-    if (eng == B200MOE_ENGINE_UMMA || eng == B200MOE_ENGINE_UMMA_1CTA) {
+    if (eng == B200MOE_ENGINE_UMMA || eng == B200MOE_ENGINE_UMMA_1CTA || eng == B200MOE_ENGINE_UMMA_GATHER4) {
         if (!ok) {
             set_error_detail("%s: shape/dtype not handled by the tcgen05 engine", what);
             return B200MOE_ERR_LAYOUT;
@@ -103,7 +103,7 @@ extern "C" const char* b200moe_error_string(int code) {
 extern "C" const char* b200moe_last_error_detail(void) { return g_detail; }
 
 extern "C" int b200moe_set_engine(int engine) {
-    if (engine < B200MOE_ENGINE_AUTO || engine > B200MOE_ENGINE_UMMA_1CTA) return B200MOE_ERR_ARG;
+    if (engine < B200MOE_ENGINE_AUTO || engine > B200MOE_ENGINE_UMMA_GATHER4) return B200MOE_ERR_ARG;
     return g_engine.exchange(engine);
 }
 
@@ -167,6 +167,7 @@ extern "C" int b200moe_scatter2scatter(const void* X, int64_t ldx, const void* W
     g.A = X;
     g.lda = ldx;
     g.a_map = need_src ? src_map : nullptr;
+    g.a_rows = M;
     g.W = W;
     g.w_se = w_se;
     g.w_sk = w_sk;
@@ -232,6 +233,7 @@ extern "C" int b200moe_up_forward(const void* x, int64_t ldx, const void* w_fc, 
     g.A = x;
     g.lda = ldx;
     g.a_map = row_token;
+    g.a_rows = row_token ? T : m_cap;
     g.W = w_fc;  // (E, 2I, H): element (e, kk, n) at e*2I*H + n*H + kk
     g.w_se = (int64_t)2 * I * H;
     g.w_sk = 1;
@@ -301,6 +303,7 @@ extern "C" int b200moe_down_dgrad(const void* grad_out, int64_t ldg, const void*
     g.A = grad_out;
     g.lda = ldg;
     g.a_map = row_token;
+    g.a_rows = row_token ? M : m_cap;  // an upper bound: the rows of grad_out are the tokens, M / k
     g.W = w_proj;  // reduction over H now: element (e, kk=h, n=i) at e*H*I + kk*I + n
     g.w_se = (int64_t)H * I;
     g.w_sk = I;
@@ -352,6 +355,7 @@ extern "C" int b200moe_wgrad(const void* P, int64_t ldp, const int32_t* p_map, c
     g.Q = Q;
     g.ldq = ldq;
     g.q_map = q_map;
+    g.map_rows = m_cap;
     g.DW = DW;
     g.d_se = (int64_t)n_out * n_in;
     g.d_sm = n_in;

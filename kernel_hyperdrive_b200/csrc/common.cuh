@@ -67,6 +67,7 @@ struct RowGemm {
     const void* A;
     int64_t lda;
     const int32_t* a_map;  // layout row -> row of A (negative: zero row); NULL: identity
+    int64_t a_rows;        // upper bound of the rows of A that a_map can name (tensor-map extent of the row gather)
     const void* W;
     int64_t w_se, w_sk, w_sn;  // element strides of W (E, K, N); one of w_sk, w_sn is 1
     void* out;
@@ -93,6 +94,7 @@ struct WGemm {
     const void* Q;
     int64_t ldq;
     const int32_t* q_map;
+    int64_t map_rows;  // upper bound of the rows p_map / q_map can name
     void* DW;
     int64_t d_se, d_sm, d_sn;
     const int64_t* offsets;

@@ -51,6 +51,15 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
         ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(c0), "r"(c1)
         : "memory");
 }
+// Row gather of one CTA of the pair: four rows (indices r[0..3]) of 64 columns starting at column c0 land as four
+// consecutive 128-byte rows at dst; rows outside the tensor read as zeros.
+__device__ __forceinline__ void tma_gather4_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, const int (&r)[4]) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes.cta_group::2 "
+        "[%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(c0), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3])
+        : "memory");
+}
 __device__ __forceinline__ void tc_commit_pair(uint32_t cluster_bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
 }
@@ -178,80 +187,128 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
     const int ntiles = total_tiles2(p, tb);
 
     if (warp == 0) {
-        // ---------------- TMA producer (one lane per CTA) ----------------
-        // A cursor walks the (tile, k step) sequence of this cluster.  (Asking L2 to prefetch the same boxes some
-        // steps ahead was measured and lost a third of the throughput: the TMA unit is busy enough with the loads.)
-        if (lane == 0) {
-            struct Box {
-                const CUtensorMap* map;
-                int c0, c1;
-                uint32_t off;  // byte offset inside the stage's A (is_b == 0) or B-half (is_b == 1) buffer
-                int is_b;
-            };
-            struct Cursor {
-                int t, ks;
-                bool valid;
-                Tile ti;
-            };
-            auto settle = [&](Cursor& c) {  // moves to the next tile that has k steps (an empty expert has none)
-                for (;;) {
-                    c.valid = c.t < ntiles;
-                    if (!c.valid) return;
-                    decode_tile2(p, tb, c.t, rank, c.ti);
-                    if (c.ti.ksteps > 0) return;
-                    c.t += nclusters;
-                }
-            };
-            auto advance = [&](Cursor& c) {
-                if (++c.ks >= c.ti.ksteps) {
-                    c.ks = 0;
-                    c.t += nclusters;
-                    settle(c);
-                }
-            };
-            auto boxes_of = [&](const Cursor& c, Box (&bx)[4]) -> int {
-                const Tile& ti = c.ti;
-                const int k0 = c.ks * BK;
-                int n = 0;
-                if (p.wfam) {
-                    int krow = ti.row0 + k0;
-                    for (int j = 0; j < 2; ++j) bx[n++] = Box{&tmap_a, ti.mb * BM + j * 64, krow, (uint32_t)j * 8192u, 0};
-                    for (int j = 0; j < 2; ++j) bx[n++] = Box{&tmap_b, ti.nb * BN + (int)rank * 128 + j * 64, krow, (uint32_t)j * 8192u, 1};
-                } else {
-                    bx[n++] = Box{&tmap_a, k0, ti.row0, 0u, 0};  // box 64 x 128: this CTA's rows
-                    if (p.b_mn) {
-                        int krow = ti.e * p.b_rows_per_expert + k0;
-                        for (int j = 0; j < 2; ++j) bx[n++] = Box{&tmap_b, ti.nb * BN + (int)rank * 128 + j * 64, krow, (uint32_t)j * 8192u, 1};
-                    } else {
-                        int r0;
-                        if (EPI == EPI_SWIGLU) {
-                            // leader: 128 "up" rows, peer: the matching 128 "gate" rows
-                            r0 = ti.e * p.b_rows_per_expert + ti.nb * 128 + (int)rank * p.swiglu_half;
-                        } else {
-                            r0 = ti.e * p.b_rows_per_expert + ti.nb * BN + (int)rank * 128;
-                        }
-                        bx[n++] = Box{&tmap_b, k0, r0, 0u, 1};  // box 64 x 128
-                    }
-                }
-                return n;
-            };
+        // ---------------- TMA producer ----------------
+        if (p.a_g4 || p.b_g4) {
+            // Row-gather variant (opt-in engine): operands whose rows are picked by a row map come in through TMA row
+            // gather (tile::gather4).  Every lane owns four rows of the stage and issues one gather per k step and
+            // gathered operand; lane 0 also waits for the free stage, arms the barrier and issues the plain tile loads.
+            // The row indices are read before the wait, so their latency hides behind it.
             int stage = 0;
             uint32_t phase = 0;
-            Cursor ld{cluster_id, 0, false, {}};
-            settle(ld);
-            Box bx[4];
-            while (ld.valid) {
-                if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 211, 40)) break;
-                const uint32_t lead_full = map_to_cta(smem_u32(&full_bar[stage]), 0);
-                if (rank == 0) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * (A_STAGE_BYTES + B_HALF_BYTES));
-                const uint32_t sa = smem_u32(smem_a + stage * A_STAGE_BYTES);
-                const uint32_t sb = smem_u32(smem_b + stage * B_HALF_BYTES);
-                int n = boxes_of(ld, bx);
-                for (int i = 0; i < n; ++i) tma_load_2d_pair((bx[i].is_b ? sb : sa) + bx[i].off, bx[i].map, lead_full, bx[i].c0, bx[i].c1);
-                advance(ld);
-                if (++stage == STAGES2) {
-                    stage = 0;
-                    phase ^= 1;
+            Tile ti;
+            int ok = 1;
+            for (int t = cluster_id; t < ntiles && ok; t += nclusters) {
+                decode_tile2(p, tb, t, rank, ti);
+                for (int ks = 0; ks < ti.ksteps; ++ks) {
+                    const int k0 = ks * BK;
+                    int ia[4], ib[4];
+                    if (!p.wfam) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {  // K-major A: rows 4*lane .. 4*lane+3 of this CTA's 128 tile rows
+                            int r = 4 * lane + i, v = -1;
+                            if (r < ti.rows_valid) v = p.a_map[ti.row0 + r];
+                            ia[i] = v < 0 ? p.a_oob : v;
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {  // MN-major: token rows k0 + 4*(lane%16) .. +3, column block lane/16
+                            int r = k0 + 4 * (lane & 15) + i, va = -1, vb = -1;
+                            if (r < ti.rows_valid) {
+                                if (p.a_g4) va = p.a_map[ti.row0 + r];
+                                if (p.b_g4) vb = p.b_map[ti.row0 + r];
+                            }
+                            ia[i] = va < 0 ? p.a_oob : va;
+                            ib[i] = vb < 0 ? p.b_oob : vb;
+                        }
+                    }
+                    const uint32_t lead_full = map_to_cta(smem_u32(&full_bar[stage]), 0);
+                    const uint32_t sa = smem_u32(smem_a + stage * A_STAGE_BYTES);
+                    const uint32_t sb = smem_u32(smem_b + stage * B_HALF_BYTES);
+                    if (lane == 0) {
+                        ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 211, 40) ? 1 : 0;
+                        if (ok) {
+                            if (rank == 0) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * (A_STAGE_BYTES + B_HALF_BYTES));
+                            if (p.wfam) {
+                                int krow = ti.row0 + k0;
+                                if (!p.a_g4)
+                                    for (int j = 0; j < 2; ++j) tma_load_2d_pair(sa + j * 8192, &tmap_a, lead_full, ti.mb * BM + j * 64, krow);
+                                if (!p.b_g4)
+                                    for (int j = 0; j < 2; ++j)
+                                        tma_load_2d_pair(sb + j * 8192, &tmap_b, lead_full, ti.nb * BN + (int)rank * 128 + j * 64, krow);
+                            } else if (p.b_mn) {
+                                int krow = ti.e * p.b_rows_per_expert + k0;
+                                for (int j = 0; j < 2; ++j)
+                                    tma_load_2d_pair(sb + j * 8192, &tmap_b, lead_full, ti.nb * BN + (int)rank * 128 + j * 64, krow);
+                            } else {
+                                int r0 = EPI == EPI_SWIGLU ? ti.e * p.b_rows_per_expert + ti.nb * 128 + (int)rank * p.swiglu_half
+                                                           : ti.e * p.b_rows_per_expert + ti.nb * BN + (int)rank * 128;
+                                tma_load_2d_pair(sb, &tmap_b, lead_full, k0, r0);
+                            }
+                        }
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) break;
+                    if (!p.wfam) {
+                        tma_gather4_pair(sa + lane * 512, &tmap_a, lead_full, k0, ia);
+                    } else {
+                        const int j = lane >> 4;
+                        const uint32_t off = (uint32_t)j * 8192u + (uint32_t)(lane & 15) * 512u;
+                        if (p.a_g4) tma_gather4_pair(sa + off, &tmap_a, lead_full, ti.mb * BM + j * 64, ia);
+                        if (p.b_g4) tma_gather4_pair(sb + off, &tmap_b, lead_full, ti.nb * BN + (int)rank * 128 + j * 64, ib);
+                    }
+                    if (++stage == STAGES2) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+        } else if (lane == 0) {
+            // plain tile loads: one lane per CTA
+            int stage = 0;
+            uint32_t phase = 0;
+            Tile ti;
+            bool ok = true;
+            for (int t = cluster_id; t < ntiles && ok; t += nclusters) {
+                decode_tile2(p, tb, t, rank, ti);
+                for (int ks = 0; ks < ti.ksteps; ++ks) {
+                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 211, 40)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t lead_full = map_to_cta(smem_u32(&full_bar[stage]), 0);
+                    if (rank == 0) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * (A_STAGE_BYTES + B_HALF_BYTES));
+                    const uint32_t sa = smem_u32(smem_a + stage * A_STAGE_BYTES);
+                    const uint32_t sb = smem_u32(smem_b + stage * B_HALF_BYTES);
+                    const int k0 = ks * BK;
+                    if (p.wfam) {
+                        int krow = ti.row0 + k0;
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) tma_load_2d_pair(sa + j * 8192, &tmap_a, lead_full, ti.mb * BM + j * 64, krow);
+#pragma unroll
+                        for (int j = 0; j < 2; ++j)
+                            tma_load_2d_pair(sb + j * 8192, &tmap_b, lead_full, ti.nb * BN + (int)rank * 128 + j * 64, krow);
+                    } else {
+                        tma_load_2d_pair(sa, &tmap_a, lead_full, k0, ti.row0);  // box 64 x 128: this CTA's rows
+                        if (p.b_mn) {
+                            int krow = ti.e * p.b_rows_per_expert + k0;
+#pragma unroll
+                            for (int j = 0; j < 2; ++j)
+                                tma_load_2d_pair(sb + j * 8192, &tmap_b, lead_full, ti.nb * BN + (int)rank * 128 + j * 64, krow);
+                        } else {
+                            int r0;
+                            if (EPI == EPI_SWIGLU) {
+                                // leader: 128 "up" rows, peer: the matching 128 "gate" rows
+                                r0 = ti.e * p.b_rows_per_expert + ti.nb * 128 + (int)rank * p.swiglu_half;
+                            } else {
+                                r0 = ti.e * p.b_rows_per_expert + ti.nb * BN + (int)rank * 128;
+                            }
+                            tma_load_2d_pair(sb, &tmap_b, lead_full, k0, r0);  // box 64 x 128
+                        }
+                    }
+                    if (++stage == STAGES2) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
                 }
             }
         }

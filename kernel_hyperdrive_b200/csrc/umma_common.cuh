@@ -27,11 +27,13 @@ struct UmmaParams {
     int swiglu_half;  // EPI_SWIGLU: I (columns of one half); tiles cover 128 columns of each half
     // operand A (R: activations; W: P)
     int a_tma, a_mn;
+    int a_g4, a_oob;  // two-CTA kernel: rows of A come through TMA row gather by a_map; a_oob = index that reads as zeros
     const void* a_ptr;
     int64_t a_ld;
     const int32_t* a_map;
     // operand B (R: weights; W: Q)
     int b_tma, b_mn;
+    int b_g4, b_oob;
     const void* b_ptr;
     int64_t b_ld;
     const int32_t* b_map;
@@ -398,6 +400,7 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
 int make_store_map(CUtensorMap* map, const void* base, int64_t experts, int64_t rows, int64_t cols, int64_t ld, int64_t se,
                    int is_f16);
 int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows, int is_f16);
+int make_gather_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int is_f16);
 int sm_count();
 uint32_t make_idesc(int a_mn, int b_mn, int is_f16, int m);
 

@@ -83,6 +83,11 @@ int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int
     return B200MOE_OK;
 }
 
+// Row-gather map: [rows][cols] with row stride ld, box of 64 columns x 1 row (tile::gather4 fetches four such rows).
+int make_gather_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int is_f16) {
+    return make_map(map, base, rows, cols, ld, 1, is_f16);
+}
+
 int sm_count() {
     static int cached[64] = {0};
     int dev = 0;
@@ -537,7 +542,14 @@ int umma_row_gemm(const RowGemm& g, int dtype, int32_t* status, cudaStream_t str
     p.K = g.K;
     p.is_f16 = dtype == B200MOE_F16;
     p.a_mn = 0;
-    p.a_tma = g.a_map == nullptr;
+    // Rows picked by a row map: cp.async gather warps of the one-CTA kernel.  TMA row gather (tile::gather4) inside
+    // the two-CTA kernel is built too but sustains only about a third of the rate (one gather instruction moves 512
+    // bytes and the TMA unit issues them far slower than box loads), so it runs only when asked for.
+    const bool gather4 = g.a_map != nullptr && current_engine() == B200MOE_ENGINE_UMMA_GATHER4 && g.a_rows > 0 &&
+                         g.a_rows < ((int64_t)1 << 31);
+    p.a_g4 = gather4;
+    p.a_oob = (int)g.a_rows;
+    p.a_tma = g.a_map == nullptr || gather4;
     p.a_ptr = g.A;
     p.a_ld = g.lda;
     p.a_map = g.a_map;
@@ -558,7 +570,10 @@ int umma_row_gemm(const RowGemm& g, int dtype, int32_t* status, cudaStream_t str
 
     CUtensorMap ma{}, mb{};
     int rc;
-    if (p.a_tma) {
+    if (p.a_g4) {
+        rc = make_gather_map(&ma, g.A, g.a_rows, g.K, g.lda, p.is_f16);
+        if (rc) return rc;
+    } else if (p.a_tma) {
         rc = make_map(&ma, g.A, g.rows_cap, g.K, g.lda, 128, p.is_f16);
         if (rc) return rc;
     }
@@ -623,8 +638,17 @@ int umma_w_gemm(const WGemm& g, int dtype, int32_t* status, cudaStream_t stream)
     p.b_mn = 1;
     // An operand can come through TMA only when its rows are the layout rows themselves and filler rows are
     // known to be zero, i.e. in the padded order; everything else is gathered with zero fill.
-    p.a_tma = g.padded && g.p_map == nullptr && g.rows_cap > 0;
-    p.b_tma = g.padded && g.q_map == nullptr && g.rows_cap > 0;
+    const bool pair_ok = current_engine() == B200MOE_ENGINE_UMMA_GATHER4 && g.map_rows > 0 && g.map_rows < ((int64_t)1 << 31);
+    p.a_g4 = g.p_map != nullptr && pair_ok;
+    p.b_g4 = g.q_map != nullptr && pair_ok;
+    p.a_oob = p.b_oob = (int)g.map_rows;
+    p.a_tma = (g.padded && g.p_map == nullptr && g.rows_cap > 0) || p.a_g4;
+    p.b_tma = (g.padded && g.q_map == nullptr && g.rows_cap > 0) || p.b_g4;
+    if (!(p.a_tma && p.b_tma)) {  // the one-CTA kernel gathers with cp.async: no row-gather maps there
+        if (p.a_g4) p.a_tma = 0;
+        if (p.b_g4) p.b_tma = 0;
+        p.a_g4 = p.b_g4 = 0;
+    }
     p.a_ptr = g.P;
     p.a_ld = g.ldp;
     p.a_map = g.p_map;
@@ -642,12 +666,12 @@ int umma_w_gemm(const WGemm& g, int dtype, int32_t* status, cudaStream_t stream)
     int rc;
     bool have = false;
     if (p.a_tma) {
-        rc = make_map(&ma, g.P, g.rows_cap, g.Mout, g.ldp, 64, p.is_f16);
+        rc = p.a_g4 ? make_gather_map(&ma, g.P, g.map_rows, g.Mout, g.ldp, p.is_f16) : make_map(&ma, g.P, g.rows_cap, g.Mout, g.ldp, 64, p.is_f16);
         if (rc) return rc;
         have = true;
     }
     if (p.b_tma) {
-        rc = make_map(&mb, g.Q, g.rows_cap, g.Nout, g.ldq, 64, p.is_f16);
+        rc = p.b_g4 ? make_gather_map(&mb, g.Q, g.map_rows, g.Nout, g.ldq, p.is_f16) : make_map(&mb, g.Q, g.rows_cap, g.Nout, g.ldq, 64, p.is_f16);
         if (rc) return rc;
         if (!have) ma = mb;
     } else if (have) {

@@ -155,6 +155,11 @@ def scattered_experts(inputs, expert_weights, k, sorted_expert_idxs, sorted_scat
 # from it without synchronising inside the step.
 _timing_sink: list | None = None
 
+# The backward pass needs the token rows in the padded grouped order again (weight gradient of the up projection).
+# True: the forward's gathered copy (k rows per token) is kept for it; False: only the tokens are kept and the rows
+# are gathered a second time, which trades one HBM pass for k-1 token copies of memory.
+KEEP_GATHERED_INPUT = True
+
 
 def set_timing_sink(sink: list | None) -> None:
     global _timing_sink
@@ -264,7 +269,8 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
         x_rows = torch.empty(cap, H, device=x.device, dtype=x.dtype)
         _gather_rows(x, row_token, x_rows)
         _launch("up_forward", _up_forward, x_rows, w_fc, offsets, None, h, a)
-        del x_rows  # re-gathered in the backward pass: cheaper than keeping k copies of every token alive
+        if not KEEP_GATHERED_INPUT:
+            x_rows = None
         y_expanded = y_out[:M] if (k == 1 and y_out is not None) else torch.empty(M, H, device=x.device, dtype=x.dtype)
         _launch("down_forward", _down_forward, a, w_proj, offsets, row_slot, gates, y_expanded)
         if k == 1:
@@ -272,7 +278,7 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
         else:
             y = torch.empty(T, H, device=x.device, dtype=x.dtype)
             combine(y_expanded, None, y, k)
-        ctx.save_for_backward(x, w_fc, w_proj, gates, offsets, row_token, row_slot, h)
+        ctx.save_for_backward(x, w_fc, w_proj, gates, offsets, row_token, row_slot, h, x_rows)
         ctx.k = k
         ctx.rw_dtype = router_weights.dtype
         ctx.dx_out = dx_out if k == 1 else None
@@ -280,7 +286,7 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_y):
-        x, w_fc, w_proj, gates, offsets, row_token, row_slot, h = ctx.saved_tensors
+        x, w_fc, w_proj, gates, offsets, row_token, row_slot, h, x_rows = ctx.saved_tensors
         k = ctx.k
         T, H = x.shape
         E, I2, _ = w_fc.shape
@@ -303,8 +309,9 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
         del ag
         if need_w1:
             d_w_fc = torch.empty_like(w_fc)
-            x_rows = g_rows  # the gathered gradient rows are dead now: reuse the buffer
-            _gather_rows(x, row_token, x_rows)
+            if x_rows is None:
+                x_rows = g_rows  # the gathered gradient rows are dead now: reuse the buffer
+                _gather_rows(x, row_token, x_rows)
             _launch("up_wgrad", _wgrad, dh, None, x_rows, None, offsets, d_w_fc, cap)
         del g_rows
         if need_x:

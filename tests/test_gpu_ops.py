@@ -27,7 +27,7 @@ def _engine_reset():
 
 
 def use_engine(name):
-    _lib.set_engine({"simt": _lib.ENGINE_SIMT, "umma": _lib.ENGINE_UMMA, "umma1": _lib.ENGINE_UMMA_1CTA, "auto": _lib.ENGINE_AUTO}[name])
+    _lib.set_engine({"simt": _lib.ENGINE_SIMT, "umma": _lib.ENGINE_UMMA, "umma1": _lib.ENGINE_UMMA_1CTA, "gather4": _lib.ENGINE_UMMA_GATHER4, "auto": _lib.ENGINE_AUTO}[name])
 
 
 def routed(E, k, T, seed, empty_from=None):
@@ -141,3 +141,35 @@ def test_shape_assertions_like_the_reference():
         kh.scatter2scatter(torch.zeros(15, 64, device="cuda"), torch.zeros(4, 64, 64, device="cuda"), se.cuda(), ss.cuda(), torch.zeros(32, 64, device="cuda"), 2)
     with pytest.raises(AssertionError):
         kh.group(torch.zeros(15, 64, device="cuda"), ss.cuda(), torch.zeros(32, 64, device="cuda"), None, 2)
+
+
+@pytest.mark.parametrize("E,k,T,K,N", [(8, 2, 300, 256, 512), (5, 3, 333, 136, 200)])
+def test_tma_row_gather_engine(E, k, T, K, N):
+    """Operands picked by a row map fetched with TMA row gather (tile::gather4) in the two-CTA kernel: same results as
+    the default engine (which gathers with cp.async in the one-CTA kernel), for the gathered forward GEMM and the
+    weight gradient with a gathered operand."""
+    ids, se, ss, off = routed(E, k, T, seed=11)
+    M = T * k
+    X = rnd((T, K), torch.bfloat16, 1).cuda()
+    W = rnd((E, N, K), torch.bfloat16, 2, 0.05).cuda().permute(0, 2, 1)
+    outs = []
+    for eng in ("umma", "gather4"):
+        use_engine(eng)
+        out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        kh.scatter2scatter(X, W, se.cuda(), ss.cuda(), out, k, False, True)
+        outs.append(out)
+    assert torch.isfinite(outs[1]).all() and torch.equal(outs[0], outs[1])
+    from kernel_hyperdrive_b200 import scattermoe as sm
+
+    flat = ids.flatten().cuda()
+    _, _, offs, _, row_token, row_slot = kh.route(flat, E, k, False, True)
+    cap = row_token.numel()
+    Q = rnd((cap, N), torch.bfloat16, 3).cuda()
+    Q[row_token < 0] = 0
+    grads = []
+    for eng in ("umma", "gather4"):
+        use_engine(eng)
+        dw = torch.full((E, K, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        sm._wgrad(X, row_token, Q, None, offs, dw, cap)
+        grads.append(dw)
+    assert torch.isfinite(grads[1]).all() and rel_l2(grads[1], grads[0]) < 1e-3
