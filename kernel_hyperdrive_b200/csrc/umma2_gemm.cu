@@ -225,7 +225,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
                     const uint32_t sa = smem_u32(smem_a + stage * A_STAGE_BYTES);
                     const uint32_t sb = smem_u32(smem_b + stage * B_HALF_BYTES);
                     if (lane == 0) {
-                        ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 211, 40) ? 1 : 0;
+                        ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 211) ? 1 : 0;
                         if (ok) {
                             if (rank == 0) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * (A_STAGE_BYTES + B_HALF_BYTES));
                             if (p.wfam) {
@@ -271,7 +271,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
             for (int t = cluster_id; t < ntiles && ok; t += nclusters) {
                 decode_tile2(p, tb, t, rank, ti);
                 for (int ks = 0; ks < ti.ksteps; ++ks) {
-                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 211, 40)) {
+                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 211)) {
                         ok = false;
                         break;
                     }

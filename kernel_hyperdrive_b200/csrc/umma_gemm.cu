@@ -211,7 +211,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
                 decode_tile(p, tb, t, ti);
                 for (int ks = 0; ks < ti.ksteps; ++ks) {
-                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 201, 40)) {
+                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 201)) {
                         ok = false;
                         break;
                     }
@@ -336,7 +336,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     for (int i = 0; i < 8; ++i) src_r[i] = src_n[i];
                     load_rows(t + gridDim.x, src_n);
                     for (int ks = 0; ks < ti.ksteps; ++ks) {
-                        if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 204, 40)) {
+                        if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 204)) {
                             ok = false;
                             break;
                         }
@@ -385,7 +385,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                             cur_b[i] = nxt_b[i];
                         }
                         if (ks + 1 < ti.ksteps) load_idx(ti, ks + 1, nxt_a, nxt_b);
-                        if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 204, 40)) {
+                        if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 204)) {
                             ok = false;
                             break;
                         }
