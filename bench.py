@@ -181,6 +181,22 @@ def workload_config(w, n_gpus, exchange="peer-memory kernels over NVLink"):
 # --------------------------------------------------------------------------------------------------
 
 
+def bind_to_gpu_numa_node(index: int) -> None:
+    """Binds this process to the CPU cores next to its GPU (NVML's ideal affinity) before any pinned host buffer is
+    allocated, so that with several ranks the host<->device copies of each rank stay on its own NUMA node."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+        cpus = [64 * i + b for i, word in enumerate(words) for b in range(64) if (word >> b) & 1]
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+    except Exception:  # noqa: BLE001 - affinity is an optimisation, never a requirement
+        pass
+
+
 def run_gpu_arm(args, w):
     import torch.distributed as dist
 
@@ -194,6 +210,7 @@ def run_gpu_arm(args, w):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        bind_to_gpu_numa_node(local_rank)
         dist.init_process_group("nccl", device_id=dev)
     dtype = synthetic.TORCH_DTYPES[w.dtype]
     E, k, H, I, T = w.num_experts, w.top_k, w.hidden, w.intermediate, w.tokens
