@@ -69,6 +69,12 @@ int64_t b200moe_launch_count(void);
  * stream; returns B200MOE_OK or B200MOE_ERR_DEVICE and clears the word.  status may not be NULL. */
 int b200moe_check_status(int32_t* status_device, b200moe_stream_t stream);
 
+/* Failure-path self test (no counterpart in the reference): launches one small CTA that waits, for at most
+ * limit_cycles SM cycles, on a barrier nothing arrives on, using the same bounded wait as the GEMM kernels.  The wait
+ * gives up, writes code 299 to the status word and the kernel returns normally (finished, optional device int32,
+ * receives 1).  b200moe_check_status then reports B200MOE_ERR_DEVICE and the context stays usable. */
+int b200moe_selftest_bounded_wait(int32_t* status, int64_t limit_cycles, int32_t* finished, b200moe_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Routing
  * ------------------------------------------------------------------------------------------------ */

@@ -67,6 +67,7 @@ def _declare(lib):
         "b200moe_set_engine": (i32, [i32]),
         "b200moe_launch_count": (i64, []),
         "b200moe_check_status": (i32, [vp, vp]),
+        "b200moe_selftest_bounded_wait": (i32, [vp, i64, vp, vp]),
         "b200moe_contiguous_count": (i32, [vp, i32, i64, vp, i32, vp]),
         "b200moe_padded_rows_cap": (i64, [i64, i32]),
         "b200moe_route_workspace_bytes": (i64, [i64, i32]),

@@ -84,7 +84,7 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // that order does not matter (epilogue warps waiting for a whole tile, producers that run stages ahead), so
 // that idle warps do not spend issue slots and power on polling.
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
-                                                   int code, unsigned sleep_ns) {
+                                                   int code, unsigned sleep_ns, long long limit_cycles = WAIT_LIMIT_CYCLES) {
     long long t0 = clock64();
     for (;;) {
 #pragma unroll 1
@@ -93,7 +93,7 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
             if (sleep_ns) __nanosleep(sleep_ns);
         }
         if (*abort_flag) return false;
-        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+        if (clock64() - t0 > limit_cycles) {
             *abort_flag = 1;
             if (status) atomicCAS(status, 0, code);
             return false;

@@ -507,6 +507,26 @@ int launch(const UmmaParams& p, const CUtensorMap& ma, const CUtensorMap& mb, co
 
 }  // namespace
 
+namespace {
+// One CTA waits, with a short limit, on an mbarrier that nothing ever arrives on: the give-up path of the GEMM
+// kernels (abort flag, status word, orderly return) exercised without touching anything that could fault.
+__global__ void bounded_wait_selftest_kernel(int32_t* status, long long limit_cycles, int* finished) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    bool ok = true;
+    if (threadIdx.x == 0) ok = mbar_wait_slow(smem_u32(&bar), 0, &abort_flag, status, 299, 100, limit_cycles);
+    __syncthreads();
+    // every thread sees the abort flag, as the roles of the GEMM kernels do, and the kernel returns normally
+    if (threadIdx.x == 0 && finished) *finished = (!ok && abort_flag) ? 1 : 2;
+}
+}  // namespace
+
 bool umma_row_gemm_supported(const RowGemm& g, int dtype) {
     if (dtype != B200MOE_BF16 && dtype != B200MOE_F16) return false;
     if (g.E > kMaxExperts || g.K % 8 || g.N % 8 || g.lda % 8 || g.ldo % 8) return false;
@@ -685,3 +705,12 @@ int umma_w_gemm(const WGemm& g, int dtype, int32_t* status, cudaStream_t stream)
 }
 
 }  // namespace b200moe
+
+extern "C" int b200moe_selftest_bounded_wait(int32_t* status, int64_t limit_cycles, int32_t* finished, b200moe_stream_t stream_) {
+    using namespace b200moe;
+    B200MOE_REQUIRE(status != nullptr && limit_cycles > 0 && limit_cycles <= 4000000000LL, B200MOE_ERR_ARG,
+                    "selftest_bounded_wait: status must be given and the limit must be at most 4e9 cycles");
+    bounded_wait_selftest_kernel<<<1, 64, 0, (cudaStream_t)stream_>>>(status, (long long)limit_cycles, finished);
+    count_launch();
+    return check_launch("bounded_wait_selftest");
+}
