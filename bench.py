@@ -361,7 +361,8 @@ def run_gpu_arm(args, w):
     peak = peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"])
 
     gemm_ms = {n: sum(v) / args.steps for n, v in per_kernel.items()}  # per step (a name can launch more than once per step)
-    gemm_total_ms = sum(gemm_ms.values())
+    gemm_total_ms = sum(ms for n, ms in gemm_ms.items() if not n.startswith("ep_"))
+    exchange_ms = {n: ms for n, ms in gemm_ms.items() if n.startswith("ep_")}
     local_flops = w.flops_fwd_bwd()
     achieved = local_flops / (gemm_total_ms * 1e-3) / 1e12 if gemm_total_ms > 0 else None
     share = {"up_forward": 4, "down_forward": 2, "down_dgrad": 2, "down_wgrad": 2, "up_wgrad": 4, "up_dgrad": 4}
@@ -377,7 +378,7 @@ def run_gpu_arm(args, w):
         "frac_of_bf16_peak_sustained": value / world / peak,
         "clocks": clock_summary,
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": 2 * x_host.numel() * x_host.element_size(), "d2h_bytes_per_step": 2 * y_host.numel() * y_host.element_size()},
-        "gpu_launches": launches, **extra_info,
+        "gpu_launches": launches, **extra_info, **({"exchange_ms_per_step": exchange_ms} if exchange_ms else {}),
         "roofline": {
             "bound": "tensor", "kernel": "umma2_grouped_kernel (6 launches per step)", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
             "frac": (achieved / peak) if achieved else None, "peak_kind": f"bf16_tflops_sustained of {peak_kind}",

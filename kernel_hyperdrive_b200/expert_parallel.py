@@ -210,6 +210,18 @@ def _make_plan(selected_experts, num_experts: int, world: int, rank: int, group,
 
 
 def _push(xc: PeerExchange, name: str, src, idx, fan_out: int, coeff, plan: "_Plan") -> None:
+    from .scattermoe import _launch
+
+    _launch("ep_push_" + name, _push_impl, xc, name, src, idx, fan_out, coeff, plan)
+
+
+def _pull(xc: PeerExchange, name: str, gates, out, expanded, plan: "_Plan") -> None:
+    from .scattermoe import _launch
+
+    _launch("ep_pull_" + name, _pull_impl, xc, name, gates, out, expanded, plan)
+
+
+def _push_impl(xc: PeerExchange, name: str, src, idx, fan_out: int, coeff, plan: "_Plan") -> None:
     from ._lib import check, dtype_code, lib, ptr, status_word, stream_ptr
 
     M = plan.ss.numel()
@@ -220,7 +232,7 @@ def _push(xc: PeerExchange, name: str, src, idx, fan_out: int, coeff, plan: "_Pl
     )
 
 
-def _pull(xc: PeerExchange, name: str, gates, out, expanded, plan: "_Plan") -> None:
+def _pull_impl(xc: PeerExchange, name: str, gates, out, expanded, plan: "_Plan") -> None:
     from ._lib import check, dtype_code, lib, ptr, stream_ptr
 
     check(
