@@ -57,6 +57,18 @@ __device__ __forceinline__ float sigmoidf_stable(float x) {
     return e / (1.f + e);
 }
 
+// 16-bit tensors round the result to 8 or 11 mantissa bits anyway: the fast exponential and division are exact
+// enough there and cut the instruction count of the element-wise kernels (the accurate form costs a branch and an
+// IEEE division per element).  fp32 tensors keep the accurate form.
+template <typename T>
+__device__ __forceinline__ float sigmoid_for(float x) {
+    return __fdividef(1.f, 1.f + __expf(-x));
+}
+template <>
+__device__ __forceinline__ float sigmoid_for<float>(float x) {
+    return sigmoidf_stable(x);
+}
+
 // ---- segment layout -----------------------------------------------------------------------------
 // Both problem descriptions address rows through a "segment layout": expert e owns layout rows
 // [seg_start(e), seg_start(e) + count(e)), where count comes from the inclusive int64 offsets and

@@ -97,7 +97,7 @@ __global__ void swiglu_fwd_kernel(const T* __restrict__ x, int64_t ldx, T* __res
 #pragma unroll
         for (int i = 0; i < V; ++i) {
             float g = Elem<T>::to_f(gt.v[i]);
-            o.v[i] = Elem<T>::from_f(Elem<T>::to_f(up.v[i]) * g * sigmoidf_stable(g));
+            o.v[i] = Elem<T>::from_f(Elem<T>::to_f(up.v[i]) * g * sigmoid_for<T>(g));
         }
         *reinterpret_cast<Pack<T, V>*>(y + r * ldy + col) = o;
     }
@@ -116,7 +116,7 @@ __global__ void swiglu_bwd_kernel(const T* __restrict__ x, int64_t ldx, const T*
 #pragma unroll
         for (int i = 0; i < V; ++i) {
             float g = Elem<T>::to_f(gt.v[i]), u = Elem<T>::to_f(up.v[i]), dv = Elem<T>::to_f(d.v[i]);
-            float sg = sigmoidf_stable(g);
+            float sg = sigmoid_for<T>(g);
             du.v[i] = Elem<T>::from_f(dv * g * sg);
             dg.v[i] = Elem<T>::from_f(dv * u * (sg + g * sg * (1.f - sg)));
         }
@@ -150,7 +150,7 @@ __global__ void dgrad_down_post_kernel(const T* __restrict__ h, T* __restrict__ 
     for (int c = threadIdx.x; c < I; c += blockDim.x) {
         float up = Elem<T>::to_f(h_row[c]), gt = Elem<T>::to_f(h_row[I + c]);
         float u = Elem<T>::to_f(ag_row[c]);
-        float sg = sigmoidf_stable(gt);
+        float sg = sigmoid_for<T>(gt);
         float act = Elem<T>::to_f(Elem<T>::from_f(up * gt * sg));  // the forward stores it in T
         dot += act * u;
         float da = Elem<T>::to_f(Elem<T>::from_f(g * u));

@@ -328,6 +328,9 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
 
 
 def fused_swiglu_experts(x, w_fc, w_proj, router_weights, selected_experts, y_out=None, dx_out=None):
+    if x.size(0) == 0:
+        # no tokens: nothing to launch; the zero-weighted sums keep every input in the graph with a zero gradient
+        return x.new_zeros(0, x.size(1)) + 0 * (x.sum() + w_fc.sum() + w_proj.sum() + router_weights.sum())
     out_bufs = (y_out, dx_out) if (y_out is not None or dx_out is not None) else None
     return _FusedSwiGLUExperts.apply(x, w_fc, w_proj, router_weights, selected_experts, out_bufs)
 

@@ -191,3 +191,30 @@ def test_torch_compile_fullgraph(act_name):
     y1, _ = mc(x)
     y1.sum().backward()
     assert rel_l2(y1, y0) < 1e-3 and rel_l2(x.grad, g0) < 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_empty_batch_and_single_token(dtype):
+    """No tokens at all: outputs and input gradient are empty, weight gradients are exact zeros.  One token (the case
+    the reference's own module test uses): matches the eager module."""
+    torch.manual_seed(1)
+    m = kh.MoE_Triton(8, 2, 256, 512, kh.swiglu_unchunked_torch, True, False, 0.02).cuda().to(dtype)
+    x0 = torch.zeros(0, 256, device="cuda", dtype=dtype, requires_grad=True)
+    y0, logits0 = m(x0)
+    assert y0.shape == (0, 256) and logits0.shape == (0, 8)
+    y0.sum().backward()
+    assert x0.grad.shape == (0, 256)
+    assert (m.c_fc.weight.grad == 0).all() and (m.c_proj.weight.grad == 0).all()
+    m.zero_grad()
+    t = kh.MoE_Torch(8, 2, 256, 512, kh.swiglu_unchunked_torch, True, False, 0.02).cuda().to(dtype)
+    t.load_state_dict(m.state_dict())
+    x1 = torch.randn(256, device="cuda", dtype=dtype)
+    outs = []
+    for layer in (t, m):
+        xr = x1.clone().requires_grad_(True)
+        y, _ = layer(xr)
+        y.sum().backward()
+        outs.append((y.detach(), xr.grad))
+    tol = 1e-5 if dtype == torch.float32 else 1.5e-2
+    assert rel_l2(outs[1][0], outs[0][0]) < tol and rel_l2(outs[1][1], outs[0][1]) < tol
+    _lib.check_status(torch.device("cuda"))
