@@ -396,6 +396,40 @@ def run_gpu_arm(args, w):
         dist.destroy_process_group()
 
 
+def run_micro():
+    """Row-kernel timings at the reference's own benchmark sizes (CUDA events): the SwiGLU operator on x = (81920, 8192),
+    the histogram and the routing sort on 1M ids.  Prints one JSON line; not the benchmark metric."""
+    import kernel_hyperdrive_b200 as kh
+    from kernel_hyperdrive_b200.ops import _swiglu_backward, _swiglu_forward
+
+    def timed(fn, iters=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        s_, e_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s_.record()
+        for _ in range(iters):
+            fn()
+        e_.record()
+        torch.cuda.synchronize()
+        return s_.elapsed_time(e_) / iters
+
+    out = {"impl": "micro"}
+    n = 81920 * 4096
+    for name, dt in (("bf16", torch.bfloat16), ("fp32", torch.float32)):
+        x = torch.randn(81920, 8192, device="cuda", dtype=dt)
+        y = torch.empty(81920, 4096, device="cuda", dtype=dt)
+        dy, dx = torch.randn_like(y), torch.empty_like(x)
+        f, b = timed(lambda: _swiglu_forward(x, y)), timed(lambda: _swiglu_backward(x, dy, dx))
+        out[f"swiglu_unchunked_forward_{name}"] = {"ms": f, "GB/s": 3 * n * x.element_size() / f / 1e6}
+        out[f"swiglu_unchunked_backward_{name}"] = {"ms": b, "GB/s": 5 * n * x.element_size() / b / 1e6}
+        del x, y, dy, dx
+    ids = torch.randint(0, 256, (1 << 20,), device="cuda")
+    out["contiguous_count_1M_ids_256_bins"] = {"us": timed(lambda: kh.contiguous_count_cute(ids, 256)) * 1e3}
+    out["route_1M_ids_256_experts"] = {"us": timed(lambda: kh.route(ids, 256, 8, True, True)) * 1e3}
+    print(json.dumps(out), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -407,6 +441,7 @@ def main():
     ap.add_argument("--cpu-sample-tokens", type=int, default=256)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ep-exchange", default="p2p", choices=["p2p", "nccl"], help="N > 1: row exchange by this package's kernels over peer memory, or NCCL all-to-all")
+    ap.add_argument("--micro", action="store_true", help="time the row kernels (SwiGLU operator, histogram, routing sort) instead of the layer")
     ap.add_argument("--profile", action="store_true", help="profiling run under ncu: exactly --warmup warm-up steps, no end-to-end and CPU legs; its numbers are not benchmark values")
     args = ap.parse_args()
     w = synthetic.WORKLOADS[args.workload]
@@ -414,7 +449,9 @@ def main():
         w = synthetic.scaled(w, tokens=args.tokens)
     elif w.name == "c5":
         w = synthetic.scaled(w, tokens=w.tokens // 8)  # the configuration is stated for 8 GPUs: 131072 tokens over 8 ranks
-    if args.impl == "reference":
+    if args.micro:
+        run_micro()
+    elif args.impl == "reference":
         run_reference_arm(args, w)
     else:
         run_gpu_arm(args, w)
