@@ -13,3 +13,4 @@ from .scattermoe import (
     route,
     scattered_experts,
 )
+from .inject import GraphInjector, adopt_moe, replace_swiglu_unchunked, swap_moe_modules
