@@ -424,6 +424,20 @@ def run_micro():
         out[f"swiglu_unchunked_forward_{name}"] = {"ms": f, "GB/s": 3 * n * x.element_size() / f / 1e6}
         out[f"swiglu_unchunked_backward_{name}"] = {"ms": b, "GB/s": 5 * n * x.element_size() / b / 1e6}
         del x, y, dy, dx
+    # router: one fused launch against the eager gate GEMM + top-k + softmax + casts (+ histogram)
+    for name, (T, H, E, k) in (("c2_T16384_H4096_E8_k2", (16384, 4096, 8, 2)), ("c5_per_gpu_T16384_H7168_E256_k8", (16384, 7168, 256, 8))):
+        x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+        wg = (torch.randn(E, H, device="cuda") * 0.02).to(torch.bfloat16)
+
+        def eager():
+            logits = torch.nn.functional.linear(x, wg)
+            vals, idx = logits.topk(k, dim=-1)
+            return torch.softmax(vals.float(), dim=-1).type_as(x), idx, idx.flatten().bincount(minlength=E)
+
+        f, e_ = timed(lambda: kh.router_forward(x, wg, k, 0)), timed(eager)
+        nbytes = (T * H + E * H + T * E + T * k) * 2 + T * k * 8
+        out[f"router_{name}"] = {"fused_us": f * 1e3, "eager_us": e_ * 1e3, "fused_GB/s": nbytes / f / 1e6, "fused_TFLOP/s": 2 * T * H * E / f / 1e9}
+        del x, wg
     ids = torch.randint(0, 256, (1 << 20,), device="cuda")
     out["contiguous_count_1M_ids_256_bins"] = {"us": timed(lambda: kh.contiguous_count_cute(ids, 256)) * 1e3}
     out["route_1M_ids_256_experts"] = {"us": timed(lambda: kh.route(ids, 256, 8, True, True)) * 1e3}

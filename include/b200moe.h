@@ -267,6 +267,21 @@ int b200moe_ep_pull_combine(const void* const* peer_ptrs, const int64_t* inv, co
                             const int32_t* base, int R, const void* gates, void* out, int64_t ldo, void* expanded,
                             int64_t T, int k, int width, int dtype, b200moe_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * Fused router (the step before the path): replaces `_compute_routing_weights` + `_get_topk`
+ * (cute_kernels/kernels/scattermoe/torch_implementation.py:120-133,193-199) and the histogram of the selected experts
+ * (cute_kernels/kernels/contiguous_count/__init__.py:8-24) for 16-bit tensors.
+ *   logits (T, E)  = x (T, H) @ gate_w (E, H)^T, fp32 accumulation on the tensor cores, rounded to the tensor type
+ *   indices (T, k) = the k largest logits of each row, descending; equal logits: lower expert first (int64)
+ *   weights (T, k) = scoring 0: softmax over the k selected logits; scoring 1: their sigmoids divided by their sum;
+ *                    computed in fp32 from the rounded logits, stored in the tensor type
+ *   counts (E)     = number of (token, slot) pairs per expert (int32; zeroed by the call)
+ * Limits: E <= 256, k <= 8, bf16 / fp16.  One launch (plus the memset of counts).
+ * ------------------------------------------------------------------------------------------------ */
+int b200moe_router_forward(const void* x, int64_t ldx, const void* gate_w, int64_t ldw, int64_t T, int H, int E, int k,
+                           int scoring, void* logits, int64_t ldl, void* weights, int64_t* indices, int32_t* counts,
+                           int dtype, int32_t* status, b200moe_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -14,3 +14,4 @@ from .scattermoe import (
     scattered_experts,
 )
 from .inject import GraphInjector, adopt_moe, replace_swiglu_unchunked, swap_moe_modules
+from .router import fused_router, router_forward

@@ -396,3 +396,26 @@ extern "C" int b200moe_up_dgrad(const void* dh, const void* w_fc, const int64_t*
     g.epi = EPI_STORE;
     return run_row_gemm(g, dtype, status, stream, "up_dgrad");
 }
+
+// ---- fused router ---------------------------------------------------------------------------------
+
+extern "C" int b200moe_router_forward(const void* x, int64_t ldx, const void* gate_w, int64_t ldw, int64_t T, int H, int E,
+                                      int k, int scoring, void* logits, int64_t ldl, void* weights, int64_t* indices,
+                                      int32_t* counts, int dtype, int32_t* status, b200moe_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    B200MOE_REQUIRE(dtype == B200MOE_BF16 || dtype == B200MOE_F16, B200MOE_ERR_DTYPE,
+                    "router_forward: 16-bit tensors only (dtype %d); route fp32 tensors with the eager router", dtype);
+    B200MOE_REQUIRE(T >= 0 && T < ((int64_t)1 << 31) && H > 0 && E > 0, B200MOE_ERR_ARG, "router_forward: bad sizes");
+    B200MOE_REQUIRE(E <= 256 && k >= 1 && k <= 8 && k <= E, B200MOE_ERR_UNSUPPORTED,
+                    "router_forward: at most 256 experts and 8 experts per token (E=%d k=%d)", E, k);
+    B200MOE_REQUIRE(scoring == 0 || scoring == 1, B200MOE_ERR_ARG, "router_forward: scoring must be 0 (softmax) or 1 (sigmoid)");
+    B200MOE_REQUIRE(counts != nullptr, B200MOE_ERR_ARG, "router_forward: NULL pointer");
+    cudaError_t err = cudaMemsetAsync(counts, 0, sizeof(int32_t) * E, stream);
+    B200MOE_REQUIRE(err == cudaSuccess, B200MOE_ERR_LAUNCH, "router_forward: memset: %s", cudaGetErrorString(err));
+    if (T == 0) return B200MOE_OK;
+    B200MOE_REQUIRE(x && gate_w && logits && weights && indices, B200MOE_ERR_ARG, "router_forward: NULL pointer");
+    B200MOE_REQUIRE(H % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && ldx >= H && ldw >= H && ldl >= E &&
+                        ((uintptr_t)x & 15) == 0 && ((uintptr_t)gate_w & 15) == 0,
+                    B200MOE_ERR_LAYOUT, "router_forward: rows of x and of the gate weight must be 16-byte aligned multiples of 16 bytes");
+    return umma_router(x, ldx, gate_w, ldw, T, H, E, k, scoring, logits, ldl, weights, indices, counts, dtype, status, stream);
+}

@@ -14,6 +14,7 @@ constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KB
 constexpr int EPI_WARPS = 8;  // two warps per TMEM lane quarter, each takes half the columns
 constexpr int STG_BYTES = 32 * 32 * 2;  // epilogue staging: 32 rows x 32 columns of 16-bit elements, 64-byte swizzle
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
+constexpr int ROUTER_KMAX = 8;  // most experts per token the fused router selects
 
 struct UmmaParams {
     int wfam;    // 0: family R (row tiles), 1: family W (per-expert weight gradient)
@@ -53,6 +54,11 @@ struct UmmaParams {
     int is_f16;
     int full_count;  // arrivals per full barrier
     int o3d;         // output tensor map is 3-D (expert, row, column): weight gradients
+    // router (EPI_ROUTER, one-CTA kernel): one group of `rows_fixed` rows (offsets == nullptr), N = number of experts
+    int64_t rows_fixed;
+    int r_k, r_scoring, r_vec;  // experts per token; 0 softmax / 1 normalised sigmoid; logits rows allow 16-byte stores
+    int64_t* r_indices;         // (rows, k) selected experts
+    int32_t* r_counts;          // (N) rows per expert, accumulated with atomics
 };
 
 // ---- PTX wrappers --------------------------------------------------------------------------------
@@ -347,6 +353,99 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
             stage_store(mo3, n0 + c, row_c, 0, hg);   // gate half of h (its own map: columns clip at I)
             stage_store(mo2, n0 + c, row_c, 0, av);   // activation
         }
+    } else if (EPI == EPI_ROUTER) {
+        // Router: the tile's columns are the experts.  One thread owns one token row: it rounds the logits to the
+        // tensor type and stores them, keeps the ROUTER_KMAX largest (ties: lower expert first) in registers, turns
+        // the first k into routing weights and counts the selected experts.  Only the first warp of each lane
+        // quarter works; a row is never split between threads.
+        if (half == 0) {
+            const int E = p.N, k = p.r_k;
+            const bool row_ok = r < ti.rows_valid;
+            const int64_t row = ti.row0 + r;
+            float tv[ROUTER_KMAX];
+            int tix[ROUTER_KMAX];
+#pragma unroll
+            for (int j = 0; j < ROUTER_KMAX; ++j) {
+                tv[j] = -INFINITY;
+                tix[j] = 0;
+            }
+            uint8_t* lrow = (uint8_t*)p.out + row * p.ldo * 2;
+#pragma unroll 1
+            for (int c = 0; c < E; c += 32) {
+                uint32_t v[32];
+                tc_ld32(taddr + c, v);
+                tc_wait_ld();
+                float f[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) f[i] = round_elem(__uint_as_float(v[i]), is_f16);
+                if (row_ok) {
+                    if (p.r_vec) {
+#pragma unroll
+                        for (int qd = 0; qd < 4; ++qd) {
+                            if (c + qd * 8 < E) {
+                                uint4 o;
+                                o.x = pack2(f[qd * 8 + 0], f[qd * 8 + 1], is_f16);
+                                o.y = pack2(f[qd * 8 + 2], f[qd * 8 + 3], is_f16);
+                                o.z = pack2(f[qd * 8 + 4], f[qd * 8 + 5], is_f16);
+                                o.w = pack2(f[qd * 8 + 6], f[qd * 8 + 7], is_f16);
+                                *reinterpret_cast<uint4*>(lrow + (c + qd * 8) * 2) = o;
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            if (c + i < E) {
+                                uint32_t pk = pack2(f[i], 0.f, is_f16);
+                                *reinterpret_cast<uint16_t*>(lrow + (c + i) * 2) = (uint16_t)(pk & 0xFFFFu);
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float val = f[i];
+                    if (c + i < E && val > tv[ROUTER_KMAX - 1]) {
+                        tv[ROUTER_KMAX - 1] = val;
+                        tix[ROUTER_KMAX - 1] = c + i;
+#pragma unroll
+                        for (int j = ROUTER_KMAX - 1; j > 0; --j) {
+                            if (tv[j] > tv[j - 1]) {
+                                float a = tv[j];
+                                tv[j] = tv[j - 1];
+                                tv[j - 1] = a;
+                                int b = tix[j];
+                                tix[j] = tix[j - 1];
+                                tix[j - 1] = b;
+                            }
+                        }
+                    }
+                }
+            }
+            // scores of the first k (fp32), as the eager router computes them from the rounded logits
+            float sc[ROUTER_KMAX], sum = 0.f;
+#pragma unroll
+            for (int j = 0; j < ROUTER_KMAX; ++j) {
+                float s = 0.f;
+                if (j < k) s = p.r_scoring ? 1.f / (1.f + expf(-tv[j])) : expf(tv[j] - tv[0]);
+                sc[j] = s;
+                sum += s;
+            }
+            const float inv = 1.f / sum;
+#pragma unroll
+            for (int j = 0; j < ROUTER_KMAX; ++j) {
+                if (j < k) {
+                    if (row_ok) {
+                        p.r_indices[row * k + j] = tix[j];
+                        uint32_t pk = pack2(sc[j] * inv, 0.f, is_f16);
+                        reinterpret_cast<uint16_t*>(p.out2)[row * k + j] = (uint16_t)(pk & 0xFFFFu);
+                    }
+                    // rows per expert: one atomic per distinct expert among the warp's rows
+                    const int key = row_ok ? tix[j] : -1;
+                    const unsigned same = __match_any_sync(0xFFFFFFFFu, key);
+                    if (key >= 0 && lane == (__ffs(same) - 1)) atomicAdd(p.r_counts + key, __popc(same));
+                }
+            }
+        }
     } else {  // EPI_DGRAD_DOWN
         const int I = p.N;
         const int64_t prow = ti.row0 + r;
@@ -402,7 +501,7 @@ int make_store_map(CUtensorMap* map, const void* base, int64_t experts, int64_t 
 int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows, int is_f16);
 int make_gather_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int is_f16);
 int sm_count();
-uint32_t make_idesc(int a_mn, int b_mn, int is_f16, int m);
+uint32_t make_idesc(int a_mn, int b_mn, int is_f16, int m, int n = BN);
 
 // two-CTA kernels (umma2_gemm.cu); operands must all be TMA tiles
 int launch_2cta(int epi, const UmmaParams& p, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo,

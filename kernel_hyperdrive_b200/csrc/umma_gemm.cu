@@ -98,9 +98,9 @@ int sm_count() {
 }
 
 
-uint32_t make_idesc(int a_mn, int b_mn, int is_f16, int m) {
+uint32_t make_idesc(int a_mn, int b_mn, int is_f16, int m, int n) {
     uint32_t fmt = is_f16 ? 0u : 1u;
-    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) | ((uint32_t)(BN >> 3) << 17) |
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) |
            ((uint32_t)(m >> 4) << 24);
 }
 
@@ -161,8 +161,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 
     // segment tables
     for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
-        int64_t prev = e ? p.offsets[e - 1] : 0;
-        tb.seg_cnt[e] = (int)(p.offsets[e] - prev);
+        if (p.offsets == nullptr) {  // one group of a size known to the host (router)
+            tb.seg_cnt[e] = (int)p.rows_fixed;
+        } else {
+            int64_t prev = e ? p.offsets[e - 1] : 0;
+            tb.seg_cnt[e] = (int)(p.offsets[e] - prev);
+        }
     }
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -203,7 +207,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0 && (p.a_tma || p.b_tma)) {
-            const uint32_t tx_bytes = (p.a_tma ? A_STAGE_BYTES : 0) + (p.b_tma ? B_STAGE_BYTES : 0);
+            // the router's weight matrix has at most 256 rows: one 128-row box when they fit, else two
+            const uint32_t b_bytes = (EPI == EPI_ROUTER && p.N <= 128) ? B_STAGE_BYTES / 2 : B_STAGE_BYTES;
+            const uint32_t tx_bytes = (p.a_tma ? A_STAGE_BYTES : 0) + (p.b_tma ? b_bytes : 0);
             int stage = 0;
             uint32_t phase = 0;
             Tile ti;
@@ -248,7 +254,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                                     r1 = r0 + 128;
                                 }
                                 tma_load_2d(sb, &tmap_b, bar, k0, r0);  // box 64 x 128
-                                tma_load_2d(sb + 16384, &tmap_b, bar, k0, r1);
+                                if (EPI != EPI_ROUTER || p.N > 128) tma_load_2d(sb + 16384, &tmap_b, bar, k0, r1);
                             }
                         }
                     }
@@ -640,6 +646,46 @@ int umma_row_gemm(const RowGemm& g, int dtype, int32_t* status, cudaStream_t str
         if (rc) return rc;
     }
     return launch_any<EPI_STORE>(p, ma, mb, mo, mo2, mo3, stream);
+}
+
+// Fused router: logits = x @ gate_wT on the tensor cores (one group of T rows, the experts are the tile's columns),
+// top-k, scores and the per-expert counts in the epilogue.
+int umma_router(const void* x, int64_t ldx, const void* gate_w, int64_t ldw, int64_t T, int H, int E, int k, int scoring,
+                void* logits, int64_t ldl, void* weights, int64_t* indices, int32_t* counts, int dtype, int32_t* status,
+                cudaStream_t stream) {
+    UmmaParams p{};
+    p.wfam = 0;
+    p.E = 1;
+    p.padded = 0;
+    p.offsets = nullptr;
+    p.rows_fixed = T;
+    p.K = H;
+    p.N = E;
+    p.nb_count = 1;
+    p.is_f16 = dtype == B200MOE_F16;
+    p.a_tma = p.b_tma = 1;
+    p.a_ptr = x;
+    p.a_ld = ldx;
+    p.b_ptr = gate_w;
+    p.b_rows_per_expert = E;
+    p.out = logits;
+    p.ldo = ldl;
+    p.out2 = weights;
+    p.r_indices = indices;
+    p.r_counts = counts;
+    p.r_k = k;
+    p.r_scoring = scoring;
+    p.r_vec = E % 8 == 0 && ldl % 8 == 0 && aligned16(logits);
+    p.status = status;
+    const int n_mma = E <= 16 ? 16 : (E + 15) / 16 * 16;
+    p.idesc = make_idesc(0, 0, p.is_f16, BM, n_mma);
+    p.full_count = 1;
+    CUtensorMap ma{}, mb{};
+    int rc = make_map(&ma, x, T, H, ldx, 128, p.is_f16);
+    if (rc) return rc;
+    rc = make_map(&mb, gate_w, E, H, ldw, 128, p.is_f16);  // rows past E read as zeros
+    if (rc) return rc;
+    return launch<EPI_ROUTER>(p, ma, mb, mb, mb, mb, stream);
 }
 
 int umma_w_gemm(const WGemm& g, int dtype, int32_t* status, cudaStream_t stream) {

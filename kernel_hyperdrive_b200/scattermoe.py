@@ -25,6 +25,7 @@ import torch.nn.functional as F
 from . import _lib
 from ._lib import check, dtype_code, lib, ptr, status_word, stream_ptr
 from .custom_op import b200_op
+from .router import fused_router, fused_router_supported
 from .ops import _workspace, combine, contiguous_count_cute, group, group_bwd_W, scatter2scatter, swiglu_unchunked_cute, swiglu_unchunked_torch
 
 # --------------------------------------------------------------------------------------------------
@@ -454,9 +455,21 @@ def is_swiglu_callable(fn) -> bool:
 
 
 class MoE_B200(MoE_Torch):
-    """MoE layer on the sm_100a kernels.  Same constructor, parameters and `state_dict` keys as `MoE_Torch`."""
+    """MoE layer on the sm_100a kernels.  Same constructor, parameters and `state_dict` keys as `MoE_Torch`.
+
+    `fused_router` (attribute, default False): route 16-bit tensors with the one-launch router kernel instead of the
+    eager gate / top-k / softmax sequence.  Off by default so that the selected experts are those of the eager router
+    bit for bit (see `router.py` for where the two can differ).
+    """
 
     experts_cls = Experts_B200
+    fused_router = False
+
+    def _compute_routing_weights(self, hidden_states: torch.Tensor):
+        if self.fused_router and self.gate.weight.dtype == hidden_states.dtype and fused_router_supported(hidden_states, self.num_experts, self.top_k):
+            logits, weights, selected_experts, _ = fused_router(hidden_states, self.gate.weight, self.top_k, self.router_scoring)
+            return logits, weights, selected_experts
+        return super()._compute_routing_weights(hidden_states)
 
     def _compute_experts(self, hidden_states: torch.Tensor, router_weights: torch.Tensor, selected_experts: torch.Tensor) -> torch.Tensor:
         if self.is_glu and is_swiglu_callable(self.act):
