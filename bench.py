@@ -424,6 +424,19 @@ def run_micro():
         out[f"swiglu_unchunked_forward_{name}"] = {"ms": f, "GB/s": 3 * n * x.element_size() / f / 1e6}
         out[f"swiglu_unchunked_backward_{name}"] = {"ms": b, "GB/s": 5 * n * x.element_size() / b / 1e6}
         del x, y, dy, dx
+    # RMSNorm of the layer's input: forward 2 passes over (T, H), backward 3
+    from kernel_hyperdrive_b200.ops import _rmsnorm_backward, _rmsnorm_forward
+
+    for name, (T, H) in (("16384x4096", (16384, 4096)), ("131072x2048", (131072, 2048)), ("65536x7168", (65536, 7168))):
+        x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+        wn = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+        y, dy, dx, dwn = torch.empty_like(x), torch.randn_like(x), torch.empty_like(x), torch.empty_like(wn)
+        rstd = torch.empty(T, device="cuda", dtype=torch.float32)
+        f = timed(lambda: _rmsnorm_forward(x, wn, y, rstd, 1e-5))
+        b = timed(lambda: _rmsnorm_backward(x, wn, dy, rstd, dx, dwn, 1e-5))
+        e_ = timed(lambda: torch.nn.functional.rms_norm(x, (H,), wn, 1e-5))
+        out[f"rmsnorm_bf16_{name}"] = {"forward_ms": f, "forward_GB/s": 2 * T * H * 2 / f / 1e6, "backward_ms": b, "backward_GB/s": 3 * T * H * 2 / b / 1e6, "torch_forward_ms": e_}
+        del x, y, dy, dx
     # router: one fused launch against the eager gate GEMM + top-k + softmax + casts (+ histogram)
     for name, (T, H, E, k) in (("c2_T16384_H4096_E8_k2", (16384, 4096, 8, 2)), ("c5_per_gpu_T16384_H7168_E256_k8", (16384, 7168, 256, 8))):
         x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)

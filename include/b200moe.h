@@ -282,6 +282,25 @@ int b200moe_router_forward(const void* x, int64_t ldx, const void* gate_w, int64
                            int scoring, void* logits, int64_t ldl, void* weights, int64_t* indices, int32_t* counts,
                            int dtype, int32_t* status, b200moe_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * RMSNorm (the normalisation feeding the layer's input in a transformer block): replaces `rmsnorm_cute`
+ * (cute_kernels/kernels/rmsnorm/__init__.py:11-112, forward.py, backward.py and the Triton kernels under
+ * triton_implementation/) whose eager definition is F.rms_norm (torch_implementation.py:5-6).
+ *   y[r, :]  = x[r, :] * rstd[r] * weight,  rstd[r] = 1 / sqrt(mean(x[r, :]^2) + eps);  weight may be NULL
+ *   dx[r, :] = rstd * (dy * weight) - x * rstd^3 * mean((dy * weight) * x);  dweight = sum_r dy * x * rstd
+ * Arithmetic in fp32, tensors bf16 / fp16 / fp32, unit inner stride.  rstd (fp32, one per row) is optional in both
+ * calls: forward stores it when given; backward recomputes it from x when NULL (the reference's memory_efficient
+ * mode).  dweight may be NULL; otherwise `workspace` must hold b200moe_rmsnorm_workspace_bytes(rows, H, dtype) bytes
+ * (fp32 partial sums, added up in a fixed order on the 16-byte aligned path).
+ * ------------------------------------------------------------------------------------------------ */
+int64_t b200moe_rmsnorm_workspace_bytes(int64_t rows, int H, int dtype);
+int b200moe_rmsnorm_forward(const void* x, int64_t ldx, const void* weight, void* y, int64_t ldy, float* rstd,
+                            int64_t rows, int H, float eps, int dtype, b200moe_stream_t stream);
+int b200moe_rmsnorm_backward(const void* x, int64_t ldx, const void* weight, const void* dy, int64_t lddy,
+                             const float* rstd, void* dx, int64_t lddx, void* dweight, void* workspace,
+                             int64_t workspace_bytes, int64_t rows, int H, float eps, int dtype,
+                             b200moe_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -17,7 +17,7 @@ import torch
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libb200moe.so")
-SOURCES = ["api.cu", "routing.cu", "rowops.cu", "simt_gemm.cu", "umma_gemm.cu", "umma2_gemm.cu", "ep.cu"]
+SOURCES = ["api.cu", "routing.cu", "rowops.cu", "simt_gemm.cu", "umma_gemm.cu", "umma2_gemm.cu", "ep.cu", "rmsnorm.cu"]
 HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(PKG_DIR, "..", "include", "b200moe.h")]
 
 F32, BF16, F16 = 0, 1, 2
@@ -59,7 +59,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 def _declare(lib):
     c = ctypes
-    vp, i32, i64 = c.c_void_p, c.c_int, c.c_int64
+    vp, i32, i64, f32 = c.c_void_p, c.c_int, c.c_int64, c.c_float
     sig = {
         "b200moe_version": (i32, []),
         "b200moe_error_string": (c.c_char_p, [i32]),
@@ -90,6 +90,9 @@ def _declare(lib):
         "b200moe_ep_pull_combine": (i32, [vp, vp, vp, vp, i32, vp, vp, i64, vp, i64, i32, i32, i32, vp]),
         "b200moe_up_dgrad": (i32, [vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, i64, i32, vp, vp]),
         "b200moe_router_forward": (i32, [vp, i64, vp, i64, i64, i32, i32, i32, i32, vp, i64, vp, vp, vp, i32, vp, vp]),
+        "b200moe_rmsnorm_workspace_bytes": (i64, [i64, i32, i32]),
+        "b200moe_rmsnorm_forward": (i32, [vp, i64, vp, vp, i64, vp, i64, i32, f32, i32, vp]),
+        "b200moe_rmsnorm_backward": (i32, [vp, i64, vp, vp, i64, vp, vp, i64, vp, vp, i64, i64, i32, f32, i32, vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)  # AttributeError here means the library does not export a declared symbol

@@ -220,3 +220,86 @@ def swiglu_unchunked_cute(x: torch.Tensor, kernel_backend_forward=None, kernel_b
     The tuning keywords of the reference's function are accepted and ignored.
     """
     return _SwigluUnchunked.apply(x)
+
+
+# ---- RMSNorm ---------------------------------------------------------------------------------------
+
+
+def rmsnorm_torch(x: torch.Tensor, weight: torch.Tensor | None, eps: float) -> torch.Tensor:
+    """Eager definition (cute_kernels/kernels/rmsnorm/torch_implementation.py:5-6)."""
+    return torch.nn.functional.rms_norm(x, (x.size(-1),), weight=weight, eps=eps)
+
+
+@b200_op("rmsnorm_forward", mutates_args={"output", "rstd"})
+def _rmsnorm_forward(x: torch.Tensor, weight: torch.Tensor | None, output: torch.Tensor, rstd: torch.Tensor | None, eps: float) -> None:
+    _require_cuda(x, weight, output, rstd)
+    check(
+        lib().b200moe_rmsnorm_forward(ptr(x), x.stride(0), ptr(weight), ptr(output), output.stride(0), ptr(rstd), x.size(0), x.size(1), eps, dtype_code(x), stream_ptr(x.device)),
+        "rmsnorm_forward",
+    )
+
+
+@b200_op("rmsnorm_backward", mutates_args={"x_grad", "weight_grad"})
+def _rmsnorm_backward(x: torch.Tensor, weight: torch.Tensor | None, output_grad: torch.Tensor, rstd: torch.Tensor | None, x_grad: torch.Tensor, weight_grad: torch.Tensor | None, eps: float) -> None:
+    _require_cuda(x, weight, output_grad, rstd, x_grad, weight_grad)
+    ws = None
+    nbytes = 0
+    if weight_grad is not None:
+        nbytes = lib().b200moe_rmsnorm_workspace_bytes(x.size(0), x.size(1), dtype_code(x))
+        ws = _workspace(x.device, nbytes)
+    check(
+        lib().b200moe_rmsnorm_backward(
+            ptr(x), x.stride(0), ptr(weight), ptr(output_grad), output_grad.stride(0), ptr(rstd), ptr(x_grad), x_grad.stride(0), ptr(weight_grad),
+            ptr(ws), nbytes, x.size(0), x.size(1), eps, dtype_code(x), stream_ptr(x.device),
+        ),
+        "rmsnorm_backward",
+    )
+
+
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, weight: torch.Tensor | None, eps: float | None, memory_efficient: bool) -> torch.Tensor:
+        if weight is not None:
+            assert weight.dim() == 1, "weight should be 1D"
+            assert weight.size(-1) == x.size(-1), "hidden size for x and weight tensor is different"
+            assert weight.dtype == x.dtype, "tensors weight and y should have same dtype"
+            weight = weight.contiguous()
+        if eps is None:
+            eps = torch.finfo(x.dtype).eps
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        out = torch.empty(x2.size(0), x2.size(1), dtype=x.dtype, device=x.device)
+        if x2.size(0) == 0:
+            ctx.save_for_backward(x2, weight, None)
+            ctx.shape, ctx.eps = shape, eps
+            return out.view(shape)
+        rstd = None if memory_efficient else torch.empty(x2.size(0), dtype=torch.float32, device=x.device)
+        _rmsnorm_forward(x2, weight, out, rstd, eps)
+        ctx.save_for_backward(x2, weight, rstd)
+        ctx.shape, ctx.eps = shape, eps
+        return out.view(shape)
+
+    @staticmethod
+    def backward(ctx, output_grad: torch.Tensor):
+        x2, weight, rstd = ctx.saved_tensors
+        if x2.size(0) == 0:
+            return x2.new_empty(ctx.shape), (torch.zeros_like(weight) if weight is not None and ctx.needs_input_grad[1] else None), None, None
+        g = output_grad.reshape(x2.shape)
+        if g.stride(-1) != 1:
+            g = g.contiguous()
+        x_grad = torch.empty_like(x2)
+        weight_grad = torch.empty_like(weight) if weight is not None and ctx.needs_input_grad[1] else None
+        _rmsnorm_backward(x2, weight, g, rstd, x_grad, weight_grad, ctx.eps)
+        return x_grad.view(ctx.shape), weight_grad, None, None
+
+
+def rmsnorm_cute(x: torch.Tensor, weight: torch.Tensor | None, eps: float | None, memory_efficient: bool = False, kernel_backend_forward=None, kernel_backend_backward=None,
+                 BLOCK_SIZE_B_forward=None, BLOCK_SIZE_B_backward=None, BLOCK_SIZE_H_forward=None, BLOCK_SIZE_H_backward=None) -> torch.Tensor:
+    """RMSNorm over the last dimension; differentiable in x and weight (cute_kernels/kernels/rmsnorm/__init__.py:88-112).
+
+    `memory_efficient=True` does not keep the per-row inverse RMS for the backward pass (it is recomputed from x).
+    The tuning keywords of the reference's function are accepted and ignored.
+    """
+    return _RMSNorm.apply(x, weight, eps, memory_efficient)

@@ -299,6 +299,31 @@ def sigmoid_routing(logits, top_k, normalise=True):
     return w.type_as(logits), idx
 
 
+def rmsnorm(x, weight, eps):
+    """y = x / sqrt(mean(x^2, last dim) + eps) * weight (weight may be None), in the arithmetic type of x.
+
+    Follows cute_kernels/kernels/rmsnorm/torch_implementation.py:5-6 (F.rms_norm) and the kernel
+    cute_kernels/kernels/rmsnorm/triton_implementation/kernels_forward.py:44-60.
+    """
+    inverse_rms = torch.rsqrt((x * x).mean(dim=-1, keepdim=True) + eps)
+    y = x * inverse_rms
+    return y if weight is None else y * weight
+
+
+def rmsnorm_backward(x, weight, dy, eps):
+    """(dx, dweight) of `rmsnorm`; dweight is None without a weight.
+
+    Follows cute_kernels/kernels/rmsnorm/triton_implementation/kernels_backward.py:64-96:
+    g = dy * weight; dx = r * g - (1/H) * r^3 * x * sum(g * x); dweight = sum over rows of dy * x * r.
+    """
+    H = x.shape[-1]
+    r = torch.rsqrt((x * x).mean(dim=-1, keepdim=True) + eps)
+    g = dy if weight is None else dy * weight
+    dx = r * g - (1.0 / H) * r * r * r * x * (g * x).sum(dim=-1, keepdim=True)
+    dw = None if weight is None else (dy * x * r).reshape(-1, H).sum(dim=0)
+    return dx, dw
+
+
 def rel_l2(a, b) -> float:
     a = torch.as_tensor(a).double().flatten()
     b = torch.as_tensor(b).double().flatten()

@@ -100,6 +100,24 @@ def swiglu_case():
     np.savez_compressed(os.path.join(HERE, "swiglu.npz"), x=x.detach().numpy(), dy=dy.numpy(), y=y.detach().numpy(), dx=x.grad.numpy())
 
 
+def rmsnorm_case():
+    # the reference's eager definition (cute_kernels/kernels/rmsnorm/torch_implementation.py:5-6), eps of its test
+    from cute_kernels.kernels.rmsnorm.torch_implementation import rmsnorm_torch
+
+    rs = np.random.RandomState(13)
+    out = {}
+    for tag, shape, has_weight in (("w", (29, 56), True), ("nw", (5, 3, 40), False), ("odd", (17, 7), True)):
+        x = torch.from_numpy(rs.standard_normal(shape).astype(np.float32)).requires_grad_(True)
+        w = torch.from_numpy(rs.standard_normal(shape[-1]).astype(np.float32)).requires_grad_(True) if has_weight else None
+        dy = torch.from_numpy(rs.standard_normal(shape).astype(np.float32))
+        y = rmsnorm_torch(x, w, 1e-5)
+        y.backward(dy)
+        out.update({f"{tag}_x": x.detach().numpy(), f"{tag}_dy": dy.numpy(), f"{tag}_y": y.detach().numpy(), f"{tag}_dx": x.grad.numpy()})
+        if has_weight:
+            out.update({f"{tag}_w": w.detach().numpy(), f"{tag}_dw": w.grad.numpy()})
+    np.savez_compressed(os.path.join(HERE, "rmsnorm.npz"), **out)
+
+
 if __name__ == "__main__":
     torch.manual_seed(0)
     torch.set_num_threads(8)
@@ -108,3 +126,4 @@ if __name__ == "__main__":
     # uneven loads, an empty expert and k=1 exercise the split/concat bookkeeping of the reference
     run_case("ragged", synthetic.MoEWorkload("ragged", 6, 1, 40, 24, 19, dtype="fp32"), seed=3, store_inputs=True)
     swiglu_case()
+    rmsnorm_case()

@@ -98,3 +98,17 @@ def test_stored_inputs_match_generators():
     x, g = synthetic.make_tokens(w, seed)
     assert np.array_equal(gold["x"], x.numpy()) and np.array_equal(gold["g"], g.numpy())
     assert np.array_equal(gold["w_fc"], wt["w_fc"].numpy()) and np.array_equal(gold["gate"], wt["gate"].numpy())
+
+
+def test_rmsnorm_matches_reference():
+    gold = load("rmsnorm")
+    for tag, has_weight in (("w", True), ("nw", False), ("odd", True)):
+        x, dy = torch.from_numpy(gold[f"{tag}_x"]), torch.from_numpy(gold[f"{tag}_dy"])
+        w = torch.from_numpy(gold[f"{tag}_w"]) if has_weight else None
+        assert orc.rel_l2(orc.rmsnorm(x, w, 1e-5), gold[f"{tag}_y"]) < 1e-6
+        dx, dw = orc.rmsnorm_backward(x, w, dy, 1e-5)
+        assert orc.rel_l2(dx, gold[f"{tag}_dx"]) < 1e-5
+        if has_weight:
+            assert orc.rel_l2(dw, gold[f"{tag}_dw"]) < 1e-5
+        else:
+            assert dw is None
