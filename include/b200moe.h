@@ -197,13 +197,19 @@ int b200moe_swiglu_unchunked_backward(const void* x, int64_t ldx, const void* dy
 int b200moe_gather_rows(const void* src, int64_t lds, const int32_t* row_map, void* out, int64_t ldo, int64_t rows,
                         int width, int dtype, b200moe_stream_t stream);
 
-/* Up projection with the token gather on the input rows and SwiGLU in the epilogue:
- * h[p, :] = x[row_token[p], :] @ w_fc[e(p)]^T  (Mcap, 2I), a[p, :] = h[p, :I] * silu(h[p, I:])  (Mcap, I).
+/* Gated activations the fused expert kernels apply between the two projections: a = h[:, :I] * m(h[:, I:]).
+ * SWIGLU: m = silu (cute_kernels/kernels/swiglu_unchunked/torch_implementation.py:5-7); GLU: m = sigmoid (torch.nn.GLU,
+ * the activation of the reference's MoE test, tests/test_commons.py:86-87). */
+#define B200MOE_ACT_SWIGLU 0
+#define B200MOE_ACT_GLU 1
+
+/* Up projection with the token gather on the input rows and the gated activation in the epilogue:
+ * h[p, :] = x[row_token[p], :] @ w_fc[e(p)]^T  (Mcap, 2I), a[p, :] = h[p, :I] * m(h[p, I:])  (Mcap, I).
  * row_token == NULL: x already holds the padded grouped rows (m_cap rows, see b200moe_gather_rows).
  * Replaces scatter2scatter for c_fc plus the activation call (SMT/__init__.py:83-91). */
 int b200moe_up_forward(const void* x, int64_t ldx, const void* w_fc, const int64_t* expert_offsets,
                        const int32_t* row_token, void* h, void* a, int64_t T, int H, int I, int E,
-                       int64_t m_cap, int dtype, int32_t* status, b200moe_stream_t stream);
+                       int64_t m_cap, int activation, int dtype, int32_t* status, b200moe_stream_t stream);
 
 /* Down projection scattered back to (token, slot) order and scaled by the gate of that slot:
  * y_expanded[s, :] = gates[s] * (a[p, :] @ w_proj[e(p)]^T), s = row_slot[p]; gates NULL means 1.
@@ -214,11 +220,12 @@ int b200moe_down_forward(const void* a, const void* w_proj, const int64_t* exper
                          int64_t M, int H, int I, int E, int64_t m_cap, int dtype, int32_t* status,
                          b200moe_stream_t stream);
 
-/* Input gradient of the down projection fused with the gate scaling, the SwiGLU backward and the gate
- * gradient.  With u[p, :] = grad_out[row_token[p], :] @ w_proj[e(p)] (Mcap, I), act = h[:, :I]*silu(h[:, I:]),
+/* Input gradient of the down projection fused with the gate scaling, the backward of the gated activation
+ * (`activation` as in b200moe_up_forward) and the gate gradient.
+ * With u[p, :] = grad_out[row_token[p], :] @ w_proj[e(p)] (Mcap, I), act = h[:, :I]*m(h[:, I:]),
  * g = gates[row_slot[p]]:
  *   d_gates[row_slot[p]] = <act[p, :], u[p, :]>          (fp32, M entries, overwritten)
- *   dh[p, :] = SwiGLU backward of h[p, :] for upstream g*u[p, :]   (Mcap, 2I)
+ *   dh[p, :] = activation backward of h[p, :] for upstream g*u[p, :]   (Mcap, 2I)
  *   ag[p, :] = g * act[p, :]                                        (Mcap, I)
  * row_token == NULL: grad_out already holds the padded grouped rows (m_cap rows).
  * Replaces, for c_proj: the d_gates bmm, group(coeff=gates), scatter2scatter (SMT/ops.py:204-256) and the
@@ -227,7 +234,7 @@ int b200moe_down_forward(const void* a, const void* w_proj, const int64_t* exper
 int b200moe_down_dgrad(const void* grad_out, int64_t ldg, const void* w_proj, const int64_t* expert_offsets,
                        const int32_t* row_token, const int32_t* row_slot, const void* gates, const void* h,
                        void* dh, void* ag, float* d_gates, int64_t M, int H, int I, int E, int64_t m_cap,
-                       int dtype, int32_t* status, b200moe_stream_t stream);
+                       int activation, int dtype, int32_t* status, b200moe_stream_t stream);
 
 /* Weight gradient of one projection, written in the layout the module stores weights in:
  * DW[e, o, i] = sum over rows p of expert e of P[pmap(p), o] * Q[qmap(p), i], DW (E, n_out, n_in) contiguous.

@@ -82,9 +82,9 @@ def _declare(lib):
         "b200moe_combine": (i32, [vp, i64, vp, vp, i64, i64, i32, i32, i32, vp]),
         "b200moe_swiglu_unchunked_forward": (i32, [vp, i64, vp, i64, i64, i32, i32, vp]),
         "b200moe_swiglu_unchunked_backward": (i32, [vp, i64, vp, i64, vp, i64, i64, i32, i32, vp]),
-        "b200moe_up_forward": (i32, [vp, i64, vp, vp, vp, vp, vp, i64, i32, i32, i32, i64, i32, vp, vp]),
+        "b200moe_up_forward": (i32, [vp, i64, vp, vp, vp, vp, vp, i64, i32, i32, i32, i64, i32, i32, vp, vp]),
         "b200moe_down_forward": (i32, [vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, i64, i32, vp, vp]),
-        "b200moe_down_dgrad": (i32, [vp, i64, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i64, i32, vp, vp]),
+        "b200moe_down_dgrad": (i32, [vp, i64, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i64, i32, i32, vp, vp]),
         "b200moe_wgrad": (i32, [vp, i64, vp, vp, i64, vp, vp, vp, i32, i32, i32, i64, i32, vp, vp]),
         "b200moe_ep_push_rows": (i32, [vp, i64, vp, i32, vp, vp, vp, vp, i32, i64, i32, i64, i32, vp, vp]),
         "b200moe_ep_pull_combine": (i32, [vp, vp, vp, vp, i32, vp, vp, i64, vp, i64, i32, i32, i32, vp]),

@@ -224,9 +224,10 @@ extern "C" int b200moe_group_bwd_W(const void* DY, int64_t lddy, const void* X, 
 
 extern "C" int b200moe_up_forward(const void* x, int64_t ldx, const void* w_fc, const int64_t* expert_offsets,
                                   const int32_t* row_token, void* h, void* a, int64_t T, int H, int I, int E,
-                                  int64_t m_cap, int dtype, int32_t* status, b200moe_stream_t stream_) {
+                                  int64_t m_cap, int activation, int dtype, int32_t* status, b200moe_stream_t stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     REQUIRE_COMMON("up_forward");
+    B200MOE_REQUIRE(activation == B200MOE_ACT_SWIGLU || activation == B200MOE_ACT_GLU, B200MOE_ERR_ARG, "up_forward: activation %d", activation);
     if (m_cap == 0) return B200MOE_OK;
     B200MOE_REQUIRE(x && w_fc && expert_offsets && h && a && T >= 0, B200MOE_ERR_ARG, "up_forward: NULL pointer");
     RowGemm g{};
@@ -248,6 +249,7 @@ extern "C" int b200moe_up_forward(const void* x, int64_t ldx, const void* w_fc, 
     g.N = 2 * I;
     g.E = E;
     g.epi = EPI_SWIGLU;
+    g.act = activation;
     g.out2 = a;
     int eng = pick_engine(g, dtype, umma_row_gemm_supported, "up_forward");
     if (eng < 0) return eng;
@@ -255,7 +257,7 @@ extern "C" int b200moe_up_forward(const void* x, int64_t ldx, const void* w_fc, 
     g.epi = EPI_STORE;
     int rc = simt_row_gemm(g, dtype, stream);
     if (rc) return rc;
-    return launch_swiglu_forward(h, 2 * (int64_t)I, a, I, m_cap, I, dtype, stream);
+    return launch_swiglu_forward(h, 2 * (int64_t)I, a, I, m_cap, I, dtype, stream, activation);
 }
 
 extern "C" int b200moe_down_forward(const void* a, const void* w_proj, const int64_t* expert_offsets,
@@ -292,10 +294,11 @@ extern "C" int b200moe_down_forward(const void* a, const void* w_proj, const int
 extern "C" int b200moe_down_dgrad(const void* grad_out, int64_t ldg, const void* w_proj,
                                   const int64_t* expert_offsets, const int32_t* row_token, const int32_t* row_slot,
                                   const void* gates, const void* h, void* dh, void* ag, float* d_gates, int64_t M,
-                                  int H, int I, int E, int64_t m_cap, int dtype, int32_t* status,
+                                  int H, int I, int E, int64_t m_cap, int activation, int dtype, int32_t* status,
                                   b200moe_stream_t stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     REQUIRE_COMMON("down_dgrad");
+    B200MOE_REQUIRE(activation == B200MOE_ACT_SWIGLU || activation == B200MOE_ACT_GLU, B200MOE_ERR_ARG, "down_dgrad: activation %d", activation);
     if (m_cap == 0 || M == 0) return B200MOE_OK;
     B200MOE_REQUIRE(grad_out && w_proj && expert_offsets && row_slot && h && dh && ag && d_gates, B200MOE_ERR_ARG,
                     "down_dgrad: NULL pointer");
@@ -318,6 +321,7 @@ extern "C" int b200moe_down_dgrad(const void* grad_out, int64_t ldg, const void*
     g.N = I;
     g.E = E;
     g.epi = EPI_DGRAD_DOWN;
+    g.act = activation;
     g.out2 = ag;
     g.h = h;
     g.d_gates = d_gates;
@@ -337,7 +341,7 @@ extern "C" int b200moe_down_dgrad(const void* grad_out, int64_t ldg, const void*
     g.scale = nullptr;
     int rc = simt_row_gemm(g, dtype, stream);
     if (rc) return rc;
-    return launch_dgrad_down_post(h, dh, ag, row_slot, gates, d_gates, m_cap, I, dtype, stream);
+    return launch_dgrad_down_post(h, dh, ag, row_slot, gates, d_gates, m_cap, I, dtype, stream, activation);
 }
 
 extern "C" int b200moe_wgrad(const void* P, int64_t ldp, const int32_t* p_map, const void* Q, int64_t ldq,

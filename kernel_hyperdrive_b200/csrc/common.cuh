@@ -69,6 +69,14 @@ __device__ __forceinline__ float sigmoid_for<float>(float x) {
     return sigmoidf_stable(x);
 }
 
+// Gated activations of the fused expert path: a = up * m(gate).  ACT_SILU: m(g) = g * sigmoid(g) (SwiGLU);
+// ACT_SIGMOID: m(g) = sigmoid(g) (GLU).  `sg` is sigmoid(g).
+enum { ACT_SILU = 0, ACT_SIGMOID = 1 };
+__device__ __forceinline__ float gate_value(int act, float g, float sg) { return act == ACT_SIGMOID ? sg : g * sg; }
+__device__ __forceinline__ float gate_slope(int act, float g, float sg) {
+    return act == ACT_SIGMOID ? sg * (1.f - sg) : sg + g * sg * (1.f - sg);
+}
+
 // ---- segment layout -----------------------------------------------------------------------------
 // Both problem descriptions address rows through a "segment layout": expert e owns layout rows
 // [seg_start(e), seg_start(e) + count(e)), where count comes from the inclusive int64 offsets and
@@ -92,6 +100,7 @@ struct RowGemm {
     int K, N, E;
     // fused epilogues (tcgen05 engine only)
     int epi;               // 0 store, 1 SwiGLU forward, 2 down-projection dgrad
+    int act;               // gated activation of epilogues 1 and 2 (ACT_SILU, ACT_SIGMOID)
     void* out2;            // SwiGLU: activation output a (rows_cap, N/2); dgrad: ag (rows_cap, N)
     const void* h;         // dgrad: pre-activation (rows_cap, 2N)
     float* d_gates;        // dgrad: fp32 (M) accumulated with atomics, indexed by o_map
@@ -130,11 +139,11 @@ int umma_router(const void* x, int64_t ldx, const void* gate_w, int64_t ldw, int
 
 // row-wise kernels used by the API layer
 int launch_swiglu_forward(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t rows, int h, int dtype,
-                          cudaStream_t stream);
+                          cudaStream_t stream, int act = ACT_SILU);
 int launch_swiglu_backward(const void* x, int64_t ldx, const void* dy, int64_t lddy, void* dx, int64_t lddx,
                            int64_t rows, int h, int dtype, cudaStream_t stream);
 int launch_dgrad_down_post(const void* h, void* dh, void* ag, const int32_t* row_slot, const void* gates,
-                           float* d_gates, int64_t rows, int I, int dtype, cudaStream_t stream);
+                           float* d_gates, int64_t rows, int I, int dtype, cudaStream_t stream, int act = ACT_SILU);
 
 int current_engine();
 

@@ -87,7 +87,7 @@ __global__ void combine_kernel(const T* __restrict__ in, int64_t ldi, const T* _
 // ---- SwiGLU --------------------------------------------------------------------------------------
 template <typename T, int V>
 __global__ void swiglu_fwd_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__ y, int64_t ldy,
-                                  int64_t rows, int h) {
+                                  int64_t rows, int h, int act) {
     int64_t r = blockIdx.x;
     if (r >= rows) return;
     for (int col = threadIdx.x * V; col < h; col += blockDim.x * V) {
@@ -97,7 +97,7 @@ __global__ void swiglu_fwd_kernel(const T* __restrict__ x, int64_t ldx, T* __res
 #pragma unroll
         for (int i = 0; i < V; ++i) {
             float g = Elem<T>::to_f(gt.v[i]);
-            o.v[i] = Elem<T>::from_f(Elem<T>::to_f(up.v[i]) * g * sigmoid_for<T>(g));
+            o.v[i] = Elem<T>::from_f(Elem<T>::to_f(up.v[i]) * gate_value(act, g, sigmoid_for<T>(g)));
         }
         *reinterpret_cast<Pack<T, V>*>(y + r * ldy + col) = o;
     }
@@ -130,7 +130,7 @@ __global__ void swiglu_bwd_kernel(const T* __restrict__ x, int64_t ldx, const T*
 template <typename T>
 __global__ void dgrad_down_post_kernel(const T* __restrict__ h, T* __restrict__ dh, T* __restrict__ ag,
                                        const int32_t* __restrict__ row_slot, const T* __restrict__ gates,
-                                       float* __restrict__ d_gates, int64_t rows, int I) {
+                                       float* __restrict__ d_gates, int64_t rows, int I, int act_kind) {
     int64_t p = blockIdx.x;
     if (p >= rows) return;
     int slot = row_slot[p];
@@ -151,11 +151,11 @@ __global__ void dgrad_down_post_kernel(const T* __restrict__ h, T* __restrict__ 
         float up = Elem<T>::to_f(h_row[c]), gt = Elem<T>::to_f(h_row[I + c]);
         float u = Elem<T>::to_f(ag_row[c]);
         float sg = sigmoid_for<T>(gt);
-        float act = Elem<T>::to_f(Elem<T>::from_f(up * gt * sg));  // the forward stores it in T
+        float act = Elem<T>::to_f(Elem<T>::from_f(up * gate_value(act_kind, gt, sg)));  // the forward stores it in T
         dot += act * u;
         float da = Elem<T>::to_f(Elem<T>::from_f(g * u));
-        dh_row[c] = Elem<T>::from_f(da * gt * sg);
-        dh_row[I + c] = Elem<T>::from_f(da * up * (sg + gt * sg * (1.f - sg)));
+        dh_row[c] = Elem<T>::from_f(da * gate_value(act_kind, gt, sg));
+        dh_row[I + c] = Elem<T>::from_f(da * up * gate_slope(act_kind, gt, sg));
         ag_row[c] = Elem<T>::from_f(g * act);
     }
     __shared__ float red[32];
@@ -192,16 +192,16 @@ static inline int row_threads(int width, int vec) {
 }  // namespace
 
 int launch_swiglu_forward(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t rows, int h, int dtype,
-                          cudaStream_t stream) {
+                          cudaStream_t stream, int act) {
     if (rows == 0 || h == 0) return B200MOE_OK;
     return dispatch_dtype(dtype, [&](auto tag) {
         using T = decltype(tag);
         constexpr int V = vec_elems<T>();
         bool vec = h % V == 0 && ldx % V == 0 && ldy % V == 0 && aligned16(x) && aligned16(y);
         if (vec) {
-            swiglu_fwd_kernel<T, V><<<(unsigned)rows, row_threads(h, V), 0, stream>>>((const T*)x, ldx, (T*)y, ldy, rows, h);
+            swiglu_fwd_kernel<T, V><<<(unsigned)rows, row_threads(h, V), 0, stream>>>((const T*)x, ldx, (T*)y, ldy, rows, h, act);
         } else {
-            swiglu_fwd_kernel<T, 1><<<(unsigned)rows, row_threads(h, 1), 0, stream>>>((const T*)x, ldx, (T*)y, ldy, rows, h);
+            swiglu_fwd_kernel<T, 1><<<(unsigned)rows, row_threads(h, 1), 0, stream>>>((const T*)x, ldx, (T*)y, ldy, rows, h, act);
         }
         count_launch();
         return check_launch("swiglu_forward");
@@ -229,12 +229,12 @@ int launch_swiglu_backward(const void* x, int64_t ldx, const void* dy, int64_t l
 }
 
 int launch_dgrad_down_post(const void* h, void* dh, void* ag, const int32_t* row_slot, const void* gates,
-                           float* d_gates, int64_t rows, int I, int dtype, cudaStream_t stream) {
+                           float* d_gates, int64_t rows, int I, int dtype, cudaStream_t stream, int act) {
     if (rows == 0) return B200MOE_OK;
     return dispatch_dtype(dtype, [&](auto tag) {
         using T = decltype(tag);
         dgrad_down_post_kernel<T><<<(unsigned)rows, 256, 0, stream>>>((const T*)h, (T*)dh, (T*)ag, row_slot,
-                                                                     (const T*)gates, d_gates, rows, I);
+                                                                     (const T*)gates, d_gates, rows, I, act);
         count_launch();
         return check_launch("dgrad_down_post");
     });

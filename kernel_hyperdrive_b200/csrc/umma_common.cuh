@@ -26,6 +26,7 @@ struct UmmaParams {
     int nb_count;   // column blocks
     int mb_count;   // W: row blocks
     int swiglu_half;  // EPI_SWIGLU: I (columns of one half); tiles cover 128 columns of each half
+    int act;          // EPI_SWIGLU / EPI_DGRAD_DOWN: ACT_SILU or ACT_SIGMOID
     // operand A (R: activations; W: P)
     int a_tma, a_mn;
     int a_g4, a_oob;  // two-CTA kernel: rows of A come through TMA row gather by a_map; a_oob = index that reads as zeros
@@ -347,7 +348,7 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
                 hg[i] = pack2(__uint_as_float(gt[2 * i]), __uint_as_float(gt[2 * i + 1]), is_f16);
                 // the activation sees the values as stored (rounded to the tensor type)
                 float2 fu = unpack2(hu[i], is_f16), fg = unpack2(hg[i], is_f16);
-                av[i] = pack2(fu.x * fg.x * sigmoid_fast(fg.x), fu.y * fg.y * sigmoid_fast(fg.y), is_f16);
+                av[i] = pack2(fu.x * gate_value(p.act, fg.x, sigmoid_fast(fg.x)), fu.y * gate_value(p.act, fg.y, sigmoid_fast(fg.y)), is_f16);
             }
             stage_store(mo, n0 + c, row_c, 0, hu);    // up half of h
             stage_store(mo3, n0 + c, row_c, 0, hg);   // gate half of h (its own map: columns clip at I)
@@ -479,11 +480,12 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
                     float2 up = unpack2(hua[i], is_f16), gt = unpack2(hga[i], is_f16);
                     float u0 = __uint_as_float(u[qd * 8 + 2 * i]), u1 = __uint_as_float(u[qd * 8 + 2 * i + 1]);
                     float s0 = sigmoid_fast(gt.x), s1 = sigmoid_fast(gt.y);
-                    float a0 = round_elem(up.x * gt.x * s0, is_f16), a1 = round_elem(up.y * gt.y * s1, is_f16);
+                    float m0 = gate_value(p.act, gt.x, s0), m1 = gate_value(p.act, gt.y, s1);
+                    float a0 = round_elem(up.x * m0, is_f16), a1 = round_elem(up.y * m1, is_f16);
                     dot += a0 * u0 + a1 * u1;
                     float d0 = round_elem(g * u0, is_f16), d1 = round_elem(g * u1, is_f16);
-                    du[qd * 4 + i] = pack2(d0 * gt.x * s0, d1 * gt.y * s1, is_f16);
-                    dg[qd * 4 + i] = pack2(d0 * up.x * (s0 + gt.x * s0 * (1.f - s0)), d1 * up.y * (s1 + gt.y * s1 * (1.f - s1)), is_f16);
+                    du[qd * 4 + i] = pack2(d0 * m0, d1 * m1, is_f16);
+                    dg[qd * 4 + i] = pack2(d0 * up.x * gate_slope(p.act, gt.x, s0), d1 * up.y * gate_slope(p.act, gt.y, s1), is_f16);
                     ag[qd * 4 + i] = pack2(g * a0, g * a1, is_f16);
                 }
             }

@@ -591,6 +591,7 @@ int umma_row_gemm(const RowGemm& g, int dtype, int32_t* status, cudaStream_t str
     p.d_gates = g.d_gates;
     p.g_map = g.g_map;
     p.status = status;
+    p.act = g.act;
     p.idesc = make_idesc(0, p.b_mn, p.is_f16, BM);
     p.full_count = 1 + (p.a_tma ? 0 : GATHER_THREADS);
 

@@ -7,7 +7,7 @@ kernels; the former name is kept as an alias), `Experts_Torch`, `Experts_Triton`
 cute_kernels/kernels/scattermoe/triton_implementation/__init__.py:11-101, ops.py:133-301).
 
 Two execution paths exist in `MoE_B200._compute_experts`:
-  * fused: taken when the layer is a GLU layer whose activation is SwiGLU on the fused tensor.  One
+  * fused: taken when the layer is a GLU layer whose activation is SwiGLU on the fused tensor or `nn.GLU()`.  One
     routing call, then up-projection + SwiGLU, down-projection + gate scaling, slot sum; the backward
     runs five kernels.  Intermediates live in the padded grouped order.
   * generic: any other activation callable.  The same sequence of operators as the reference
@@ -190,10 +190,10 @@ def _gather_rows(src: torch.Tensor, row_map: torch.Tensor, out: torch.Tensor) ->
 
 
 @b200_op("up_forward", mutates_args={"h", "a"})
-def _up_forward(x: torch.Tensor, w_fc: torch.Tensor, expert_offsets: torch.Tensor, row_token: torch.Tensor | None, h: torch.Tensor, a: torch.Tensor) -> None:
+def _up_forward(x: torch.Tensor, w_fc: torch.Tensor, expert_offsets: torch.Tensor, row_token: torch.Tensor | None, h: torch.Tensor, a: torch.Tensor, activation: int = 0) -> None:
     E, I2, H = w_fc.shape
     check(
-        lib().b200moe_up_forward(ptr(x), x.stride(0), ptr(w_fc), ptr(expert_offsets), ptr(row_token), ptr(h), ptr(a), x.size(0), H, I2 // 2, E, h.size(0), dtype_code(x), ptr(status_word(x.device)), stream_ptr(x.device)),
+        lib().b200moe_up_forward(ptr(x), x.stride(0), ptr(w_fc), ptr(expert_offsets), ptr(row_token), ptr(h), ptr(a), x.size(0), H, I2 // 2, E, h.size(0), activation, dtype_code(x), ptr(status_word(x.device)), stream_ptr(x.device)),
         "up_forward",
     )
 
@@ -208,12 +208,12 @@ def _down_forward(a: torch.Tensor, w_proj: torch.Tensor, expert_offsets: torch.T
 
 
 @b200_op("down_dgrad", mutates_args={"dh", "ag", "d_gates"})
-def _down_dgrad(grad_out: torch.Tensor, w_proj: torch.Tensor, expert_offsets: torch.Tensor, row_token: torch.Tensor | None, row_slot: torch.Tensor, gates: torch.Tensor | None, h: torch.Tensor, dh: torch.Tensor, ag: torch.Tensor, d_gates: torch.Tensor) -> None:
+def _down_dgrad(grad_out: torch.Tensor, w_proj: torch.Tensor, expert_offsets: torch.Tensor, row_token: torch.Tensor | None, row_slot: torch.Tensor, gates: torch.Tensor | None, h: torch.Tensor, dh: torch.Tensor, ag: torch.Tensor, d_gates: torch.Tensor, activation: int = 0) -> None:
     E, H, I = w_proj.shape
     check(
         lib().b200moe_down_dgrad(
             ptr(grad_out), grad_out.stride(0), ptr(w_proj), ptr(expert_offsets), ptr(row_token), ptr(row_slot), ptr(gates), ptr(h), ptr(dh), ptr(ag), ptr(d_gates),
-            d_gates.numel(), H, I, E, h.size(0), dtype_code(h), ptr(status_word(h.device)), stream_ptr(h.device),
+            d_gates.numel(), H, I, E, h.size(0), activation, dtype_code(h), ptr(status_word(h.device)), stream_ptr(h.device),
         ),
         "down_dgrad",
     )
@@ -246,7 +246,7 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, x, w_fc, w_proj, router_weights, selected_experts, out_bufs=None):
+    def forward(ctx, x, w_fc, w_proj, router_weights, selected_experts, out_bufs=None, activation=0):
         # out_bufs = (y_out, dx_out), k == 1 only: caller-owned (rows >= T, H) buffers that receive the output / the
         # input gradient directly, e.g. exchange buffers other ranks read from.  Passed as a tuple so that autograd
         # does not see them as inputs.
@@ -269,7 +269,7 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
         # rows of x in the padded grouped order: one HBM pass, after which every operand is a plain TMA tile
         x_rows = torch.empty(cap, H, device=x.device, dtype=x.dtype)
         _gather_rows(x, row_token, x_rows)
-        _launch("up_forward", _up_forward, x_rows, w_fc, offsets, None, h, a)
+        _launch("up_forward", _up_forward, x_rows, w_fc, offsets, None, h, a, activation)
         if not KEEP_GATHERED_INPUT:
             x_rows = None
         y_expanded = y_out[:M] if (k == 1 and y_out is not None) else torch.empty(M, H, device=x.device, dtype=x.dtype)
@@ -281,6 +281,7 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
             combine(y_expanded, None, y, k)
         ctx.save_for_backward(x, w_fc, w_proj, gates, offsets, row_token, row_slot, h, x_rows)
         ctx.k = k
+        ctx.activation = activation
         ctx.rw_dtype = router_weights.dtype
         ctx.dx_out = dx_out if k == 1 else None
         return y
@@ -301,7 +302,7 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
         d_gates = torch.empty(M, device=x.device, dtype=torch.float32)
         g_rows = torch.empty(cap, H, device=x.device, dtype=x.dtype)
         _gather_rows(grad_y, row_token, g_rows)
-        _launch("down_dgrad", _down_dgrad, g_rows, w_proj, offsets, None, row_slot, gates, h, dh, ag, d_gates)
+        _launch("down_dgrad", _down_dgrad, g_rows, w_proj, offsets, None, row_slot, gates, h, dh, ag, d_gates, ctx.activation)
 
         d_w_proj = d_w_fc = d_x = d_rw = None
         if need_w2:
@@ -325,15 +326,19 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
                 combine(dx_expanded, None, d_x, k)
         if need_g:
             d_rw = d_gates.view(T, k).to(ctx.rw_dtype)
-        return d_x, d_w_fc, d_w_proj, d_rw, None, None
+        return d_x, d_w_fc, d_w_proj, d_rw, None, None, None
 
 
-def fused_swiglu_experts(x, w_fc, w_proj, router_weights, selected_experts, y_out=None, dx_out=None):
+ACTIVATIONS = {"swiglu": 0, "glu": 1}  # a = h[:, :I] * silu(h[:, I:]) / h[:, :I] * sigmoid(h[:, I:])
+
+
+def fused_swiglu_experts(x, w_fc, w_proj, router_weights, selected_experts, y_out=None, dx_out=None, activation: str = "swiglu"):
+    """Routed GLU experts on the fused kernels; `activation` selects the gate function (`ACTIVATIONS`)."""
     if x.size(0) == 0:
         # no tokens: nothing to launch; the zero-weighted sums keep every input in the graph with a zero gradient
         return x.new_zeros(0, x.size(1)) + 0 * (x.sum() + w_fc.sum() + w_proj.sum() + router_weights.sum())
     out_bufs = (y_out, dx_out) if (y_out is not None or dx_out is not None) else None
-    return _FusedSwiGLUExperts.apply(x, w_fc, w_proj, router_weights, selected_experts, out_bufs)
+    return _FusedSwiGLUExperts.apply(x, w_fc, w_proj, router_weights, selected_experts, out_bufs, ACTIVATIONS[activation])
 
 
 # --------------------------------------------------------------------------------------------------
@@ -454,6 +459,15 @@ def is_swiglu_callable(fn) -> bool:
     return getattr(fn, "__name__", "") in ("swiglu_unchunked_torch", "swiglu_unchunked_cute")
 
 
+def fused_activation(fn) -> str | None:
+    """Name of the fused gate function an activation callable maps to, or None (the layer then runs it un-fused)."""
+    if is_swiglu_callable(fn):
+        return "swiglu"
+    if isinstance(fn, nn.GLU) and fn.dim in (-1, 1):  # the layer applies it to 2-D (rows, 2I) tensors
+        return "glu"
+    return None
+
+
 class MoE_B200(MoE_Torch):
     """MoE layer on the sm_100a kernels.  Same constructor, parameters and `state_dict` keys as `MoE_Torch`.
 
@@ -472,8 +486,9 @@ class MoE_B200(MoE_Torch):
         return super()._compute_routing_weights(hidden_states)
 
     def _compute_experts(self, hidden_states: torch.Tensor, router_weights: torch.Tensor, selected_experts: torch.Tensor) -> torch.Tensor:
-        if self.is_glu and is_swiglu_callable(self.act):
-            return fused_swiglu_experts(hidden_states, self.c_fc.weight, self.c_proj.weight, router_weights, selected_experts)
+        fused = fused_activation(self.act) if self.is_glu else None
+        if fused is not None:
+            return fused_swiglu_experts(hidden_states, self.c_fc.weight, self.c_proj.weight, router_weights, selected_experts, activation=fused)
         with torch.no_grad():
             sorted_expert_idxs, sorted_scattered_idxs, expert_offsets, _, _, _ = route(selected_experts.flatten(), self.num_experts, self.top_k, True, False)
         h = self.c_fc(hidden_states, self.top_k, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets, grouped_out=True)

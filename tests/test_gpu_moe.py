@@ -36,12 +36,12 @@ def _engine_reset():
     _lib.check_status(torch.device("cuda"))
 
 
-def run_fused(case_dev):
+def run_fused(case_dev, activation="swiglu"):
     x = case_dev["x"].clone().requires_grad_(True)
     w1 = case_dev["w_fc"].clone().requires_grad_(True)
     w2 = case_dev["w_proj"].clone().requires_grad_(True)
     rw = case_dev["rw"].clone().requires_grad_(True)
-    y = kh.fused_swiglu_experts(x, w1, w2, rw, case_dev["sel"])
+    y = kh.fused_swiglu_experts(x, w1, w2, rw, case_dev["sel"], activation=activation)
     y.backward(case_dev["g"])
     return dict(y=y.detach(), dx=x.grad, d_w_fc=w1.grad, d_w_proj=w2.grad, d_router_weights=rw.grad)
 
@@ -96,12 +96,42 @@ def test_layer_matches_golden_fp32(name):
     assert rel_l2(sub(m.c_fc.weight.grad), gold["ext_d_w_fc_sub"]) < 1e-5
 
 
+@pytest.mark.parametrize("name", ["tiny", "c2_small", "c5_small", "odd"])
+@pytest.mark.parametrize("engine,dtype", [("simt", torch.float32), ("umma", torch.bfloat16), ("umma", torch.float16), ("umma1", torch.bfloat16)])
+def test_fused_glu_experts_match_oracle(name, engine, dtype):
+    """The sigmoid-gated variant of the fused path (torch.nn.GLU between the projections, the activation of the
+    reference's module test, tests/test_commons.py:86-87) against the CPU oracle with that activation."""
+    w = SMALL[name]
+    _lib.set_engine({"simt": _lib.ENGINE_SIMT, "umma": _lib.ENGINE_UMMA, "umma1": _lib.ENGINE_UMMA_1CTA}[engine])
+    case = make_case(w, seed=2, dtype=dtype)
+    ref = orc.experts_with_grads(case["x"], case["w_fc"], case["w_proj"], case["rw"], case["sel"], case["g"], act=lambda t: torch.nn.functional.glu(t, dim=-1))
+    got = run_fused(to_dev(case, dtype), activation="glu")
+    check(got, ref, tolerance(dtype), (name, engine, dtype))
+
+
+def test_glu_module_takes_the_fused_path():
+    from kernel_hyperdrive_b200 import scattermoe
+
+    assert scattermoe.fused_activation(torch.nn.GLU()) == "glu" and scattermoe.fused_activation(torch.nn.GLU(dim=0)) is None
+    assert scattermoe.fused_activation(kh.swiglu_unchunked_torch) == "swiglu" and scattermoe.fused_activation(torch.tanh) is None
+    m = kh.MoE_Triton(8, 2, 256, 512, torch.nn.GLU(), True, False, 0.02).cuda().bfloat16()
+    x = torch.randn(300, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    names = []
+    scattermoe.set_timing_sink(names)
+    try:
+        y, _ = m(x)
+        y.sum().backward()
+    finally:
+        scattermoe.set_timing_sink(None)
+    assert [n[0] for n in names] == ["up_forward", "down_forward", "down_dgrad", "down_wgrad", "up_wgrad", "up_dgrad"]
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("act_name,is_glu", [("glu", True), ("gelu", False), ("swiglu", True)])
+@pytest.mark.parametrize("act_name,is_glu", [("glu", True), ("glu_callable", True), ("gelu", False), ("swiglu", True)])
 def test_generic_path_matches_eager_module(dtype, act_name, is_glu):
     """Any activation callable: same operator sequence as the reference's scatter module; compared with the
     eager torch module on the same device and weights (the reference's own test strategy, many tokens)."""
-    act = {"glu": torch.nn.GLU(), "gelu": lambda t: torch.nn.functional.gelu(t, approximate="tanh"), "swiglu": lambda t: kh.swiglu_unchunked_torch(t)}[act_name]
+    act = {"glu": torch.nn.GLU(), "glu_callable": lambda t: torch.nn.functional.glu(t, dim=-1), "gelu": lambda t: torch.nn.functional.gelu(t, approximate="tanh"), "swiglu": lambda t: kh.swiglu_unchunked_torch(t)}[act_name]
     torch.manual_seed(42)
     E, k, H, I, T = 8, 2, 256, 512, 200
     ref_m = kh.MoE_Torch(E, k, H, I, act, is_glu, False, 0.02).cuda().to(dtype)
