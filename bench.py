@@ -386,6 +386,17 @@ def run_gpu_arm(args, w):
         },
     }
 
+    if world > 1:
+        # load report: the experts of a rank get the rows the routing sends them, so ranks differ; the step runs at
+        # the pace of the busiest one (every pass ends with a rank barrier)
+        from kernel_hyperdrive_b200 import expert_parallel
+
+        mine = torch.tensor([float(expert_parallel.last_received_rows or 0), gemm_total_ms, sum(exchange_ms.values())], device=dev, dtype=torch.float64)
+        everyone = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(everyone, mine)
+        table = torch.stack(everyone).cpu()
+        line["per_rank"] = {"received_rows": [int(v) for v in table[:, 0]], "gemm_ms": [round(float(v), 3) for v in table[:, 1]],
+                            "exchange_ms": [round(float(v), 3) for v in table[:, 2]]}
     if rank == 0 and world == 1 and not args.no_cpu_baseline and not args.profile and w.name in ("c1", "c2"):
         cpu_w = dict(gate=layer.gate.weight.detach().cpu(), w_fc=layer.c_fc.weight.detach().cpu(), w_proj=layer.c_proj.weight.detach().cpu())
         val, sec, sample, threads = cpu_reference_run(w, 1, 1, args.cpu_sample_tokens, weights=cpu_w)

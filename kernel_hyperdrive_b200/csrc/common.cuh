@@ -124,7 +124,12 @@ struct WGemm {
     int Mout, Nout, E;
 };
 
-enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_DGRAD_DOWN = 2, EPI_ROUTER = 3 };
+// Epilogues of the tensor-core kernels (template arguments).  The two gated-activation epilogues exist once per gate
+// function so that the choice costs nothing at run time; RowGemm names them as (EPI_SWIGLU or EPI_DGRAD_DOWN, act).
+enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_DGRAD_DOWN = 2, EPI_ROUTER = 3, EPI_GLU = 4, EPI_DGRAD_DOWN_GLU = 5 };
+__host__ __device__ constexpr bool epi_gated_forward(int epi) { return epi == EPI_SWIGLU || epi == EPI_GLU; }
+__host__ __device__ constexpr bool epi_gated_dgrad(int epi) { return epi == EPI_DGRAD_DOWN || epi == EPI_DGRAD_DOWN_GLU; }
+__host__ __device__ constexpr int epi_act(int epi) { return (epi == EPI_GLU || epi == EPI_DGRAD_DOWN_GLU) ? 1 : 0; }
 
 // engines
 int simt_row_gemm(const RowGemm& g, int dtype, cudaStream_t stream);

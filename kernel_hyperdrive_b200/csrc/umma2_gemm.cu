@@ -240,7 +240,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
                                 for (int j = 0; j < 2; ++j)
                                     tma_load_2d_pair(sb + j * 8192, &tmap_b, lead_full, ti.nb * BN + (int)rank * 128 + j * 64, krow);
                             } else {
-                                int r0 = EPI == EPI_SWIGLU ? ti.e * p.b_rows_per_expert + ti.nb * 128 + (int)rank * p.swiglu_half
+                                int r0 = epi_gated_forward(EPI) ? ti.e * p.b_rows_per_expert + ti.nb * 128 + (int)rank * p.swiglu_half
                                                            : ti.e * p.b_rows_per_expert + ti.nb * BN + (int)rank * 128;
                                 tma_load_2d_pair(sb, &tmap_b, lead_full, k0, r0);
                             }
@@ -296,7 +296,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
                                 tma_load_2d_pair(sb + j * 8192, &tmap_b, lead_full, ti.nb * BN + (int)rank * 128 + j * 64, krow);
                         } else {
                             int r0;
-                            if (EPI == EPI_SWIGLU) {
+                            if (epi_gated_forward(EPI)) {
                                 // leader: 128 "up" rows, peer: the matching 128 "gate" rows
                                 r0 = ti.e * p.b_rows_per_expert + ti.nb * 128 + (int)rank * p.swiglu_half;
                             } else {
@@ -448,6 +448,10 @@ int launch_2cta(int epi, const UmmaParams& p, const CUtensorMap& ma, const CUten
             return launch2<EPI_SWIGLU>(p, ma, mb, mo, mo2, mo3, stream);
         case EPI_DGRAD_DOWN:
             return launch2<EPI_DGRAD_DOWN>(p, ma, mb, mo, mo2, mo3, stream);
+        case EPI_GLU:
+            return launch2<EPI_GLU>(p, ma, mb, mo, mo2, mo3, stream);
+        case EPI_DGRAD_DOWN_GLU:
+            return launch2<EPI_DGRAD_DOWN_GLU>(p, ma, mb, mo, mo2, mo3, stream);
         default:
             set_error_detail("unknown epilogue %d", epi);
             return B200MOE_ERR_ARG;

@@ -26,7 +26,6 @@ struct UmmaParams {
     int nb_count;   // column blocks
     int mb_count;   // W: row blocks
     int swiglu_half;  // EPI_SWIGLU: I (columns of one half); tiles cover 128 columns of each half
-    int act;          // EPI_SWIGLU / EPI_DGRAD_DOWN: ACT_SILU or ACT_SIGMOID
     // operand A (R: activations; W: P)
     int a_tma, a_mn;
     int a_g4, a_oob;  // two-CTA kernel: rows of A come through TMA row gather by a_map; a_oob = index that reads as zeros
@@ -329,7 +328,8 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
                 }
             }
         }
-    } else if (EPI == EPI_SWIGLU) {
+    } else if (epi_gated_forward(EPI)) {
+        constexpr int ACT = epi_act(EPI);
         // accumulator columns [0,128) = up, [128,256) = gate, for output columns nb*128 .. +128 of each half;
         // the layout is the padded grouped order, so all 128 rows of the tile are written (fillers get zeros)
         const int I = p.swiglu_half;
@@ -348,7 +348,7 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
                 hg[i] = pack2(__uint_as_float(gt[2 * i]), __uint_as_float(gt[2 * i + 1]), is_f16);
                 // the activation sees the values as stored (rounded to the tensor type)
                 float2 fu = unpack2(hu[i], is_f16), fg = unpack2(hg[i], is_f16);
-                av[i] = pack2(fu.x * gate_value(p.act, fg.x, sigmoid_fast(fg.x)), fu.y * gate_value(p.act, fg.y, sigmoid_fast(fg.y)), is_f16);
+                av[i] = pack2(fu.x * gate_value(ACT, fg.x, sigmoid_fast(fg.x)), fu.y * gate_value(ACT, fg.y, sigmoid_fast(fg.y)), is_f16);
             }
             stage_store(mo, n0 + c, row_c, 0, hu);    // up half of h
             stage_store(mo3, n0 + c, row_c, 0, hg);   // gate half of h (its own map: columns clip at I)
@@ -447,7 +447,8 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
                 }
             }
         }
-    } else {  // EPI_DGRAD_DOWN
+    } else {  // EPI_DGRAD_DOWN, EPI_DGRAD_DOWN_GLU
+        constexpr int ACT = epi_act(EPI);
         const int I = p.N;
         const int64_t prow = ti.row0 + r;
         const int n0 = ti.nb * BN;
@@ -480,12 +481,12 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
                     float2 up = unpack2(hua[i], is_f16), gt = unpack2(hga[i], is_f16);
                     float u0 = __uint_as_float(u[qd * 8 + 2 * i]), u1 = __uint_as_float(u[qd * 8 + 2 * i + 1]);
                     float s0 = sigmoid_fast(gt.x), s1 = sigmoid_fast(gt.y);
-                    float m0 = gate_value(p.act, gt.x, s0), m1 = gate_value(p.act, gt.y, s1);
+                    float m0 = gate_value(ACT, gt.x, s0), m1 = gate_value(ACT, gt.y, s1);
                     float a0 = round_elem(up.x * m0, is_f16), a1 = round_elem(up.y * m1, is_f16);
                     dot += a0 * u0 + a1 * u1;
                     float d0 = round_elem(g * u0, is_f16), d1 = round_elem(g * u1, is_f16);
                     du[qd * 4 + i] = pack2(d0 * m0, d1 * m1, is_f16);
-                    dg[qd * 4 + i] = pack2(d0 * up.x * gate_slope(p.act, gt.x, s0), d1 * up.y * gate_slope(p.act, gt.y, s1), is_f16);
+                    dg[qd * 4 + i] = pack2(d0 * up.x * gate_slope(ACT, gt.x, s0), d1 * up.y * gate_slope(ACT, gt.y, s1), is_f16);
                     ag[qd * 4 + i] = pack2(g * a0, g * a1, is_f16);
                 }
             }

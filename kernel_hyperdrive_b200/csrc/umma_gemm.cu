@@ -246,7 +246,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                                 for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tmap_b, bar, ti.nb * BN + j * 64, krow);
                             } else {
                                 int r0, r1;
-                                if (EPI == EPI_SWIGLU) {
+                                if (epi_gated_forward(EPI)) {
                                     r0 = ti.e * p.b_rows_per_expert + ti.nb * 128;
                                     r1 = r0 + p.swiglu_half;
                                 } else {
@@ -591,7 +591,6 @@ int umma_row_gemm(const RowGemm& g, int dtype, int32_t* status, cudaStream_t str
     p.d_gates = g.d_gates;
     p.g_map = g.g_map;
     p.status = status;
-    p.act = g.act;
     p.idesc = make_idesc(0, p.b_mn, p.is_f16, BM);
     p.full_count = 1 + (p.a_tma ? 0 : GATHER_THREADS);
 
@@ -628,7 +627,7 @@ int umma_row_gemm(const RowGemm& g, int dtype, int32_t* status, cudaStream_t str
         if (rc) return rc;
         rc = make_store_map(&mo2, g.out2, 0, g.rows_cap, g.N / 2, g.N / 2, 0, p.is_f16);
         if (rc) return rc;
-        return launch_any<EPI_SWIGLU>(p, ma, mb, mo, mo2, mo3, stream);
+        return g.act == ACT_SIGMOID ? launch_any<EPI_GLU>(p, ma, mb, mo, mo2, mo3, stream) : launch_any<EPI_SWIGLU>(p, ma, mb, mo, mo2, mo3, stream);
     }
     p.N = g.N;
     p.nb_count = (g.N + BN - 1) / BN;
@@ -640,7 +639,8 @@ int umma_row_gemm(const RowGemm& g, int dtype, int32_t* status, cudaStream_t str
         if (rc) return rc;
         rc = make_store_map(&mo2, g.out2, 0, g.rows_cap, g.N, g.N, 0, p.is_f16);
         if (rc) return rc;
-        return launch_any<EPI_DGRAD_DOWN>(p, ma, mb, mo, mo2, mo3, stream);
+        return g.act == ACT_SIGMOID ? launch_any<EPI_DGRAD_DOWN_GLU>(p, ma, mb, mo, mo2, mo3, stream)
+                                    : launch_any<EPI_DGRAD_DOWN>(p, ma, mb, mo, mo2, mo3, stream);
     }
     if (g.o_map == nullptr && g.scale == nullptr) {
         rc = make_store_map(&mo, g.out, 0, g.rows_cap, g.N, g.ldo, 0, p.is_f16);

@@ -125,6 +125,9 @@ def exchange_counts(counts: torch.Tensor, world: int, group) -> torch.Tensor:
     return recv.view(world, -1)
 
 
+last_received_rows = None  # rows this rank's experts received in the most recent exchange pass (load report)
+
+
 def ep_experts(x, router_weights, selected_experts, num_experts: int, local_experts_fn: Callable, group, ops=CudaRowOps):
     """Routed experts over an expert-parallel group.  `local_experts_fn(rows, local_expert_ids)` evaluates
     this rank's experts on the received rows (unit gates, one expert per row) and must be differentiable."""
@@ -140,6 +143,8 @@ def ep_experts(x, router_weights, selected_experts, num_experts: int, local_expe
         # one host read per pass: NCCL takes the split sizes as host integers
         host = torch.cat([counts.view(world, e_local).sum(1), recv_counts.sum(1), ]).tolist()
         send_splits, recv_splits = [int(v) for v in host[:world]], [int(v) for v in host[world:]]
+        global last_received_rows
+        last_received_rows = sum(recv_splits)
         local_ids = torch.repeat_interleave(
             torch.arange(e_local, device=x.device).repeat(world), recv_counts.flatten().long(), output_size=sum(recv_splits)
         )
@@ -203,6 +208,8 @@ def _make_plan(selected_experts, num_experts: int, world: int, rank: int, group,
     plan.base = (to_rank.cumsum(0) - to_rank)[rank].to(torch.int32)  # rows of lower-ranked sources in each destination
     recv_counts = counts_all[:, rank * e_local : (rank + 1) * e_local]
     plan.m_recv = int(recv_counts.sum().item())  # the one host read of the pass: sizes the local expert tensors
+    global last_received_rows
+    last_received_rows = plan.m_recv
     plan.local_ids = torch.repeat_interleave(
         torch.arange(e_local, device=ss.device).repeat(world), recv_counts.reshape(-1).long(), output_size=plan.m_recv
     )
