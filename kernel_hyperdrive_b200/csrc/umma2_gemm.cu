@@ -37,6 +37,18 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
     return r;
 }
+// Non-blocking look at a barrier phase (the wait proper follows later if this says "not yet").
+__device__ __forceinline__ uint32_t mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -268,6 +280,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
             uint32_t phase = 0;
             Tile ti;
             bool ok = true;
+            const uint32_t lead_full0 = map_to_cta(smem_u32(&full_bar[0]), 0);
             for (int t = cluster_id; t < ntiles && ok; t += nclusters) {
                 decode_tile2(p, tb, t, rank, ti);
                 for (int ks = 0; ks < ti.ksteps; ++ks) {
@@ -275,7 +288,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
                         ok = false;
                         break;
                     }
-                    const uint32_t lead_full = map_to_cta(smem_u32(&full_bar[stage]), 0);
+                    const uint32_t lead_full = lead_full0 + stage * 8;
                     if (rank == 0) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * (A_STAGE_BYTES + B_HALF_BYTES));
                     const uint32_t sa = smem_u32(smem_a + stage * A_STAGE_BYTES);
                     const uint32_t sb = smem_u32(smem_b + stage * B_HALF_BYTES);
@@ -323,32 +336,42 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
             bool ok = true;
             const uint32_t a_step = p.a_mn ? 128u : 2u;
             const uint32_t b_step = p.b_mn ? 128u : 2u;
+            // The tensor pipe queues only a few instructions, so every cycle this lane spends between the last MMA of a
+            // k step and the first of the next one can leave the pipe idle: addresses are formed once, the next stage's
+            // barrier is looked at while the current MMAs are being issued, and the wait proper runs only if that look
+            // said "not yet".
+            const uint64_t adesc0 = make_desc(smem_u32(smem_a), p.a_mn);
+            const uint64_t bdesc0 = make_desc(smem_u32(smem_b), p.b_mn);
+            const uint32_t full0 = smem_u32(&full_bar[0]);
+            const uint32_t empty0 = smem_u32(&empty_bar[0]);
+            const uint32_t empty0_peer = map_to_cta(empty0, 1);
+            const uint32_t idesc = p.idesc;
+            uint32_t ready = 0;  // the look-ahead result for (stage, phase)
             for (int t = cluster_id; t < ntiles && ok; t += nclusters) {
                 decode_tile2(p, tb, t, 0, ti);
                 if (!mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1, abort_flag, p.status, 212)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 for (int ks = 0; ks < ti.ksteps; ++ks) {
-                    if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, 213)) {
+                    if (!ready && !mbar_wait(full0 + stage * 8, phase, abort_flag, p.status, 213)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    uint64_t adesc = make_desc(smem_u32(smem_a + stage * A_STAGE_BYTES), p.a_mn);
-                    uint64_t bdesc = make_desc(smem_u32(smem_b + stage * B_HALF_BYTES), p.b_mn);
-#pragma unroll
-                    for (int j = 0; j < BK / 16; ++j) {
-                        tc_mma_pair(d_tmem, adesc + (uint64_t)(j * a_step), bdesc + (uint64_t)(j * b_step), p.idesc,
-                                    (ks | j) ? 1u : 0u);
-                    }
-                    // the stage is free in both CTAs once these MMAs have read it
-                    const uint32_t eb = smem_u32(&empty_bar[stage]);
-                    tc_commit_pair(eb);
-                    tc_commit_pair(map_to_cta(eb, 1));
+                    const uint64_t adesc = adesc0 + (uint64_t)(stage * (A_STAGE_BYTES >> 4));
+                    const uint64_t bdesc = bdesc0 + (uint64_t)(stage * (B_HALF_BYTES >> 4));
+                    const int s_cur = stage;
                     if (++stage == STAGES2) {
                         stage = 0;
                         phase ^= 1;
                     }
+                    tc_mma_pair(d_tmem, adesc, bdesc, idesc, ks ? 1u : 0u);
+                    ready = mbar_test(full0 + stage * 8, phase);  // next k step's data (also across tiles)
+#pragma unroll
+                    for (int j = 1; j < BK / 16; ++j) tc_mma_pair(d_tmem, adesc + (uint64_t)(j * a_step), bdesc + (uint64_t)(j * b_step), idesc, 1u);
+                    // the stage is free in both CTAs once these MMAs have read it
+                    tc_commit_pair(empty0 + s_cur * 8);
+                    tc_commit_pair(empty0_peer + s_cur * 8);
                 }
                 if (!ok) break;
                 const uint32_t fb = smem_u32(&tmem_full_bar[acc]);
