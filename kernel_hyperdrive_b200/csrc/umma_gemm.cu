@@ -445,7 +445,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const uint32_t stg = smem_u32(smem_stg + (warp - 6) * STG_BYTES);
         const uint32_t stg_row = stg + lane * 64;
         const uint32_t stg_swz = (uint32_t)((lane >> 1) & 3);
-        auto stage_store = [&](const CUtensorMap* map, int c0, int c1, int c2, const uint32_t (&pk)[16]) {
+        auto stage_store = [&](int /*slot: one box per warp here*/, const CUtensorMap* map, int c0, int c1, int c2, const uint32_t (&pk)[16]) {
             if (lane == 0) bulk_wait_read0();
             __syncwarp();
 #pragma unroll
