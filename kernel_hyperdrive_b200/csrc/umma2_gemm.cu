@@ -420,14 +420,28 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
         int acc = 0;
         uint32_t acc_phase = 0;
         Tile ti;
+        if (epi_gated_dgrad(EPI) && cluster_id < ntiles) {
+            decode_tile2(p, tb, cluster_id, rank, ti);
+            epilogue_prefetch<EPI>(p, ti, q, half, lane);
+        }
         for (int t = cluster_id; t < ntiles; t += nclusters) {
+            if (epi_gated_dgrad(EPI) && t + nclusters < ntiles) {  // the tile after this one: requested a whole tile ahead
+                decode_tile2(p, tb, t + nclusters, rank, ti);
+                epilogue_prefetch<EPI>(p, ti, q, half, lane);
+            }
             decode_tile2(p, tb, t, rank, ti);
             if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status, 215, 200)) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
             // a CTA whose half of the cluster tile does not exist (odd number of row blocks) has nothing to write
             const bool live = p.wfam || ti.rows_valid > 0;
-            if (live) epilogue_tile<EPI>(p, ti, taddr, q, half, lane, &tmap_o, &tmap_o2, &tmap_o3, stage_store);
+            if (live) {
+                if (p.is_f16) {
+                    epilogue_tile<EPI, true>(p, ti, taddr, q, half, lane, &tmap_o, &tmap_o2, &tmap_o3, stage_store);
+                } else {
+                    epilogue_tile<EPI, false>(p, ti, taddr, q, half, lane, &tmap_o, &tmap_o2, &tmap_o3, stage_store);
+                }
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));

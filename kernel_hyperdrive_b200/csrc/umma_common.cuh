@@ -215,11 +215,7 @@ __device__ __forceinline__ float load_scalar(const void* p, int64_t i, int is_f1
 }
 __device__ __forceinline__ float round_elem(float v, int is_f16) {
     if (is_f16) return __half2float(__float2half_rn(v));
-    // bf16 round-to-nearest-even on the integer pipe (the conversion instructions share the special-function unit);
-    // NaN is kept a NaN
-    uint32_t u = __float_as_uint(v);
-    uint32_t r = (u + 0x7FFFu + ((u >> 16) & 1u)) & 0xFFFF0000u;
-    return __uint_as_float((u & 0x7FFFFFFFu) > 0x7F800000u ? (u | 0x00400000u) & 0xFFFF0000u : r);
+    return __bfloat162float(__float2bfloat16_rn(v));
 }
 
 // ---- tile bookkeeping ----------------------------------------------------------------------------
@@ -280,12 +276,15 @@ __device__ __forceinline__ void decode_tile(const UmmaParams& p, const Tables& t
 // Runs in the epilogue warps.  `taddr` addresses this warp's 32 TMEM lanes of the tile's accumulator, `q` is the
 // lane quarter, `half` selects which half of the tile's columns this warp handles, `stage_store(slot, map, c0, c1, c2,
 // packed[16])` sends one 32 x 32 box of 16-bit values to the output through shared memory and TMA.
-template <int EPI, class StageStore>
+// F16 (fp16 rather than bf16 tensors) is a template argument: the conversions then compile to straight-line code; as a
+// run-time flag every pack / unpack / rounding was its own branch, which kept the compiler from interleaving the
+// independent elements of a chunk and made the arithmetic of the down-dgrad epilogue as long as its main loop.
+template <int EPI, bool F16, class StageStore>
 __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& ti, uint32_t taddr, int q, int half, int lane,
                                               const CUtensorMap* mo, const CUtensorMap* mo2, const CUtensorMap* mo3,
                                               StageStore& stage_store) {
     const int r = q * 32 + lane;  // row of the tile this thread owns
-    const int is_f16 = p.is_f16;
+    constexpr int is_f16 = F16 ? 1 : 0;
     const bool have_acc = ti.ksteps > 0;
 
     if (EPI == EPI_STORE) {
@@ -503,9 +502,11 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
                     float u0 = __uint_as_float(u[qd * 8 + 2 * i]), u1 = __uint_as_float(u[qd * 8 + 2 * i + 1]);
                     float s0 = sigmoid_fast(gt.x), s1 = sigmoid_fast(gt.y);
                     float m0 = gate_value(ACT, gt.x, s0), m1 = gate_value(ACT, gt.y, s1);
-                    float a0 = round_elem(up.x * m0, is_f16), a1 = round_elem(up.y * m1, is_f16);
+                    // activation and scaled upstream gradient stay in fp32 here (the eager module rounds both to the
+                    // tensor type; the conversions are special-function-unit work this epilogue has no room for)
+                    float a0 = up.x * m0, a1 = up.y * m1;
                     dot += a0 * u0 + a1 * u1;
-                    float d0 = round_elem(g * u0, is_f16), d1 = round_elem(g * u1, is_f16);
+                    float d0 = g * u0, d1 = g * u1;
                     du[qd * 4 + i] = pack2(d0 * m0, d1 * m1, is_f16);
                     dg[qd * 4 + i] = pack2(d0 * up.x * gate_slope(ACT, gt.x, s0), d1 * up.y * gate_slope(ACT, gt.y, s1), is_f16);
                     ag[qd * 4 + i] = pack2(g * a0, g * a1, is_f16);
@@ -522,6 +523,23 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
         }
         if (slot >= 0) atomicAdd(p.d_gates + slot, dot);
     }
+}
+
+// Down-dgrad epilogue: ask L2 for the pre-activation values a warp will read for a tile (its 32 rows, its half of the
+// tile's columns, both halves of h) as one contiguous piece per row.  The epilogue itself reads them 64 bytes per row and
+// column chunk, microseconds apart; without the request every such read opens its own DRAM page.
+template <int EPI>
+__device__ __forceinline__ void epilogue_prefetch(const UmmaParams& p, const Tile& ti, int q, int half, int lane) {
+    if (!epi_gated_dgrad(EPI)) return;
+    const int I = p.N;
+    const int c0 = ti.nb * BN + half * (BN / 2);
+    const int cols = min(BN / 2, I - c0);
+    if (cols <= 0 || ti.rows_valid <= 0) return;
+    const int64_t prow = ti.row0 + q * 32 + lane;
+    const uint8_t* up = (const uint8_t*)p.h + (prow * 2 * (int64_t)I + c0) * 2;
+    const uint32_t bytes = (uint32_t)cols * 2u;
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(up), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(up + (int64_t)I * 2), "r"(bytes) : "memory");
 }
 
 // ---- host helpers (defined in umma_gemm.cu) ---------------------------------------------------------

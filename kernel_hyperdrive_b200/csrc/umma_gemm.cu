@@ -470,7 +470,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status, 205, 200)) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
-            epilogue_tile<EPI>(p, ti, taddr, q, half, lane, &tmap_o, &tmap_o2, &tmap_o3, stage_store);
+            if (p.is_f16) {
+                epilogue_tile<EPI, true>(p, ti, taddr, q, half, lane, &tmap_o, &tmap_o2, &tmap_o3, stage_store);
+            } else {
+                epilogue_tile<EPI, false>(p, ti, taddr, q, half, lane, &tmap_o, &tmap_o2, &tmap_o3, stage_store);
+            }
             tc_fence_before();
             mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
             if (++acc == 2) {
