@@ -23,13 +23,7 @@ namespace umma {
 
 namespace {
 
-constexpr int STAGES2 = 6;  // most stages any instantiation uses (barrier arrays are sized for it)
-// Kernels whose epilogue sends three outputs per column chunk (the gated-activation epilogues) give every epilogue warp
-// three staging boxes, so the three TMA stores of a chunk go out back to back instead of each waiting until the previous
-// one has read the single box (that wait, about a microsecond per store, made the down-dgrad epilogue longer than its main
-// loop); the 32 KB come from running five pipeline stages instead of six, which the main loop does not notice.
-__host__ __device__ constexpr int stages_of(int epi) { return (epi_gated_forward(epi) || epi_gated_dgrad(epi)) ? 5 : 6; }
-__host__ __device__ constexpr int stg_boxes_of(int epi) { return (epi_gated_forward(epi) || epi_gated_dgrad(epi)) ? 3 : 1; }
+constexpr int STAGES2 = 6;
 constexpr int B_HALF_BYTES = (BN / 2) * BK * 2;  // 16 KB
 constexpr int NUM_THREADS2 = (2 + EPI_WARPS) * 32;  // 320: TMA warp, MMA warp, 8 epilogue warps
 
@@ -149,10 +143,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
     // identical layout in both CTAs of the pair: the peer's buffers and barriers sit at the same offsets
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* smem_a = smem;
-    constexpr int NST = stages_of(EPI), NBOX = stg_boxes_of(EPI);
-    uint8_t* smem_b = smem + NST * A_STAGE_BYTES;
-    uint8_t* smem_stg = smem + NST * (A_STAGE_BYTES + B_HALF_BYTES);
-    uint64_t* bars = (uint64_t*)(smem_stg + EPI_WARPS * NBOX * STG_BYTES);
+    uint8_t* smem_b = smem + STAGES2 * A_STAGE_BYTES;
+    uint8_t* smem_stg = smem + STAGES2 * (A_STAGE_BYTES + B_HALF_BYTES);
+    uint64_t* bars = (uint64_t*)(smem_stg + EPI_WARPS * STG_BYTES);
     uint64_t* full_bar = bars;                       // used in the leader only
     uint64_t* empty_bar = bars + STAGES2;            // one set per CTA
     uint64_t* tmem_full_bar = bars + 2 * STAGES2;    // one set per CTA
@@ -171,7 +164,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
     }
     if (threadIdx.x == 0) {
         *abort_flag = 0;
-        for (int s = 0; s < NST; ++s) {
+        for (int s = 0; s < STAGES2; ++s) {
             mbar_init(smem_u32(&full_bar[s]), 1);
             mbar_init(smem_u32(&empty_bar[s]), 1);
         }
@@ -275,7 +268,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
                         if (p.a_g4) tma_gather4_pair(sa + off, &tmap_a, lead_full, ti.mb * BM + j * 64, ia);
                         if (p.b_g4) tma_gather4_pair(sb + off, &tmap_b, lead_full, ti.nb * BN + (int)rank * 128 + j * 64, ib);
                     }
-                    if (++stage == NST) {
+                    if (++stage == STAGES2) {
                         stage = 0;
                         phase ^= 1;
                     }
@@ -325,7 +318,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
                             tma_load_2d_pair(sb, &tmap_b, lead_full, k0, r0);  // box 64 x 128
                         }
                     }
-                    if (++stage == NST) {
+                    if (++stage == STAGES2) {
                         stage = 0;
                         phase ^= 1;
                     }
@@ -368,7 +361,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
                     const uint64_t adesc = adesc0 + (uint64_t)(stage * (A_STAGE_BYTES >> 4));
                     const uint64_t bdesc = bdesc0 + (uint64_t)(stage * (B_HALF_BYTES >> 4));
                     const int s_cur = stage;
-                    if (++stage == NST) {
+                    if (++stage == STAGES2) {
                         stage = 0;
                         phase ^= 1;
                     }
@@ -394,14 +387,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
         // ---------------- epilogue (both CTAs, each on its own 128 rows) ----------------
         const int q = warp & 3;
         const int half = (warp - 2) >> 2;
-        const uint32_t stg0 = smem_u32(smem_stg + (warp - 2) * NBOX * STG_BYTES);
+        const uint32_t stg = smem_u32(smem_stg + (warp - 2) * STG_BYTES);
+        const uint32_t stg_row = stg + lane * 64;
         const uint32_t stg_swz = (uint32_t)((lane >> 1) & 3);
-        // `slot` picks the warp's staging box; callers cycle through the slots in order, so the store that last used a box
-        // is the NBOX-th most recent one and has been read once at most NBOX - 1 stores are still reading
-        auto stage_store = [&](int slot, const CUtensorMap* map, int c0, int c1, int c2, const uint32_t (&pk)[16]) {
-            const uint32_t stg = stg0 + (NBOX > 1 ? slot : 0) * STG_BYTES;
-            const uint32_t stg_row = stg + lane * 64;
-            if (lane == 0) bulk_wait_read<NBOX - 1>();
+        auto stage_store = [&](const CUtensorMap* map, int c0, int c1, int c2, const uint32_t (&pk)[16]) {
+            if (lane == 0) bulk_wait_read0();
             __syncwarp();
 #pragma unroll
             for (int j = 0; j < 4; ++j)
@@ -420,28 +410,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
         int acc = 0;
         uint32_t acc_phase = 0;
         Tile ti;
-        if (epi_gated_dgrad(EPI) && cluster_id < ntiles) {
-            decode_tile2(p, tb, cluster_id, rank, ti);
-            epilogue_prefetch<EPI>(p, ti, q, half, lane);
-        }
         for (int t = cluster_id; t < ntiles; t += nclusters) {
-            if (epi_gated_dgrad(EPI) && t + nclusters < ntiles) {  // the tile after this one: requested a whole tile ahead
-                decode_tile2(p, tb, t + nclusters, rank, ti);
-                epilogue_prefetch<EPI>(p, ti, q, half, lane);
-            }
             decode_tile2(p, tb, t, rank, ti);
             if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status, 215, 200)) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
             // a CTA whose half of the cluster tile does not exist (odd number of row blocks) has nothing to write
             const bool live = p.wfam || ti.rows_valid > 0;
-            if (live) {
-                if (p.is_f16) {
-                    epilogue_tile<EPI, true>(p, ti, taddr, q, half, lane, &tmap_o, &tmap_o2, &tmap_o3, stage_store);
-                } else {
-                    epilogue_tile<EPI, false>(p, ti, taddr, q, half, lane, &tmap_o, &tmap_o2, &tmap_o3, stage_store);
-                }
-            }
+            if (live) epilogue_tile<EPI>(p, ti, taddr, q, half, lane, &tmap_o, &tmap_o2, &tmap_o3, stage_store);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));
@@ -466,15 +442,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
     }
 }
 
-constexpr int smem_bytes2(int epi) {
-    return 1024 + stages_of(epi) * (A_STAGE_BYTES + B_HALF_BYTES) + EPI_WARPS * stg_boxes_of(epi) * STG_BYTES + 128 + (int)sizeof(Tables) + 64;
-}
+constexpr int SMEM_BYTES2 =
+    1024 + STAGES2 * (A_STAGE_BYTES + B_HALF_BYTES) + EPI_WARPS * STG_BYTES + 128 + (int)sizeof(Tables) + 64;
 
 template <int EPI>
 int launch2(const UmmaParams& p, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mo2,
             const CUtensorMap& mo3, cudaStream_t stream) {
     auto kern = umma2_grouped_kernel<EPI>;
-    constexpr int SMEM_BYTES2 = smem_bytes2(EPI);
     cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES2);
     if (err != cudaSuccess) {
         set_error_detail("cudaFuncSetAttribute(smem=%d): %s", SMEM_BYTES2, cudaGetErrorString(err));

@@ -141,19 +141,17 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t sr
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-// waits until at most N of this thread's bulk stores are still reading their shared-memory source
-template <int N>
-__device__ __forceinline__ void bulk_wait_read() {
-    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
 __device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
+// 1 / (1 + exp(-x)) with the fast exponential and division; exp overflow gives 1 / inf = 0, never NaN
+__device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+
 // sigmoid(x) = 0.5 * tanh(0.5 x) + 0.5 with the hardware tanh: one special-function instruction instead of two
-// (exponential and reciprocal); the epilogues that use it are bound by that unit.  Relative error about 2^-11, below
-// the rounding of the 16-bit tensors it feeds; saturates cleanly at 0 and 1.
-__device__ __forceinline__ float sigmoid_fast(float x) {
+// (exponential and reciprocal).  Relative error about 2^-11, below the rounding of the 16-bit tensors it feeds.  Used in
+// the forward epilogue; the down-dgrad epilogue measured slower with it and keeps sigmoid_fast.
+__device__ __forceinline__ float sigmoid_tanh(float x) {
     float t;
     asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
     return fmaf(0.5f, t, 0.5f);
@@ -274,17 +272,14 @@ __device__ __forceinline__ void decode_tile(const UmmaParams& p, const Tables& t
 
 // ---- epilogue of one tile ------------------------------------------------------------------------
 // Runs in the epilogue warps.  `taddr` addresses this warp's 32 TMEM lanes of the tile's accumulator, `q` is the
-// lane quarter, `half` selects which half of the tile's columns this warp handles, `stage_store(slot, map, c0, c1, c2,
+// lane quarter, `half` selects which half of the tile's columns this warp handles, `stage_store(map, c0, c1, c2,
 // packed[16])` sends one 32 x 32 box of 16-bit values to the output through shared memory and TMA.
-// F16 (fp16 rather than bf16 tensors) is a template argument: the conversions then compile to straight-line code; as a
-// run-time flag every pack / unpack / rounding was its own branch, which kept the compiler from interleaving the
-// independent elements of a chunk and made the arithmetic of the down-dgrad epilogue as long as its main loop.
-template <int EPI, bool F16, class StageStore>
+template <int EPI, class StageStore>
 __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& ti, uint32_t taddr, int q, int half, int lane,
                                               const CUtensorMap* mo, const CUtensorMap* mo2, const CUtensorMap* mo3,
                                               StageStore& stage_store) {
     const int r = q * 32 + lane;  // row of the tile this thread owns
-    constexpr int is_f16 = F16 ? 1 : 0;
+    const int is_f16 = p.is_f16;
     const bool have_acc = ti.ksteps > 0;
 
     if (EPI == EPI_STORE) {
@@ -306,7 +301,7 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
                 }
 #pragma unroll
                 for (int i = 0; i < 16; ++i) pk[i] = pack2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]), is_f16);
-                stage_store(0, mo, n0 + c, row_c, ti.e, pk);
+                stage_store(mo, n0 + c, row_c, ti.e, pk);
             }
         } else {
             bool row_ok = r < ti.rows_valid;
@@ -362,11 +357,11 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
                 hg[i] = pack2(__uint_as_float(gt[2 * i]), __uint_as_float(gt[2 * i + 1]), is_f16);
                 // the activation sees the values as stored (rounded to the tensor type)
                 float2 fu = unpack2(hu[i], is_f16), fg = unpack2(hg[i], is_f16);
-                av[i] = pack2(fu.x * gate_value(ACT, fg.x, sigmoid_fast(fg.x)), fu.y * gate_value(ACT, fg.y, sigmoid_fast(fg.y)), is_f16);
+                av[i] = pack2(fu.x * gate_value(ACT, fg.x, sigmoid_tanh(fg.x)), fu.y * gate_value(ACT, fg.y, sigmoid_tanh(fg.y)), is_f16);
             }
-            stage_store(0, mo, n0 + c, row_c, 0, hu);    // up half of h
-            stage_store(1, mo3, n0 + c, row_c, 0, hg);   // gate half of h (its own map: columns clip at I)
-            stage_store(2, mo2, n0 + c, row_c, 0, av);   // activation
+            stage_store(mo, n0 + c, row_c, 0, hu);    // up half of h
+            stage_store(mo3, n0 + c, row_c, 0, hg);   // gate half of h (its own map: columns clip at I)
+            stage_store(mo2, n0 + c, row_c, 0, av);   // activation
         }
     } else if (EPI == EPI_ROUTER) {
         // Router: the tile's columns are the experts.  One thread owns one token row: it rounds the logits to the
@@ -472,23 +467,17 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
         if (slot >= 0) g = p.scale ? load_scalar(p.scale, slot, is_f16) : 1.f;
         const uint8_t* hrow = (const uint8_t*)p.h + (prow * 2 * (int64_t)I + n0) * 2;
         float dot = 0.f;
-        // the pre-activation values of this row are requested one column chunk ahead, so that their latency (they
-        // stream from HBM, one 16-byte piece per thread and request) runs under the arithmetic of the chunk before
-        uint4 hu4[4], hg4[4];
-        auto load_h = [&](int c, uint4 (&hu)[4], uint4 (&hg)[4]) {
-#pragma unroll
-            for (int qd = 0; qd < 4; ++qd) {
-                bool in = c < (half + 1) * (BN / 2) && n0 + c + qd * 8 < I;
-                hu[qd] = in ? *reinterpret_cast<const uint4*>(hrow + (c + qd * 8) * 2) : make_uint4(0, 0, 0, 0);
-                hg[qd] = in ? *reinterpret_cast<const uint4*>(hrow + ((int64_t)I + c + qd * 8) * 2) : make_uint4(0, 0, 0, 0);
-            }
-        };
-        load_h(half * (BN / 2), hu4, hg4);
 #pragma unroll 1
         for (int c = half * (BN / 2); c < (half + 1) * (BN / 2); c += 32) {
             if (n0 + c >= I) break;
-            uint4 hu_next[4], hg_next[4];
-            load_h(c + 32, hu_next, hg_next);
+            // the pre-activation values of this row: requested before the accumulator is read
+            uint4 hu4[4], hg4[4];
+#pragma unroll
+            for (int qd = 0; qd < 4; ++qd) {
+                bool in = n0 + c + qd * 8 < I;
+                hu4[qd] = in ? *reinterpret_cast<const uint4*>(hrow + (c + qd * 8) * 2) : make_uint4(0, 0, 0, 0);
+                hg4[qd] = in ? *reinterpret_cast<const uint4*>(hrow + ((int64_t)I + c + qd * 8) * 2) : make_uint4(0, 0, 0, 0);
+            }
             uint32_t u[32], du[16], dg[16], ag[16];
             tc_ld32(taddr + c, u);
             tc_wait_ld();
@@ -502,44 +491,20 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
                     float u0 = __uint_as_float(u[qd * 8 + 2 * i]), u1 = __uint_as_float(u[qd * 8 + 2 * i + 1]);
                     float s0 = sigmoid_fast(gt.x), s1 = sigmoid_fast(gt.y);
                     float m0 = gate_value(ACT, gt.x, s0), m1 = gate_value(ACT, gt.y, s1);
-                    // activation and scaled upstream gradient stay in fp32 here (the eager module rounds both to the
-                    // tensor type; the conversions are special-function-unit work this epilogue has no room for)
-                    float a0 = up.x * m0, a1 = up.y * m1;
+                    float a0 = round_elem(up.x * m0, is_f16), a1 = round_elem(up.y * m1, is_f16);
                     dot += a0 * u0 + a1 * u1;
-                    float d0 = g * u0, d1 = g * u1;
+                    float d0 = round_elem(g * u0, is_f16), d1 = round_elem(g * u1, is_f16);
                     du[qd * 4 + i] = pack2(d0 * m0, d1 * m1, is_f16);
                     dg[qd * 4 + i] = pack2(d0 * up.x * gate_slope(ACT, gt.x, s0), d1 * up.y * gate_slope(ACT, gt.y, s1), is_f16);
                     ag[qd * 4 + i] = pack2(g * a0, g * a1, is_f16);
                 }
             }
-            stage_store(0, mo, n0 + c, row_c, 0, du);    // up half of dh
-            stage_store(1, mo3, n0 + c, row_c, 0, dg);   // gate half of dh
-            stage_store(2, mo2, n0 + c, row_c, 0, ag);   // gate-scaled activation
-#pragma unroll
-            for (int qd = 0; qd < 4; ++qd) {
-                hu4[qd] = hu_next[qd];
-                hg4[qd] = hg_next[qd];
-            }
+            stage_store(mo, n0 + c, row_c, 0, du);    // up half of dh
+            stage_store(mo3, n0 + c, row_c, 0, dg);   // gate half of dh
+            stage_store(mo2, n0 + c, row_c, 0, ag);   // gate-scaled activation
         }
         if (slot >= 0) atomicAdd(p.d_gates + slot, dot);
     }
-}
-
-// Down-dgrad epilogue: ask L2 for the pre-activation values a warp will read for a tile (its 32 rows, its half of the
-// tile's columns, both halves of h) as one contiguous piece per row.  The epilogue itself reads them 64 bytes per row and
-// column chunk, microseconds apart; without the request every such read opens its own DRAM page.
-template <int EPI>
-__device__ __forceinline__ void epilogue_prefetch(const UmmaParams& p, const Tile& ti, int q, int half, int lane) {
-    if (!epi_gated_dgrad(EPI)) return;
-    const int I = p.N;
-    const int c0 = ti.nb * BN + half * (BN / 2);
-    const int cols = min(BN / 2, I - c0);
-    if (cols <= 0 || ti.rows_valid <= 0) return;
-    const int64_t prow = ti.row0 + q * 32 + lane;
-    const uint8_t* up = (const uint8_t*)p.h + (prow * 2 * (int64_t)I + c0) * 2;
-    const uint32_t bytes = (uint32_t)cols * 2u;
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(up), "r"(bytes) : "memory");
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(up + (int64_t)I * 2), "r"(bytes) : "memory");
 }
 
 // ---- host helpers (defined in umma_gemm.cu) ---------------------------------------------------------

@@ -445,7 +445,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const uint32_t stg = smem_u32(smem_stg + (warp - 6) * STG_BYTES);
         const uint32_t stg_row = stg + lane * 64;
         const uint32_t stg_swz = (uint32_t)((lane >> 1) & 3);
-        auto stage_store = [&](int /*slot: one box per warp here*/, const CUtensorMap* map, int c0, int c1, int c2, const uint32_t (&pk)[16]) {
+        auto stage_store = [&](const CUtensorMap* map, int c0, int c1, int c2, const uint32_t (&pk)[16]) {
             if (lane == 0) bulk_wait_read0();
             __syncwarp();
 #pragma unroll
@@ -470,11 +470,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status, 205, 200)) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
-            if (p.is_f16) {
-                epilogue_tile<EPI, true>(p, ti, taddr, q, half, lane, &tmap_o, &tmap_o2, &tmap_o3, stage_store);
-            } else {
-                epilogue_tile<EPI, false>(p, ti, taddr, q, half, lane, &tmap_o, &tmap_o2, &tmap_o3, stage_store);
-            }
+            epilogue_tile<EPI>(p, ti, taddr, q, half, lane, &tmap_o, &tmap_o2, &tmap_o3, stage_store);
             tc_fence_before();
             mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
             if (++acc == 2) {
