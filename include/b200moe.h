@@ -274,6 +274,12 @@ int b200moe_ep_pull_combine(const void* const* peer_ptrs, const int64_t* inv, co
                             const int32_t* base, int R, const void* gates, void* out, int64_t ldo, void* expanded,
                             int64_t T, int k, int width, int dtype, b200moe_stream_t stream);
 
+/* Gate gradient of the return path: d_gates[t, j] = <expanded[t*k + j, :], grad[t, :]> (fp32 accumulation, stored in the
+ * tensor type), expanded (T*k x width) being the unweighted rows b200moe_ep_pull_combine kept.  Replaces the bmm of
+ * SMT/ops.py:204 on the rank that owns the tokens. */
+int b200moe_ep_gate_grad(const void* expanded, int64_t lde, const void* grad, int64_t ldg, void* d_gates, int64_t T, int k,
+                         int width, int dtype, b200moe_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Fused router (the step before the path): replaces `_compute_routing_weights` + `_get_topk`
  * (cute_kernels/kernels/scattermoe/torch_implementation.py:120-133,193-199) and the histogram of the selected experts

@@ -88,6 +88,36 @@ __global__ void ep_pull_combine_kernel(PeerTable peers, const int64_t* __restric
     }
 }
 
+// d_gates[t, j] = <expanded[t*k + j, :], grad[t, :]> in fp32: the gate gradient of the return path, one block per token
+// (the gradient row is read once for the k products).  Replaces the batched (k x H)(H x 1) products of
+// cute_kernels/kernels/scattermoe/triton_implementation/ops.py:204, which run far below the HBM rate as a library bmm.
+template <typename T, int V>
+__global__ void gate_grad_kernel(const T* __restrict__ expanded, int64_t lde, const T* __restrict__ grad, int64_t ldg,
+                                 T* __restrict__ d_gates, int64_t Tn, int k, int width) {
+    int64_t t = blockIdx.x;
+    if (t >= Tn) return;
+    __shared__ float red[8];
+    for (int j = 0; j < k; ++j) {
+        const T* row = expanded + (t * k + j) * lde;
+        float acc = 0.f;
+        for (int col = threadIdx.x * V; col < width; col += blockDim.x * V) {
+            Pack<T, V> a = *reinterpret_cast<const Pack<T, V>*>(row + col);
+            Pack<T, V> g = *reinterpret_cast<const Pack<T, V>*>(grad + t * ldg + col);
+#pragma unroll
+            for (int i = 0; i < V; ++i) acc += Elem<T>::to_f(a.v[i]) * Elem<T>::to_f(g.v[i]);
+        }
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        __syncthreads();  // red may still be read for the previous slot
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float s = 0.f;
+            for (int w = 0; w < (int)(blockDim.x >> 5); ++w) s += red[w];
+            d_gates[t * k + j] = Elem<T>::from_f(s);
+        }
+    }
+}
+
 int fill_peers(PeerTable& tab, const void* const* peer_ptrs, int R, const char* what) {
     B200MOE_REQUIRE(R >= 1 && R <= kMaxRanks && peer_ptrs, B200MOE_ERR_ARG, "%s: bad rank count or NULL peer table", what);
     for (int i = 0; i < R; ++i) {
@@ -167,4 +197,27 @@ extern "C" int b200moe_ep_pull_combine(const void* const* peer_ptrs, const int64
     }
     count_launch();
     return check_launch("ep_pull_combine");
+}
+
+extern "C" int b200moe_ep_gate_grad(const void* expanded, int64_t lde, const void* grad, int64_t ldg, void* d_gates, int64_t T_,
+                                    int k, int width, int dtype, b200moe_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    B200MOE_REQUIRE(T_ >= 0 && width > 0 && k > 0, B200MOE_ERR_ARG, "ep_gate_grad: bad sizes");
+    if (T_ == 0) return B200MOE_OK;
+    B200MOE_REQUIRE(expanded && grad && d_gates, B200MOE_ERR_ARG, "ep_gate_grad: NULL pointer");
+    B200MOE_REQUIRE(dtype == B200MOE_BF16 || dtype == B200MOE_F16 || dtype == B200MOE_F32, B200MOE_ERR_DTYPE, "ep_gate_grad: dtype");
+    int esz = dtype == B200MOE_F32 ? 4 : 2, V = 16 / esz;
+    B200MOE_REQUIRE(width % V == 0 && lde % V == 0 && ldg % V == 0 && ((uintptr_t)expanded & 15) == 0 && ((uintptr_t)grad & 15) == 0,
+                    B200MOE_ERR_LAYOUT, "ep_gate_grad: rows must be 16-byte aligned and a multiple of 16 bytes wide");
+    int threads = row_threads(width, V);
+    if (dtype == B200MOE_F32) {
+        gate_grad_kernel<float, 4><<<(unsigned)T_, threads, 0, stream>>>((const float*)expanded, lde, (const float*)grad, ldg, (float*)d_gates, T_, k, width);
+    } else if (dtype == B200MOE_BF16) {
+        gate_grad_kernel<__nv_bfloat16, 8><<<(unsigned)T_, threads, 0, stream>>>((const __nv_bfloat16*)expanded, lde, (const __nv_bfloat16*)grad, ldg,
+                                                                            (__nv_bfloat16*)d_gates, T_, k, width);
+    } else {
+        gate_grad_kernel<__half, 8><<<(unsigned)T_, threads, 0, stream>>>((const __half*)expanded, lde, (const __half*)grad, ldg, (__half*)d_gates, T_, k, width);
+    }
+    count_launch();
+    return check_launch("ep_gate_grad");
 }

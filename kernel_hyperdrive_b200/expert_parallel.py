@@ -249,6 +249,19 @@ def _pull_impl(xc: PeerExchange, name: str, gates, out, expanded, plan: "_Plan")
     )
 
 
+def _gate_grad(expanded: torch.Tensor, grad_y: torch.Tensor, k: int) -> torch.Tensor:
+    """d_gates (T, k): dot products of the kept expert rows with the output gradient of their token."""
+    from ._lib import check, dtype_code, lib, ptr, stream_ptr
+
+    T = grad_y.size(0)
+    d_gates = torch.empty(T, k, dtype=grad_y.dtype, device=grad_y.device)
+    check(
+        lib().b200moe_ep_gate_grad(ptr(expanded), expanded.stride(0), ptr(grad_y), grad_y.stride(0), ptr(d_gates), T, k, grad_y.size(1), dtype_code(grad_y), stream_ptr(grad_y.device)),
+        "ep_gate_grad",
+    )
+    return d_gates
+
+
 class _PeerDispatch(torch.autograd.Function):
     """Forward: every rank stores its routed rows into the owners' "x" buffers.  Backward: the owners publish the
     input gradients of the rows they received in "dx"; the source pulls them and sums the k slots of a token."""
@@ -306,7 +319,7 @@ class _PeerCombine(torch.autograd.Function):
         xc, plan = ctx.xc, ctx.plan
         T, k = gates.shape
         grad_y = grad_y.contiguous()
-        d_gates = torch.bmm(expanded.view(T, k, -1), grad_y.unsqueeze(2)).squeeze(-1).to(gates.dtype)
+        d_gates = _gate_grad(expanded, grad_y, k)
         _push(xc, "dy", grad_y, plan.ss, k, gates.reshape(-1), plan)
         xc.barrier()  # all gradient rows have landed
         return xc.bufs["dy"][: plan.m_recv], d_gates, None, None

@@ -173,3 +173,20 @@ def test_tma_row_gather_engine(E, k, T, K, N):
         sm._wgrad(X, row_token, Q, None, offs, dw, cap)
         grads.append(dw)
     assert torch.isfinite(grads[1]).all() and rel_l2(grads[1], grads[0]) < 1e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("T,k,H", [(1, 1, 8), (333, 2, 512), (64, 6, 2048), (0, 2, 64)])
+def test_gate_grad_row_dots(dtype, T, k, H):
+    """Gate gradient of the expert-parallel return path: row dots against the bmm of the reference
+    (cute_kernels/kernels/scattermoe/triton_implementation/ops.py:204)."""
+    from kernel_hyperdrive_b200.expert_parallel import _gate_grad
+
+    torch.manual_seed(T + k)
+    expanded = torch.randn(T * k, H, device="cuda").to(dtype)
+    grad = torch.randn(T, H, device="cuda").to(dtype)
+    got = _gate_grad(expanded, grad, k)
+    assert got.shape == (T, k) and got.dtype == dtype
+    want = torch.bmm(expanded.float().view(T, k, H), grad.float().unsqueeze(2)).squeeze(-1)
+    if T:
+        assert rel_l2(got, want) <= tolerance(dtype)
