@@ -180,6 +180,7 @@ class PeerExchange:
             self.peer_ptrs[name] = (ctypes.c_void_p * self.world)(*[int(p) for p in hdl.buffer_ptrs])
         self._barrier_handle = self._handles["x"]
         self.backward_reads_pending = False
+        self.host_rows = torch.empty(1, dtype=torch.int64).pin_memory()  # landing place of the per-pass host read
 
     def barrier(self) -> None:
         self._barrier_handle.barrier(channel=0)
@@ -188,10 +189,26 @@ class PeerExchange:
 class _Plan:
     """Where this rank's sorted rows go: computed once per pass from the all-gathered expert counts."""
 
-    __slots__ = ("ss", "inv", "start", "base", "m_recv", "local_ids", "k")
+    __slots__ = ("ss", "inv", "start", "base", "m_recv", "local_ids", "k", "_recv_counts", "_host", "_event", "_e_local", "_world")
+
+    def resolve(self) -> None:
+        """Finish the plan with the one host read of the pass (the number of rows this rank receives sizes its local
+        tensors).  The copy was queued when the plan was made, before the dispatch kernel; called after that kernel and
+        its barrier are queued, the read returns while the GPU is still busy with them, so the device never waits for
+        the host to catch up."""
+        if self.m_recv is not None:
+            return
+        self._event.synchronize()
+        self.m_recv = int(self._host.item())
+        global last_received_rows
+        last_received_rows = self.m_recv
+        dev = self._recv_counts.device
+        self.local_ids = torch.repeat_interleave(
+            torch.arange(self._e_local, device=dev).repeat(self._world), self._recv_counts.reshape(-1).long(), output_size=self.m_recv
+        )
 
 
-def _make_plan(selected_experts, num_experts: int, world: int, rank: int, group, ops) -> "_Plan":
+def _make_plan(selected_experts, num_experts: int, world: int, rank: int, group, ops, host_rows=None) -> "_Plan":
     T, k = selected_experts.shape
     e_local = num_experts // world
     plan = _Plan()
@@ -207,12 +224,12 @@ def _make_plan(selected_experts, num_experts: int, world: int, rank: int, group,
     plan.start = torch.cat([zero, to_rank[rank].cumsum(0)]).to(torch.int32)
     plan.base = (to_rank.cumsum(0) - to_rank)[rank].to(torch.int32)  # rows of lower-ranked sources in each destination
     recv_counts = counts_all[:, rank * e_local : (rank + 1) * e_local]
-    plan.m_recv = int(recv_counts.sum().item())  # the one host read of the pass: sizes the local expert tensors
-    global last_received_rows
-    last_received_rows = plan.m_recv
-    plan.local_ids = torch.repeat_interleave(
-        torch.arange(e_local, device=ss.device).repeat(world), recv_counts.reshape(-1).long(), output_size=plan.m_recv
-    )
+    plan._recv_counts, plan._e_local, plan._world = recv_counts, e_local, world
+    plan.m_recv, plan.local_ids = None, None
+    plan._host = host_rows if host_rows is not None else torch.empty(1, dtype=torch.int64).pin_memory()
+    plan._host.copy_(recv_counts.sum().to(torch.int64).reshape(1), non_blocking=True)
+    plan._event = torch.cuda.Event()
+    plan._event.record()
     return plan
 
 
@@ -278,6 +295,9 @@ class _PeerDispatch(torch.autograd.Function):
         xc.backward_reads_pending = torch.is_grad_enabled()
         _push(xc, "x", x.contiguous(), plan.ss, plan.k, None, plan)
         xc.barrier()  # all rows have landed
+        plan.resolve()
+        if plan.m_recv > xc.cap_rows:  # the push kernel skipped the rows that did not fit and raised status 301
+            raise RuntimeError(f"expert-parallel exchange buffer too small: {plan.m_recv} rows arrive, capacity {xc.cap_rows}")
         return xc.bufs["x"][: plan.m_recv]
 
     @staticmethod
@@ -330,9 +350,7 @@ def ep_experts_p2p(x, router_weights, selected_experts, num_experts: int, local_
     memory (see PeerExchange).  Same contract as `ep_experts`."""
     world, rank = xc.world, dist.get_rank(xc.group)
     with torch.no_grad():
-        plan = _make_plan(selected_experts, num_experts, world, rank, xc.group, ops)
-    if plan.m_recv > xc.cap_rows:
-        raise RuntimeError(f"expert-parallel exchange buffer too small: {plan.m_recv} rows arrive, capacity {xc.cap_rows}")
+        plan = _make_plan(selected_experts, num_experts, world, rank, xc.group, ops, xc.host_rows)
     recv = _PeerDispatch.apply(x, xc, plan)
     out_rows = local_experts_fn(recv, plan.local_ids)
     return _PeerCombine.apply(out_rows, router_weights.to(x.dtype), xc, plan)
