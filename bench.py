@@ -497,6 +497,16 @@ def run_micro():
         nbytes = (T * H + E * H + T * E + T * k) * 2 + T * k * 8
         out[f"router_{name}"] = {"fused_us": f * 1e3, "eager_us": e_ * 1e3, "fused_GB/s": nbytes / f / 1e6, "fused_TFLOP/s": 2 * T * H * E / f / 1e9}
         del x, wg
+    # gate gradient of the expert-parallel return path: row dots against the batched product of the reference
+    from kernel_hyperdrive_b200.expert_parallel import _gate_grad
+
+    T, k, H = 16384, 2, 4096
+    expanded = torch.randn(T * k, H, device="cuda", dtype=torch.bfloat16)
+    gy = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    f = timed(lambda: _gate_grad(expanded, gy, k))
+    e_ = timed(lambda: torch.bmm(expanded.view(T, k, -1), gy.unsqueeze(2)))
+    out["ep_gate_grad_16384x2x4096_bf16"] = {"us": f * 1e3, "GB/s": (T * k + T) * H * 2 / f / 1e6, "torch_bmm_us": e_ * 1e3}
+    del expanded, gy
     ids = torch.randint(0, 256, (1 << 20,), device="cuda")
     out["contiguous_count_1M_ids_256_bins"] = {"us": timed(lambda: kh.contiguous_count_cute(ids, 256)) * 1e3}
     out["route_1M_ids_256_experts"] = {"us": timed(lambda: kh.route(ids, 256, 8, True, True)) * 1e3}
