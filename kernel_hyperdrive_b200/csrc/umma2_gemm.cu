@@ -25,7 +25,11 @@ namespace {
 
 constexpr int STAGES2 = 6;
 constexpr int B_HALF_BYTES = (BN / 2) * BK * 2;  // 16 KB
-constexpr int NUM_THREADS2 = (2 + EPI_WARPS) * 32;  // 320: TMA warp, MMA warp, 8 epilogue warps
+// Epilogue warps per CTA: eight (two per TMEM lane quarter, 128 columns each), except for the down-dgrad epilogues, whose
+// per-element work makes a tile's epilogue as long as its main loop with eight warps (the epilogue is latency-bound:
+// about a quarter of an instruction per cycle and scheduler): twelve there, three per lane quarter with 96 / 96 / 64 columns.
+__host__ __device__ constexpr int epi_warps_of(int epi) { return epi_gated_dgrad(epi) ? 12 : 8; }
+__host__ __device__ constexpr int threads_of(int epi) { return (2 + epi_warps_of(epi)) * 32; }  // + TMA warp, MMA warp
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -135,7 +139,7 @@ __device__ __forceinline__ void decode_tile2(const UmmaParams& p, const Tables& 
 }
 
 template <int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(EPI), 1)
     umma2_grouped_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a,
                          const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_o,
                          const __grid_constant__ CUtensorMap tmap_o2, const __grid_constant__ CUtensorMap tmap_o3) {
@@ -145,7 +149,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
     uint8_t* smem_a = smem;
     uint8_t* smem_b = smem + STAGES2 * A_STAGE_BYTES;
     uint8_t* smem_stg = smem + STAGES2 * (A_STAGE_BYTES + B_HALF_BYTES);
-    uint64_t* bars = (uint64_t*)(smem_stg + EPI_WARPS * STG_BYTES);
+    constexpr int EW = epi_warps_of(EPI);
+    uint64_t* bars = (uint64_t*)(smem_stg + EW * STG_BYTES);
     uint64_t* full_bar = bars;                       // used in the leader only
     uint64_t* empty_bar = bars + STAGES2;            // one set per CTA
     uint64_t* tmem_full_bar = bars + 2 * STAGES2;    // one set per CTA
@@ -170,7 +175,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&tmem_full_bar[a]), 1);
-            mbar_init(smem_u32(&tmem_empty_bar[a]), 2 * EPI_WARPS);
+            mbar_init(smem_u32(&tmem_empty_bar[a]), 2 * EW);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -386,7 +391,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
     } else {
         // ---------------- epilogue (both CTAs, each on its own 128 rows) ----------------
         const int q = warp & 3;
-        const int half = (warp - 2) >> 2;
+        const int half = (warp - 2) >> 2;  // which part of the tile's columns this warp handles
+        // column range of a BN-wide epilogue: halves with eight warps; 96 / 96 / 64 columns with twelve
+        const int c_begin = EW == 8 ? half * (BN / 2) : half * 96;
+        const int c_end = EW == 8 ? c_begin + BN / 2 : (half == 2 ? BN : c_begin + 96);
         const uint32_t stg = smem_u32(smem_stg + (warp - 2) * STG_BYTES);
         const uint32_t stg_row = stg + lane * 64;
         const uint32_t stg_swz = (uint32_t)((lane >> 1) & 3);
@@ -417,7 +425,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
             // a CTA whose half of the cluster tile does not exist (odd number of row blocks) has nothing to write
             const bool live = p.wfam || ti.rows_valid > 0;
-            if (live) epilogue_tile<EPI>(p, ti, taddr, q, half, lane, &tmap_o, &tmap_o2, &tmap_o3, stage_store);
+            if (live) epilogue_tile<EPI>(p, ti, taddr, q, half, lane, &tmap_o, &tmap_o2, &tmap_o3, stage_store, c_begin, c_end);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));
@@ -442,20 +450,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS2, 1)
     }
 }
 
-constexpr int SMEM_BYTES2 =
-    1024 + STAGES2 * (A_STAGE_BYTES + B_HALF_BYTES) + EPI_WARPS * STG_BYTES + 128 + (int)sizeof(Tables) + 64;
+constexpr int smem_bytes2(int epi) {
+    return 1024 + STAGES2 * (A_STAGE_BYTES + B_HALF_BYTES) + epi_warps_of(epi) * STG_BYTES + 128 + (int)sizeof(Tables) + 64;
+}
 
 template <int EPI>
 int launch2(const UmmaParams& p, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mo2,
             const CUtensorMap& mo3, cudaStream_t stream) {
     auto kern = umma2_grouped_kernel<EPI>;
+    constexpr int SMEM_BYTES2 = smem_bytes2(EPI);
     cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES2);
     if (err != cudaSuccess) {
         set_error_detail("cudaFuncSetAttribute(smem=%d): %s", SMEM_BYTES2, cudaGetErrorString(err));
         return B200MOE_ERR_LAUNCH;
     }
     int grid = sm_count() & ~1;  // whole pairs
-    kern<<<grid, NUM_THREADS2, SMEM_BYTES2, stream>>>(p, ma, mb, mo, mo2, mo3);
+    kern<<<grid, threads_of(EPI), SMEM_BYTES2, stream>>>(p, ma, mb, mo, mo2, mo3);
     count_launch();
     return check_launch("umma2_grouped_kernel");
 }

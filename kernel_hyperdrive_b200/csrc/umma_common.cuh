@@ -277,7 +277,12 @@ __device__ __forceinline__ void decode_tile(const UmmaParams& p, const Tables& t
 template <int EPI, class StageStore>
 __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& ti, uint32_t taddr, int q, int half, int lane,
                                               const CUtensorMap* mo, const CUtensorMap* mo2, const CUtensorMap* mo3,
-                                              StageStore& stage_store) {
+                                              StageStore& stage_store, int c_begin = -1, int c_end = -1) {
+    // column range of this warp in BN-wide epilogues; the default is the half the warp's index names
+    if (c_begin < 0) {
+        c_begin = half * (BN / 2);
+        c_end = c_begin + BN / 2;
+    }
     const int r = q * 32 + lane;  // row of the tile this thread owns
     const int is_f16 = p.is_f16;
     const bool have_acc = ti.ksteps > 0;
@@ -468,7 +473,7 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
         const uint8_t* hrow = (const uint8_t*)p.h + (prow * 2 * (int64_t)I + n0) * 2;
         float dot = 0.f;
 #pragma unroll 1
-        for (int c = half * (BN / 2); c < (half + 1) * (BN / 2); c += 32) {
+        for (int c = c_begin; c < c_end; c += 32) {
             if (n0 + c >= I) break;
             // the pre-activation values of this row: requested before the accumulator is read
             uint4 hu4[4], hg4[4];
