@@ -64,6 +64,32 @@ def test_argument_errors_do_not_launch():
     assert lib.b200moe_launch_count() == before
 
 
+def test_argument_errors_of_the_steps_around_the_path():
+    """Router, RMSNorm and the gate-gradient kernel: bad arguments come back as codes, nothing is launched."""
+    import ctypes
+
+    lib = _lib.lib()
+    before = lib.b200moe_launch_count()
+    f32 = ctypes.c_float(1e-5)
+    # router: fp32 tensors, too many experts, k > 8, missing counts
+    assert lib.b200moe_router_forward(None, 64, None, 64, 4, 64, 8, 2, 0, None, 8, None, None, None, _lib.DTYPE_CODE[torch.float32], None, None) == -2
+    assert lib.b200moe_router_forward(None, 64, None, 64, 4, 64, 257, 2, 0, None, 257, None, None, None, _lib.DTYPE_CODE[torch.bfloat16], None, None) == -6
+    assert lib.b200moe_router_forward(None, 64, None, 64, 4, 64, 8, 9, 0, None, 8, None, None, None, _lib.DTYPE_CODE[torch.bfloat16], None, None) == -6
+    assert lib.b200moe_router_forward(None, 64, None, 64, 4, 64, 8, 2, 3, None, 8, None, None, None, _lib.DTYPE_CODE[torch.bfloat16], None, None) == -1
+    assert b"router_forward" in lib.b200moe_last_error_detail()
+    # rmsnorm: unknown dtype, NULL pointers with rows > 0, weight gradient without weight; the workspace size is positive
+    assert lib.b200moe_rmsnorm_forward(None, 64, None, None, 64, None, 4, 64, f32, 9, None) == -2
+    assert lib.b200moe_rmsnorm_forward(None, 64, None, None, 64, None, 4, 64, f32, 1, None) == -1
+    assert lib.b200moe_rmsnorm_forward(None, 64, None, None, 64, None, 0, 64, f32, 1, None) == 0  # no rows: nothing to do
+    assert lib.b200moe_rmsnorm_backward(None, 64, None, None, 64, None, None, 64, ctypes.c_void_p(16), None, 0, 4, 64, f32, 1, None) == -1
+    assert lib.b200moe_rmsnorm_workspace_bytes(1000, 4096, 1) >= 4096 * 4
+    assert lib.b200moe_rmsnorm_workspace_bytes(-1, 4096, 1) == 0
+    # gate gradient
+    assert lib.b200moe_ep_gate_grad(None, 64, None, 64, None, 4, 2, 64, 1, None) == -1
+    assert lib.b200moe_ep_gate_grad(None, 64, None, 64, None, 0, 2, 64, 1, None) == 0
+    assert lib.b200moe_launch_count() == before
+
+
 def test_ops_refuse_cpu_tensors():
     with pytest.raises(RuntimeError, match="CUDA"):
         kh.contiguous_count_cute(torch.zeros(4, dtype=torch.long), 3)
