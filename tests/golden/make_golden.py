@@ -22,7 +22,9 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "..", ".."))
 sys.dont_write_bytecode = True
-sys.path.insert(0, os.environ.get("REFERENCE_ROOT", "/root/reference"))
+if "REFERENCE_ROOT" not in os.environ:
+    raise SystemExit("set REFERENCE_ROOT to a checkout of the reference (kernel-hyperdrive) before running this script")
+sys.path.insert(0, os.environ["REFERENCE_ROOT"])
 
 import cute_kernels.kernels.scattermoe.torch_implementation as ref_impl  # noqa: E402
 from cute_kernels.kernels.swiglu_unchunked.torch_implementation import swiglu_unchunked_torch  # noqa: E402
