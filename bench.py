@@ -302,12 +302,16 @@ def run_gpu_arm(args, w):
     # End-to-end loop as a host program would run it: inputs start in pinned host memory every step and the
     # results (layer output and input gradient) are read back to the host every step.  Copies run on their own
     # streams, double-buffered, so the upload of step i+1 and the read-back of step i-1 overlap the kernels of
-    # step i; every copy of every timed step lies inside the timed region.
+    # step i; every copy of every timed step lies inside the timed region.  The tokens are uploaded before the output
+    # gradient (the forward pass needs only the former) and the layer output is read back as soon as the forward pass
+    # has produced it, so that only half of a step's traffic is exposed when the pipeline fills and drains.
     copy_in, copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
     x_slots = [torch.empty(T, H, device=dev, dtype=dtype) for _ in range(2)]
     g_slots = [torch.empty(T, H, device=dev, dtype=dtype) for _ in range(2)]
     ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_in_g = [torch.cuda.Event() for _ in range(2)]
     ev_free = [torch.cuda.Event() for _ in range(2)]
+    ev_fwd = [torch.cuda.Event() for _ in range(2)]
     ev_done = [torch.cuda.Event() for _ in range(2)]
     keep = [None, None]
 
@@ -315,8 +319,9 @@ def run_gpu_arm(args, w):
         with torch.cuda.stream(copy_in):
             copy_in.wait_event(ev_free[slot])  # the step that last read this slot has finished
             x_slots[slot].copy_(x_host, non_blocking=True)
-            g_slots[slot].copy_(g_host, non_blocking=True)
             ev_in[slot].record(copy_in)
+            g_slots[slot].copy_(g_host, non_blocking=True)
+            ev_in_g[slot].record(copy_in)
 
     def run_e2e(steps):
         main = torch.cuda.current_stream(dev)
@@ -332,14 +337,18 @@ def run_gpu_arm(args, w):
                 p.grad = None
             x = x_slots[slot].detach().requires_grad_(True)
             y = forward(x)
+            ev_fwd[slot].record(main)
+            with torch.cuda.stream(copy_out):
+                copy_out.wait_event(ev_fwd[slot])
+                y_host.copy_(y.detach(), non_blocking=True)
+                y.record_stream(copy_out)
+            main.wait_event(ev_in_g[slot])
             y.backward(g_slots[slot])
             ev_free[slot].record(main)
             ev_done[slot].record(main)
             with torch.cuda.stream(copy_out):
                 copy_out.wait_event(ev_done[slot])
-                y_host.copy_(y.detach(), non_blocking=True)
                 dx_host.copy_(x.grad, non_blocking=True)
-                y.record_stream(copy_out)
                 x.grad.record_stream(copy_out)
             keep[slot] = (y, x)  # keep the device results alive until their read-back has been issued and ordered
         main.wait_stream(copy_out)
