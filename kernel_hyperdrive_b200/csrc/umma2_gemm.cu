@@ -25,10 +25,11 @@ namespace {
 
 constexpr int STAGES2 = 6;
 constexpr int B_HALF_BYTES = (BN / 2) * BK * 2;  // 16 KB
-// Epilogue warps per CTA: eight (two per TMEM lane quarter, 128 columns each), except for the down-dgrad epilogues, whose
-// per-element work makes a tile's epilogue as long as its main loop with eight warps (the epilogue is latency-bound:
-// about a quarter of an instruction per cycle and scheduler): twelve there, three per lane quarter with 96 / 96 / 64 columns.
-__host__ __device__ constexpr int epi_warps_of(int epi) { return epi_gated_dgrad(epi) ? 12 : 8; }
+// Epilogue warps per CTA: twelve (three per TMEM lane quarter with 96 / 96 / 64 columns) for the store and down-dgrad
+// epilogues (latency-bound work: about a quarter of an instruction per cycle and scheduler with eight warps; exposed when
+// the reduction loop of a tile is short), eight (two per lane quarter, 128 columns each) for the SwiGLU forward epilogue,
+// whose register count does not fit twelve.
+__host__ __device__ constexpr int epi_warps_of(int epi) { return (epi_gated_dgrad(epi) || epi == EPI_STORE) ? 12 : 8; }
 __host__ __device__ constexpr int threads_of(int epi) { return (2 + epi_warps_of(epi)) * 32; }  // + TMA warp, MMA warp
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {

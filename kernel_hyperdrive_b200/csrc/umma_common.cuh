@@ -294,7 +294,7 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
         if (via_tma) {
             const int row_c = p.wfam ? ti.mb * BM + q * 32 : ti.row0 + q * 32;
 #pragma unroll 1
-            for (int c = half * (BN / 2); c < (half + 1) * (BN / 2); c += 32) {
+            for (int c = c_begin; c < c_end; c += 32) {
                 if (n0 + c >= p.N) break;
                 uint32_t v[32], pk[16];
                 if (have_acc) {
@@ -318,7 +318,7 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
             if (row_ok && p.scale) sc = load_scalar(p.scale, dst, is_f16);
             uint8_t* orow = (uint8_t*)p.out + (dst * p.ldo + n0) * 2;
 #pragma unroll 1
-            for (int c = half * (BN / 2); c < (half + 1) * (BN / 2); c += 32) {
+            for (int c = c_begin; c < c_end; c += 32) {
                 uint32_t v[32];
                 if (have_acc) {
                     tc_ld32(taddr + c, v);
