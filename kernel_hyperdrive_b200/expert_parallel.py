@@ -59,6 +59,11 @@ class CudaRowOps:
         combine(expanded, gates, out, k)
         return out
 
+    @staticmethod
+    def gate_grad(expanded: torch.Tensor, grad: torch.Tensor, k: int) -> torch.Tensor:
+        """d_gates[t, j] = <expanded[t*k + j, :], grad[t, :]>."""
+        return _gate_grad(expanded, grad, k)
+
 
 class _AllToAllRows(torch.autograd.Function):
     """Variable-split row exchange; the backward is the same exchange with the splits swapped."""
@@ -111,7 +116,11 @@ class _UnsortCombine(torch.autograd.Function):
         expanded, gates, ss = ctx.saved_tensors
         T, k = gates.shape
         grad = grad.contiguous()
-        d_gates = torch.bmm(expanded.view(T, k, -1), grad.unsqueeze(2)).squeeze(-1).to(gates.dtype)
+        gate_grad = getattr(ctx.ops, "gate_grad", None)  # optional in injected row operations
+        if gate_grad is not None:
+            d_gates = gate_grad(expanded, grad, k).to(gates.dtype)
+        else:
+            d_gates = torch.bmm(expanded.view(T, k, -1), grad.unsqueeze(2)).squeeze(-1).to(gates.dtype)
         # gradient of row n (sorted order) = gates[ss[n]] * grad[ss[n] // k]
         d_rows = ctx.ops.gather(grad, ss, k, gates.reshape(-1).contiguous())
         return d_rows, d_gates, None, None, None
