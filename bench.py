@@ -249,6 +249,9 @@ def run_gpu_arm(args, w):
         dist.init_process_group("nccl", device_id=dev)
     dtype = synthetic.TORCH_DTYPES[w.dtype]
     E, k, H, I, T = w.num_experts, w.top_k, w.hidden, w.intermediate, w.tokens
+    _lib.set_option(_lib.OPT_TILE_VARIANT, {"table": -1, "pair": _lib.TILE_PAIR_256x256, "cta": _lib.TILE_CTA_128x256}[args.tile_variant])
+    if args.tile_scheduler is not None:
+        _lib.set_option(_lib.OPT_DYNAMIC_TILES, args.tile_scheduler)
     extra = dict(num_shared_experts=w.shared_experts, router_scoring="sigmoid" if w.routing == "sigmoid" else "softmax")
 
     if world > 1:
@@ -422,7 +425,7 @@ def run_gpu_arm(args, w):
         "frac_of_bf16_peak_sustained": value / world / peak,
         "clocks": clock_summary,
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": 2 * x_host.numel() * x_host.element_size(), "d2h_bytes_per_step": 2 * y_host.numel() * y_host.element_size()},
-        "gpu_launches": launches, **extra_info, **({"exchange_ms_per_step": exchange_ms} if exchange_ms else {}),
+        "gpu_launches": launches, "tile_variant": args.tile_variant, "tile_scheduler": _lib.get_option(_lib.OPT_DYNAMIC_TILES), **extra_info, **({"exchange_ms_per_step": exchange_ms} if exchange_ms else {}),
         "roofline": {
             "bound": "tensor", "kernel": "umma2_grouped_kernel (6 launches per step)", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
             "frac": (achieved / peak) if achieved else None, "peak_kind": f"bf16_tflops_sustained of {peak_kind}",
@@ -507,7 +510,7 @@ def run_micro():
         out[f"router_{name}"] = {"fused_us": f * 1e3, "eager_us": e_ * 1e3, "fused_GB/s": nbytes / f / 1e6, "fused_TFLOP/s": 2 * T * H * E / f / 1e9}
         del x, wg
     # gate gradient of the expert-parallel return path: row dots against the batched product of the reference
-    from kernel_hyperdrive_b200.expert_parallel import _gate_grad
+    from kernel_hyperdrive_b200.ops import gate_grad as _gate_grad
 
     T, k, H = 16384, 2, 4096
     expanded = torch.randn(T * k, H, device="cuda", dtype=torch.bfloat16)
@@ -533,6 +536,8 @@ def main():
     ap.add_argument("--cpu-sample-tokens", type=int, default=256)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ep-exchange", default="p2p", choices=["p2p", "nccl"], help="N > 1: row exchange by this package's kernels over peer memory, or NCCL all-to-all")
+    ap.add_argument("--tile-variant", default="table", choices=["table", "pair", "cta"], help="tensor-core tile: per-shape table (default), or force the two-CTA 256x256 / one-CTA 128x256 tile (A/B measurements)")
+    ap.add_argument("--tile-scheduler", type=int, default=None, choices=[0, 1, 2], help="two-CTA kernels: 2 = every launch draws its tiles from a counter, 1 = only the weight-gradient launches, 0 = fixed stride; default: the library's own setting")
     ap.add_argument("--micro", action="store_true", help="time the row kernels (SwiGLU operator, histogram, routing sort) instead of the layer")
     ap.add_argument("--profile", action="store_true", help="profiling run under ncu: exactly --warmup warm-up steps, no end-to-end and CPU legs; its numbers are not benchmark values")
     args = ap.parse_args()

@@ -55,6 +55,26 @@ extern "C" {
                                        * cp.async gather warps of the one-CTA kernel; measured about 3x slower, kept
                                        * for comparison */
 
+/* Options (b200moe_set_option).  Process-wide, meant for measurements and tests; the defaults are the product path. */
+#define B200MOE_OPT_DYNAMIC_TILES 1 /* two-CTA kernels: 2 = every launch draws its tiles from a per-launch counter, in
+                                     * list order (weight-gradient tiles longest reduction first); 1 = only the
+                                     * weight-gradient launches do; 0 = fixed stride everywhere */
+#define B200MOE_OPT_TILE_VARIANT 2  /* -1 (default): the per-shape tile table decides; otherwise a B200MOE_TILE_* value
+                                     * forced on every tensor-core launch whose operands allow it */
+#define B200MOE_OPT_COUNT 3
+
+/* Tiles of the tensor-core engine and the operations the tile table is keyed on (b200moe_tile_table_lookup).  The table
+ * plays the part of the reference's autotuner configurations, which are keyed on the same quantities
+ * (SMT/kernels.py:8-11,152-159: N, K), reduced to fixed entries measured on a B200. */
+#define B200MOE_TILE_PAIR_256x256 0 /* cluster of two CTAs, tcgen05.mma.cta_group::2, 256 x 256 x 64, six stages */
+#define B200MOE_TILE_CTA_128x256 1  /* one CTA, 128 x 256 x 64, four stages */
+#define B200MOE_TILE_COUNT 2
+#define B200MOE_OP_UP_FORWARD 0  /* gathered rows @ w_fc^T with the gated activation in the epilogue */
+#define B200MOE_OP_ROW_STORE 1   /* row GEMM with a plain / scattered store epilogue (down forward, up dgrad) */
+#define B200MOE_OP_DOWN_DGRAD 2  /* row GEMM with the activation backward in the epilogue */
+#define B200MOE_OP_WGRAD 3       /* per-expert weight gradient (reduction over the expert's rows) */
+#define B200MOE_OP_COUNT 4
+
 typedef void* b200moe_stream_t; /* cudaStream_t */
 
 int b200moe_version(void);
@@ -63,6 +83,12 @@ const char* b200moe_error_string(int code);
 const char* b200moe_last_error_detail(void);
 /* Process-wide engine choice; returns the previous value. */
 int b200moe_set_engine(int engine);
+/* Sets a B200MOE_OPT_* option; returns B200MOE_OK or B200MOE_ERR_ARG.  b200moe_get_option reads one back. */
+int b200moe_set_option(int option, int value);
+int b200moe_get_option(int option);
+/* The tile (B200MOE_TILE_*) the table assigns to operation `op` (B200MOE_OP_*) with reduction extent K (weight
+ * gradients: output rows), N output columns and about rows_per_expert rows per expert. */
+int b200moe_tile_table_lookup(int op, int K, int N, int64_t rows_per_expert);
 /* Number of kernels this library has launched since load (all streams); for launch accounting. */
 int64_t b200moe_launch_count(void);
 /* Reads the device status word (one int32 written by kernels that give up) after synchronising the
@@ -172,6 +198,17 @@ int b200moe_group(const void* A, int64_t lda, const int64_t* idx, void* out, int
 int b200moe_combine(const void* in, int64_t ldi, const void* gates, void* out, int64_t ldo, int64_t T,
                     int k, int H, int dtype, b200moe_stream_t stream);
 
+/* The same sum reading its rows through an index: out[t, :] = sum_j gates[t, j] * in[pos[t*k + j], :] (a negative
+ * index contributes nothing).  With pos = the padded grouped row of every slot (b200moe_invert_row_map) it forms the
+ * layer output / the input gradient straight from the grouped-order results of b200moe_down_forward / b200moe_up_dgrad,
+ * i.e. the un-sort of SMT/kernels.py:97-102 moves from the GEMM epilogue into this pass.  k <= 64. */
+int b200moe_combine_rows(const void* in, int64_t ldi, const int32_t* pos, const void* gates, void* out, int64_t ldo,
+                         int64_t T, int k, int H, int dtype, b200moe_stream_t stream);
+
+/* slot_row[row_slot[p]] = p for every real row p of the padded grouped order (row_slot from b200moe_route; `rows`
+ * entries, M slots).  No counterpart in the reference, whose kernels scatter through sorted_scattered_idxs. */
+int b200moe_invert_row_map(const int32_t* row_slot, int64_t rows, int32_t* slot_row, int64_t M, b200moe_stream_t stream);
+
 /* y[:, :h] = x[:, :h] * silu(x[:, h:]) on a (rows, 2h) tensor, and its gradient.  Replaces
  * swiglu_unchunked forward / backward
  * (cute_kernels/kernels/swiglu_unchunked/triton_implementation/kernels_forward.py:13-38,
@@ -205,36 +242,49 @@ int b200moe_gather_rows(const void* src, int64_t lds, const int32_t* row_map, vo
 
 /* Up projection with the token gather on the input rows and the gated activation in the epilogue:
  * h[p, :] = x[row_token[p], :] @ w_fc[e(p)]^T  (Mcap, 2I), a[p, :] = h[p, :I] * m(h[p, I:])  (Mcap, I).
+ * h is kept for b200moe_down_dgrad only and its column order is the engine's own (see there).
  * row_token == NULL: x already holds the padded grouped rows (m_cap rows, see b200moe_gather_rows).
  * Replaces scatter2scatter for c_fc plus the activation call (SMT/__init__.py:83-91). */
 int b200moe_up_forward(const void* x, int64_t ldx, const void* w_fc, const int64_t* expert_offsets,
                        const int32_t* row_token, void* h, void* a, int64_t T, int H, int I, int E,
                        int64_t m_cap, int activation, int dtype, int32_t* status, b200moe_stream_t stream);
 
-/* Down projection scattered back to (token, slot) order and scaled by the gate of that slot:
+/* Down projection, optionally scattered back to (token, slot) order and scaled by the gate of that slot:
  * y_expanded[s, :] = gates[s] * (a[p, :] @ w_proj[e(p)]^T), s = row_slot[p]; gates NULL means 1.
- * Replaces scatter2scatter for c_proj (SMT/__init__.py:92-100); b200moe_combine(gates = NULL) then gives
- * the layer output that SMT/ops.py:160-164 forms with bmm. */
+ * row_slot == NULL (gates NULL too): the rows stay in the padded grouped order, y_expanded[p, :] for all m_cap rows
+ * (zeros on filler rows), written by TMA; b200moe_combine_rows then un-sorts while it sums.
+ * Replaces scatter2scatter for c_proj (SMT/__init__.py:92-100).  The layer passes gates = NULL, keeps the unweighted
+ * rows for the gate gradient as the reference does (SMT/ops.py:163,173) and forms the output with
+ * b200moe_combine(gates), which is the bmm of SMT/ops.py:160-164. */
 int b200moe_down_forward(const void* a, const void* w_proj, const int64_t* expert_offsets,
                          const int32_t* row_slot, const void* gates, void* y_expanded, int64_t ldy,
                          int64_t M, int H, int I, int E, int64_t m_cap, int dtype, int32_t* status,
                          b200moe_stream_t stream);
 
-/* Input gradient of the down projection fused with the gate scaling, the backward of the gated activation
- * (`activation` as in b200moe_up_forward) and the gate gradient.
- * With u[p, :] = grad_out[row_token[p], :] @ w_proj[e(p)] (Mcap, I), act = h[:, :I]*m(h[:, I:]),
- * g = gates[row_slot[p]]:
- *   d_gates[row_slot[p]] = <act[p, :], u[p, :]>          (fp32, M entries, overwritten)
- *   dh[p, :] = activation backward of h[p, :] for upstream g*u[p, :]   (Mcap, 2I)
- *   ag[p, :] = g * act[p, :]                                        (Mcap, I)
- * row_token == NULL: grad_out already holds the padded grouped rows (m_cap rows).
- * Replaces, for c_proj: the d_gates bmm, group(coeff=gates), scatter2scatter (SMT/ops.py:204-256) and the
- * activation backward between the two projections
- * (cute_kernels/kernels/swiglu_unchunked/triton_implementation/kernels_backward.py:13-48). */
-int b200moe_down_dgrad(const void* grad_out, int64_t ldg, const void* w_proj, const int64_t* expert_offsets,
-                       const int32_t* row_token, const int32_t* row_slot, const void* gates, const void* h,
-                       void* dh, void* ag, float* d_gates, int64_t M, int H, int I, int E, int64_t m_cap,
-                       int activation, int dtype, int32_t* status, b200moe_stream_t stream);
+/* Upstream gradient rows of the backward pass in the padded grouped order, scaled by the gate of their slot, and
+ * the gate gradient, in one pass over grad_out:
+ *   out[p, :]  = gates[s] * grad_out[t, :]  with s = row_slot[p], t = row_token[p]; zeros on filler rows; gates NULL: 1
+ *   d_gates[s] = <y_expanded[s, :], grad_out[t, :]>   fp32 (M entries); y_expanded (the unweighted expert outputs the
+ *                forward kept: M x width in (token, slot) order, or with y_grouped != 0 rows x width in the padded
+ *                grouped order, row p then belongs to slot row_slot[p]) and d_gates are given together or both NULL
+ * Replaces `group(grad_out, coeff=gates)` and the d_gates bmm of the c_proj backward (SMT/ops.py:200-222).  Every
+ * dot product is summed in a fixed order, so the gate gradient is reproducible from run to run. */
+int b200moe_gather_grad_rows(const void* grad_out, int64_t ldg, const int32_t* row_token, const int32_t* row_slot,
+                             const void* gates, const void* y_expanded, int64_t ldy, int y_grouped, void* out,
+                             int64_t ldo, float* d_gates, int64_t rows, int width, int dtype, b200moe_stream_t stream);
+
+/* Input gradient of the down projection fused with the backward of the gated activation (`activation` as in
+ * b200moe_up_forward).  grad_rows holds the gate-scaled upstream gradient rows in the padded grouped order (m_cap
+ * rows, from b200moe_gather_grad_rows); with row_token given it holds T token rows instead and the kernel gathers
+ * them (no gate scaling then).  With d[p, :] = grad_rows[p, :] @ w_proj[e(p)] rounded to the tensor type (Mcap, I):
+ *   dh[p, :] = activation backward of h[p, :] for upstream d[p, :]   (Mcap, 2I), plain (up | gate) column order
+ * h is the buffer b200moe_up_forward wrote IN THE SAME ENGINE: the tensor-core engine stores it interleaved per
+ * 32-column chunk (up part, gate part), the CUDA-core engine as (up | gate); treat it as opaque between the two calls.
+ * Replaces scatter2scatter of the c_proj backward (SMT/ops.py:247-256) and the activation backward between the two
+ * projections (cute_kernels/kernels/swiglu_unchunked/triton_implementation/kernels_backward.py:13-48). */
+int b200moe_down_dgrad(const void* grad_rows, int64_t ldg, const void* w_proj, const int64_t* expert_offsets,
+                       const int32_t* row_token, const void* h, void* dh, int64_t T, int H, int I, int E,
+                       int64_t m_cap, int activation, int dtype, int32_t* status, b200moe_stream_t stream);
 
 /* Weight gradient of one projection, written in the layout the module stores weights in:
  * DW[e, o, i] = sum over rows p of expert e of P[pmap(p), o] * Q[qmap(p), i], DW (E, n_out, n_in) contiguous.
@@ -247,6 +297,7 @@ int b200moe_wgrad(const void* P, int64_t ldp, const int32_t* p_map, const void* 
 
 /* Input gradient of the up projection scattered to (token, slot) order:
  * dx_expanded[row_slot[p], :] = dh[p, :] @ w_fc[e(p)]   (M, H); b200moe_combine then sums over the slots.
+ * row_slot == NULL: dx_expanded[p, :] in the padded grouped order (m_cap rows), for b200moe_combine_rows.
  * Replaces scatter2scatter in the c_fc backward and the sum over k (SMT/ops.py:247-261). */
 int b200moe_up_dgrad(const void* dh, const void* w_fc, const int64_t* expert_offsets, const int32_t* row_slot,
                      void* dx_expanded, int64_t ldd, int64_t M, int H, int I, int E, int64_t m_cap, int dtype,
@@ -273,6 +324,14 @@ int b200moe_ep_push_rows(const void* src, int64_t lds, const int64_t* idx, int f
 int b200moe_ep_pull_combine(const void* const* peer_ptrs, const int64_t* inv, const int32_t* start,
                             const int32_t* base, int R, const void* gates, void* out, int64_t ldo, void* expanded,
                             int64_t T, int k, int width, int dtype, b200moe_stream_t stream);
+
+/* Rank barrier on the stream, over a symmetric flag array: flag_ptrs is a HOST array of R device pointers, entry d being
+ * rank d's array of R int32 words (zero before the first barrier), mapped into this process.  `epoch` is the number of
+ * this barrier (1, 2, 3, ... the same on every rank).  The kernel publishes the epoch to every peer and waits, for at most
+ * limit_cycles SM cycles, until every peer has published it; when a peer does not arrive it writes 302 to the status word
+ * and returns (b200moe_check_status then reports B200MOE_ERR_DEVICE), it never traps.  R <= 64. */
+int b200moe_ep_barrier(const void* const* flag_ptrs, int rank, int R, int epoch, int64_t limit_cycles, int32_t* status,
+                       b200moe_stream_t stream);
 
 /* Gate gradient of the return path: d_gates[t, j] = <expanded[t*k + j, :], grad[t, :]> (fp32 accumulation, stored in the
  * tensor type), expanded (T*k x width) being the unweighted rows b200moe_ep_pull_combine kept.  Replaces the bmm of

@@ -22,18 +22,27 @@ HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(PKG_DIR, "..", "includ
 
 F32, BF16, F16 = 0, 1, 2
 ENGINE_AUTO, ENGINE_SIMT, ENGINE_UMMA, ENGINE_UMMA_1CTA, ENGINE_UMMA_GATHER4 = 0, 1, 2, 3, 4
+OPT_DYNAMIC_TILES, OPT_TILE_VARIANT = 1, 2
+TILE_PAIR_256x256, TILE_CTA_128x256 = 0, 1
+OP_UP_FORWARD, OP_ROW_STORE, OP_DOWN_DGRAD, OP_WGRAD = 0, 1, 2, 3
 DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
 
 _lock = threading.Lock()
 _lib = None
 
 
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
+OBJ_DIR = os.path.join(PKG_DIR, "build")
+
+
+def _nvcc() -> str:
+    return os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
+
+
 def nvcc_command(out: str = LIB_PATH, extra: list[str] | None = None) -> list[str]:
-    nvcc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
-    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared", "--expt-relaxed-constexpr"]
-    cmd += extra or []
-    cmd += ["-o", out] + [os.path.join(CSRC, s) for s in SOURCES]
-    return cmd
+    """The one-command form of the build (every source in one nvcc call); `build()` runs the same flags per source in
+    parallel and links the objects."""
+    return [_nvcc()] + NVCC_FLAGS + ["-shared"] + (extra or []) + ["-o", out] + [os.path.join(CSRC, s) for s in SOURCES]
 
 
 def needs_build() -> bool:
@@ -45,15 +54,38 @@ def needs_build() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile the library in-tree for sm_100a.  Returns the path of the shared object."""
+    """Compile the library in-tree for sm_100a: one nvcc process per source file, run concurrently, then one link.
+    Returns the path of the shared object."""
     if force or needs_build():
-        tmp = LIB_PATH + f".tmp{os.getpid()}"
-        proc = subprocess.run(nvcc_command(tmp, ["-Xptxas", "-v"] if verbose else None), capture_output=True, text=True)
-        if proc.returncode != 0:
-            raise RuntimeError("nvcc failed:\n" + proc.stdout + proc.stderr)
-        os.replace(tmp, LIB_PATH)
+        os.makedirs(OBJ_DIR, exist_ok=True)
+        tag = f".tmp{os.getpid()}"
+        extra = ["-Xptxas", "-v"] if verbose else []
+        jobs = []
+        for src in SOURCES:
+            obj = os.path.join(OBJ_DIR, src + tag + ".o")
+            cmd = [_nvcc()] + NVCC_FLAGS + extra + ["-c", "-o", obj, os.path.join(CSRC, src)]
+            jobs.append((src, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+        logs, failed = [], []
+        for src, obj, proc in jobs:
+            out, _ = proc.communicate()
+            logs.append(f"== {src}\n{out}")
+            if proc.returncode != 0:
+                failed.append(src)
+        objs = [obj for _, obj, _ in jobs]
+        try:
+            if failed:
+                raise RuntimeError("nvcc failed for " + ", ".join(failed) + ":\n" + "\n".join(logs))
+            tmp = LIB_PATH + tag
+            proc = subprocess.run([_nvcc(), "-shared", "-o", tmp] + objs, capture_output=True, text=True)
+            if proc.returncode != 0:
+                raise RuntimeError("link failed:\n" + proc.stdout + proc.stderr)
+            os.replace(tmp, LIB_PATH)
+        finally:
+            for obj in objs:
+                if os.path.exists(obj):
+                    os.remove(obj)
         if verbose:
-            print(proc.stderr)
+            print("\n".join(logs))
     return LIB_PATH
 
 
@@ -65,6 +97,9 @@ def _declare(lib):
         "b200moe_error_string": (c.c_char_p, [i32]),
         "b200moe_last_error_detail": (c.c_char_p, []),
         "b200moe_set_engine": (i32, [i32]),
+        "b200moe_set_option": (i32, [i32, i32]),
+        "b200moe_get_option": (i32, [i32]),
+        "b200moe_tile_table_lookup": (i32, [i32, i32, i32, i64]),
         "b200moe_launch_count": (i64, []),
         "b200moe_check_status": (i32, [vp, vp]),
         "b200moe_selftest_bounded_wait": (i32, [vp, i64, vp, vp]),
@@ -84,10 +119,14 @@ def _declare(lib):
         "b200moe_swiglu_unchunked_backward": (i32, [vp, i64, vp, i64, vp, i64, i64, i32, i32, vp]),
         "b200moe_up_forward": (i32, [vp, i64, vp, vp, vp, vp, vp, i64, i32, i32, i32, i64, i32, i32, vp, vp]),
         "b200moe_down_forward": (i32, [vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, i64, i32, vp, vp]),
-        "b200moe_down_dgrad": (i32, [vp, i64, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i64, i32, i32, vp, vp]),
+        "b200moe_gather_grad_rows": (i32, [vp, i64, vp, vp, vp, vp, i64, i32, vp, i64, vp, i64, i32, i32, vp]),
+        "b200moe_combine_rows": (i32, [vp, i64, vp, vp, vp, i64, i64, i32, i32, i32, vp]),
+        "b200moe_invert_row_map": (i32, [vp, i64, vp, i64, vp]),
+        "b200moe_down_dgrad": (i32, [vp, i64, vp, vp, vp, vp, vp, i64, i32, i32, i32, i64, i32, i32, vp, vp]),
         "b200moe_wgrad": (i32, [vp, i64, vp, vp, i64, vp, vp, vp, i32, i32, i32, i64, i32, vp, vp]),
         "b200moe_ep_push_rows": (i32, [vp, i64, vp, i32, vp, vp, vp, vp, i32, i64, i32, i64, i32, vp, vp]),
         "b200moe_ep_pull_combine": (i32, [vp, vp, vp, vp, i32, vp, vp, i64, vp, i64, i32, i32, i32, vp]),
+        "b200moe_ep_barrier": (i32, [vp, i32, i32, i32, i64, vp, vp]),
         "b200moe_ep_gate_grad": (i32, [vp, i64, vp, i64, vp, i64, i32, i32, i32, vp]),
         "b200moe_up_dgrad": (i32, [vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, i64, i32, vp, vp]),
         "b200moe_router_forward": (i32, [vp, i64, vp, i64, i64, i32, i32, i32, i32, vp, i64, vp, vp, vp, i32, vp, vp]),
@@ -169,6 +208,14 @@ def check_status(device: torch.device) -> None:
 
 def set_engine(engine: int) -> int:
     return lib().b200moe_set_engine(engine)
+
+
+def set_option(option: int, value: int) -> None:
+    check(lib().b200moe_set_option(option, value), "set_option")
+
+
+def get_option(option: int) -> int:
+    return lib().b200moe_get_option(option)
 
 
 def launch_count() -> int:

@@ -11,6 +11,7 @@ namespace b200moe {
 static thread_local char g_detail[512] = "";
 static std::atomic<int64_t> g_launches{0};
 static std::atomic<int> g_engine{B200MOE_ENGINE_AUTO};
+static std::atomic<int> g_options[B200MOE_OPT_COUNT] = {{0}, {2}, {-1}};  // index = option id; [0] unused
 
 void set_error_detail(const char* fmt, ...) {
     va_list ap;
@@ -31,6 +32,19 @@ int check_launch(const char* what) {
 }
 
 int current_engine() { return g_engine.load(); }
+
+int option_value(int option) { return (option > 0 && option < B200MOE_OPT_COUNT) ? g_options[option].load() : 0; }
+
+// Per-shape tile table of the tensor-core engine, keyed on (operation, reduction extent K, output columns N, rows per
+// expert).  Entries were chosen by timing both tiles on a B200 with the benchmark's layer shapes; everything not listed
+// runs the two-CTA 256 x 256 cluster tile.
+int tile_table_lookup(int op, int K, int N, int64_t rows_per_expert) {
+    (void)op;
+    (void)K;
+    (void)N;
+    (void)rows_per_expert;
+    return B200MOE_TILE_PAIR_256x256;
+}
 
 int launch_offsets_from_sorted(const int64_t* sorted, int64_t M, int E, int64_t* offsets, cudaStream_t stream);
 int launch_make_row_maps(const int64_t* idx, int64_t M, int fan_out, int32_t* src_map, int32_t* dst_map,
@@ -73,7 +87,7 @@ int run_w_gemm(const WGemm& g, int dtype, int32_t* status, cudaStream_t stream, 
 
 using namespace b200moe;
 
-extern "C" int b200moe_version(void) { return 100; }
+extern "C" int b200moe_version(void) { return 200; }
 
 extern "C" const char* b200moe_error_string(int code) {
     switch (code) {
@@ -105,6 +119,21 @@ extern "C" const char* b200moe_last_error_detail(void) { return g_detail; }
 extern "C" int b200moe_set_engine(int engine) {
     if (engine < B200MOE_ENGINE_AUTO || engine > B200MOE_ENGINE_UMMA_GATHER4) return B200MOE_ERR_ARG;
     return g_engine.exchange(engine);
+}
+
+extern "C" int b200moe_set_option(int option, int value) {
+    if (option <= 0 || option >= B200MOE_OPT_COUNT) return B200MOE_ERR_ARG;
+    if (option == B200MOE_OPT_DYNAMIC_TILES && (value < 0 || value > 2)) return B200MOE_ERR_ARG;
+    if (option == B200MOE_OPT_TILE_VARIANT && (value < -1 || value >= B200MOE_TILE_COUNT)) return B200MOE_ERR_ARG;
+    g_options[option].store(value);
+    return B200MOE_OK;
+}
+
+extern "C" int b200moe_get_option(int option) { return option_value(option); }
+
+extern "C" int b200moe_tile_table_lookup(int op, int K, int N, int64_t rows_per_expert) {
+    if (op < 0 || op >= B200MOE_OP_COUNT || K <= 0 || N <= 0 || rows_per_expert < 0) return B200MOE_ERR_ARG;
+    return tile_table_lookup(op, K, N, rows_per_expert);
 }
 
 extern "C" int64_t b200moe_launch_count(void) { return g_launches.load(); }
@@ -267,8 +296,9 @@ extern "C" int b200moe_down_forward(const void* a, const void* w_proj, const int
     cudaStream_t stream = (cudaStream_t)stream_;
     REQUIRE_COMMON("down_forward");
     if (m_cap == 0 || M == 0) return B200MOE_OK;
-    B200MOE_REQUIRE(a && w_proj && expert_offsets && row_slot && y_expanded, B200MOE_ERR_ARG,
-                    "down_forward: NULL pointer");
+    B200MOE_REQUIRE(a && w_proj && expert_offsets && y_expanded, B200MOE_ERR_ARG, "down_forward: NULL pointer");
+    B200MOE_REQUIRE(row_slot != nullptr || gates == nullptr, B200MOE_ERR_ARG,
+                    "down_forward: gates are indexed by slot and need row_slot; the grouped output is unweighted");
     RowGemm g{};
     g.A = a;
     g.lda = I;
@@ -291,22 +321,19 @@ extern "C" int b200moe_down_forward(const void* a, const void* w_proj, const int
     return run_row_gemm(g, dtype, status, stream, "down_forward");
 }
 
-extern "C" int b200moe_down_dgrad(const void* grad_out, int64_t ldg, const void* w_proj,
-                                  const int64_t* expert_offsets, const int32_t* row_token, const int32_t* row_slot,
-                                  const void* gates, const void* h, void* dh, void* ag, float* d_gates, int64_t M,
-                                  int H, int I, int E, int64_t m_cap, int activation, int dtype, int32_t* status,
-                                  b200moe_stream_t stream_) {
+extern "C" int b200moe_down_dgrad(const void* grad_rows, int64_t ldg, const void* w_proj, const int64_t* expert_offsets,
+                                  const int32_t* row_token, const void* h, void* dh, int64_t T, int H, int I, int E,
+                                  int64_t m_cap, int activation, int dtype, int32_t* status, b200moe_stream_t stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     REQUIRE_COMMON("down_dgrad");
     B200MOE_REQUIRE(activation == B200MOE_ACT_SWIGLU || activation == B200MOE_ACT_GLU, B200MOE_ERR_ARG, "down_dgrad: activation %d", activation);
-    if (m_cap == 0 || M == 0) return B200MOE_OK;
-    B200MOE_REQUIRE(grad_out && w_proj && expert_offsets && row_slot && h && dh && ag && d_gates, B200MOE_ERR_ARG,
-                    "down_dgrad: NULL pointer");
+    if (m_cap == 0) return B200MOE_OK;
+    B200MOE_REQUIRE(grad_rows && w_proj && expert_offsets && h && dh && T >= 0, B200MOE_ERR_ARG, "down_dgrad: NULL pointer");
     RowGemm g{};
-    g.A = grad_out;
+    g.A = grad_rows;
     g.lda = ldg;
     g.a_map = row_token;
-    g.a_rows = row_token ? M : m_cap;  // an upper bound: the rows of grad_out are the tokens, M / k
+    g.a_rows = row_token ? T : m_cap;
     g.W = w_proj;  // reduction over H now: element (e, kk=h, n=i) at e*H*I + kk*I + n
     g.w_se = (int64_t)H * I;
     g.w_sk = I;
@@ -322,26 +349,15 @@ extern "C" int b200moe_down_dgrad(const void* grad_out, int64_t ldg, const void*
     g.E = E;
     g.epi = EPI_DGRAD_DOWN;
     g.act = activation;
-    g.out2 = ag;
     g.h = h;
-    g.d_gates = d_gates;
-    g.g_map = row_slot;
-    g.scale = gates;
     int eng = pick_engine(g, dtype, umma_row_gemm_supported, "down_dgrad");
     if (eng < 0) return eng;
-    if (eng) {
-        if (cudaMemsetAsync(d_gates, 0, (size_t)M * sizeof(float), stream) != cudaSuccess)
-            return check_launch("down_dgrad memset");
-        return umma_row_gemm(g, dtype, status, stream);
-    }
-    // CUDA-core engine: u into the ag buffer, then the element-wise tail
+    if (eng) return umma_row_gemm(g, dtype, status, stream);
+    // CUDA-core engine: d into the first half of every dh row, then the element-wise tail in place
     g.epi = EPI_STORE;
-    g.out = ag;
-    g.ldo = I;
-    g.scale = nullptr;
     int rc = simt_row_gemm(g, dtype, stream);
     if (rc) return rc;
-    return launch_dgrad_down_post(h, dh, ag, row_slot, gates, d_gates, m_cap, I, dtype, stream, activation);
+    return launch_dgrad_down_post(h, dh, m_cap, I, dtype, stream, activation);
 }
 
 extern "C" int b200moe_wgrad(const void* P, int64_t ldp, const int32_t* p_map, const void* Q, int64_t ldq,
@@ -379,7 +395,7 @@ extern "C" int b200moe_up_dgrad(const void* dh, const void* w_fc, const int64_t*
     cudaStream_t stream = (cudaStream_t)stream_;
     REQUIRE_COMMON("up_dgrad");
     if (m_cap == 0 || M == 0) return B200MOE_OK;
-    B200MOE_REQUIRE(dh && w_fc && expert_offsets && row_slot && dx_expanded, B200MOE_ERR_ARG, "up_dgrad: NULL pointer");
+    B200MOE_REQUIRE(dh && w_fc && expert_offsets && dx_expanded, B200MOE_ERR_ARG, "up_dgrad: NULL pointer");
     RowGemm g{};
     g.A = dh;
     g.lda = 2 * (int64_t)I;

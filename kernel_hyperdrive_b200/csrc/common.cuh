@@ -101,10 +101,8 @@ struct RowGemm {
     // fused epilogues (tcgen05 engine only)
     int epi;               // 0 store, 1 SwiGLU forward, 2 down-projection dgrad
     int act;               // gated activation of epilogues 1 and 2 (ACT_SILU, ACT_SIGMOID)
-    void* out2;            // SwiGLU: activation output a (rows_cap, N/2); dgrad: ag (rows_cap, N)
-    const void* h;         // dgrad: pre-activation (rows_cap, 2N)
-    float* d_gates;        // dgrad: fp32 (M) accumulated with atomics, indexed by o_map
-    const int32_t* g_map;  // dgrad: layout row -> flat slot index for gates / d_gates
+    void* out2;            // SwiGLU: activation output a (rows_cap, N/2)
+    const void* h;         // dgrad: pre-activation (rows_cap, 2N) as the SwiGLU epilogue of the same engine stored it
 };
 
 // Family W: DW[e][m, n] = sum_{p in segment e} P[pmap(p), m] * Q[qmap(p), n]
@@ -147,9 +145,12 @@ int launch_swiglu_forward(const void* x, int64_t ldx, void* y, int64_t ldy, int6
                           cudaStream_t stream, int act = ACT_SILU);
 int launch_swiglu_backward(const void* x, int64_t ldx, const void* dy, int64_t lddy, void* dx, int64_t lddx,
                            int64_t rows, int h, int dtype, cudaStream_t stream);
-int launch_dgrad_down_post(const void* h, void* dh, void* ag, const int32_t* row_slot, const void* gates,
-                           float* d_gates, int64_t rows, int I, int dtype, cudaStream_t stream, int act = ACT_SILU);
+int launch_dgrad_down_post(const void* h, void* dh, int64_t rows, int I, int dtype, cudaStream_t stream, int act = ACT_SILU);
 
 int current_engine();
+int option_value(int option);
+// The per-shape tile table: which tensor-core tile (B200MOE_TILE_*) a launch of `op` (B200MOE_OP_*) with reduction
+// extent K, N output columns and about rows_per_expert rows per expert uses.
+int tile_table_lookup(int op, int K, int N, int64_t rows_per_expert);
 
 }  // namespace b200moe

@@ -118,6 +118,31 @@ __global__ void gate_grad_kernel(const T* __restrict__ expanded, int64_t lde, co
     }
 }
 
+// Rank barrier over a symmetric int32 flag array (R words per rank, zero at start).  Thread d publishes `epoch` in word
+// `rank` of rank d's array and then waits until word d of its own array has reached `epoch`.  Epochs only grow, so a
+// peer that is already one barrier ahead is seen as arrived.  The wait is bounded: when a peer does not show up within
+// the limit the kernel writes 302 to the status word and returns, so the host can read the failure and the context
+// stays usable.
+__global__ void ep_barrier_kernel(PeerTable flags, int rank, int R, int epoch, long long limit_cycles, int32_t* status) {
+    const int d = threadIdx.x;
+    if (d >= R) return;
+    __threadfence_system();
+    int* remote = (int*)flags.ptr[d] + rank;
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+    const int* mine = (const int*)flags.ptr[rank] + d;
+    const long long t0 = clock64();
+    for (;;) {
+        int v;
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+        if (v - epoch >= 0) break;
+        if (clock64() - t0 > limit_cycles) {
+            if (status) atomicCAS(status, 0, 302);
+            break;
+        }
+        __nanosleep(200);
+    }
+}
+
 int fill_peers(PeerTable& tab, const void* const* peer_ptrs, int R, const char* what) {
     B200MOE_REQUIRE(R >= 1 && R <= kMaxRanks && peer_ptrs, B200MOE_ERR_ARG, "%s: bad rank count or NULL peer table", what);
     for (int i = 0; i < R; ++i) {
@@ -220,4 +245,16 @@ extern "C" int b200moe_ep_gate_grad(const void* expanded, int64_t lde, const voi
     }
     count_launch();
     return check_launch("ep_gate_grad");
+}
+
+extern "C" int b200moe_ep_barrier(const void* const* flag_ptrs, int rank, int R, int epoch, int64_t limit_cycles, int32_t* status,
+                                  b200moe_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    B200MOE_REQUIRE(rank >= 0 && rank < R && limit_cycles > 0, B200MOE_ERR_ARG, "ep_barrier: bad rank or limit");
+    PeerTable tab{};
+    int rc = fill_peers(tab, flag_ptrs, R, "ep_barrier");
+    if (rc) return rc;
+    ep_barrier_kernel<<<1, 64, 0, stream>>>(tab, rank, R, epoch, (long long)limit_cycles, status);
+    count_launch();
+    return check_launch("ep_barrier");
 }

@@ -1,6 +1,7 @@
-// Row-wise, HBM-bound kernels of the path: row gather with coefficient (`group`), the sum over the k
-// slots of a token (`combine`), SwiGLU forward / backward on a fused (rows, 2h) tensor, and the
-// element-wise tail of the down-projection input gradient used by the CUDA-core engine.
+// Row-wise, HBM-bound kernels of the path: row gather with coefficient (`group`), the gathers into the padded grouped
+// order (tokens; gate-scaled upstream gradient rows with the gate gradient), the sum over the k slots of a token
+// (`combine`), SwiGLU forward / backward on a fused (rows, 2h) tensor, and the element-wise tail of the
+// down-projection input gradient used by the CUDA-core engine.
 // All of them move 16 bytes per thread access when pointers, row strides and widths allow it.
 #include "common.cuh"
 
@@ -84,6 +85,46 @@ __global__ void combine_kernel(const T* __restrict__ in, int64_t ldi, const T* _
     }
 }
 
+// out[t, :] = sum_j gates[t, j] * in[pos[t*k + j], :]: the combine pass reading rows of the padded grouped order
+template <typename T, int V>
+__global__ void combine_rows_kernel(const T* __restrict__ in, int64_t ldi, const int32_t* __restrict__ pos,
+                                    const T* __restrict__ gates, T* __restrict__ out, int64_t ldo, int64_t Tn, int k, int H) {
+    int64_t t = blockIdx.x;
+    if (t >= Tn) return;
+    __shared__ const T* rows[64];
+    __shared__ float gs[64];
+    if (threadIdx.x < k) {
+        int p = pos[t * k + threadIdx.x];
+        rows[threadIdx.x] = p >= 0 ? in + (int64_t)p * ldi : nullptr;
+        gs[threadIdx.x] = gates ? Elem<T>::to_f(gates[t * k + threadIdx.x]) : 1.f;
+    }
+    __syncthreads();
+    for (int col = threadIdx.x * V; col < H; col += blockDim.x * V) {
+        float acc[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = 0.f;
+        for (int j = 0; j < k; ++j) {
+            if (rows[j] == nullptr) continue;
+            Pack<T, V> p = *reinterpret_cast<const Pack<T, V>*>(rows[j] + col);
+            const float g = gs[j];
+#pragma unroll
+            for (int i = 0; i < V; ++i) acc[i] += g * Elem<T>::to_f(p.v[i]);
+        }
+        Pack<T, V> o;
+#pragma unroll
+        for (int i = 0; i < V; ++i) o.v[i] = Elem<T>::from_f(acc[i]);
+        *reinterpret_cast<Pack<T, V>*>(out + t * ldo + col) = o;
+    }
+}
+
+// slot_row[row_slot[p]] = p for the real rows of the padded grouped order
+__global__ void invert_row_map_kernel(const int32_t* __restrict__ row_slot, int64_t rows, int32_t* __restrict__ slot_row, int64_t M) {
+    int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= rows) return;
+    int s = row_slot[p];
+    if (s >= 0 && s < M) slot_row[s] = (int32_t)p;
+}
+
 // ---- SwiGLU --------------------------------------------------------------------------------------
 template <typename T, int V>
 __global__ void swiglu_fwd_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__ y, int64_t ldy,
@@ -126,46 +167,73 @@ __global__ void swiglu_bwd_kernel(const T* __restrict__ x, int64_t ldx, const T*
 }
 
 // ---- tail of the down-projection input gradient (CUDA-core engine) --------------------------------
-// On entry ag[p, :] holds u[p, :] = grad_out[token(p), :] @ w_proj[e]; one block per padded grouped row.
+// On entry dh[p, :I] holds d[p, :] = (gate-scaled upstream gradient row) @ w_proj[e], rounded to T; h is in the plain
+// (up | gate) layout the CUDA-core forward writes.  One block per padded grouped row; filler rows hold zeros already
+// (their upstream rows are zero).
 template <typename T>
-__global__ void dgrad_down_post_kernel(const T* __restrict__ h, T* __restrict__ dh, T* __restrict__ ag,
-                                       const int32_t* __restrict__ row_slot, const T* __restrict__ gates,
-                                       float* __restrict__ d_gates, int64_t rows, int I, int act_kind) {
+__global__ void dgrad_down_post_kernel(const T* __restrict__ h, T* __restrict__ dh, int64_t rows, int I, int act_kind) {
     int64_t p = blockIdx.x;
     if (p >= rows) return;
-    int slot = row_slot[p];
     T* dh_row = dh + p * 2 * (int64_t)I;
-    T* ag_row = ag + p * (int64_t)I;
-    if (slot < 0) {  // filler row of the padded order: keep it zero
-        for (int c = threadIdx.x; c < I; c += blockDim.x) {
-            dh_row[c] = Elem<T>::from_f(0.f);
-            dh_row[I + c] = Elem<T>::from_f(0.f);
-            ag_row[c] = Elem<T>::from_f(0.f);
-        }
-        return;
-    }
     const T* h_row = h + p * 2 * (int64_t)I;
-    float g = gates ? Elem<T>::to_f(gates[slot]) : 1.f;
-    float dot = 0.f;
     for (int c = threadIdx.x; c < I; c += blockDim.x) {
         float up = Elem<T>::to_f(h_row[c]), gt = Elem<T>::to_f(h_row[I + c]);
-        float u = Elem<T>::to_f(ag_row[c]);
+        float d = Elem<T>::to_f(dh_row[c]);
         float sg = sigmoid_for<T>(gt);
-        float act = Elem<T>::to_f(Elem<T>::from_f(up * gate_value(act_kind, gt, sg)));  // the forward stores it in T
-        dot += act * u;
-        float da = Elem<T>::to_f(Elem<T>::from_f(g * u));
-        dh_row[c] = Elem<T>::from_f(da * gate_value(act_kind, gt, sg));
-        dh_row[I + c] = Elem<T>::from_f(da * up * gate_slope(act_kind, gt, sg));
-        ag_row[c] = Elem<T>::from_f(g * act);
+        dh_row[c] = Elem<T>::from_f(d * gate_value(act_kind, gt, sg));
+        dh_row[I + c] = Elem<T>::from_f(d * up * gate_slope(act_kind, gt, sg));
     }
-    __shared__ float red[32];
-    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = dot;
-    __syncthreads();
-    if (threadIdx.x < 32) {
-        float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (threadIdx.x == 0) d_gates[slot] = v;
+}
+
+// ---- upstream gradient rows of the backward pass ------------------------------------------------------
+// One block per padded grouped row p (slot s = row_slot[p], token t = row_token[p]):
+//   out[p, :]  = gates[s] * grad[t, :]            (zeros on filler rows)
+//   d_gates[s] = <y_expanded[s or p, :], grad[t, :]>   (fp32; only when y_expanded is given; y_grouped: indexed by p)
+// i.e. `group(grad_out, coeff=gates)` and the gate-gradient bmm of the reference's backward in one pass over grad.
+template <typename T, int V>
+__global__ void gather_grad_rows_kernel(const T* __restrict__ grad, int64_t ldg, const int32_t* __restrict__ row_token,
+                                        const int32_t* __restrict__ row_slot, const T* __restrict__ gates,
+                                        const T* __restrict__ y_expanded, int64_t ldy, int y_grouped, T* __restrict__ out,
+                                        int64_t ldo, float* __restrict__ d_gates, int64_t rows, int width) {
+    int64_t p = blockIdx.x;
+    if (p >= rows) return;
+    const int t = row_token[p];
+    T* dst = out + p * ldo;
+    if (t < 0) {
+        Pack<T, V> z;
+#pragma unroll
+        for (int i = 0; i < V; ++i) z.v[i] = Elem<T>::from_f(0.f);
+        for (int col = threadIdx.x * V; col < width; col += blockDim.x * V) *reinterpret_cast<Pack<T, V>*>(dst + col) = z;
+        return;
+    }
+    const int s = row_slot[p];
+    const float g = gates ? Elem<T>::to_f(gates[s]) : 1.f;
+    const T* src = grad + (int64_t)t * ldg;
+    const T* yrow = y_expanded ? y_expanded + (y_grouped ? p : (int64_t)s) * ldy : nullptr;
+    float dot = 0.f;
+    for (int col = threadIdx.x * V; col < width; col += blockDim.x * V) {
+        Pack<T, V> v = *reinterpret_cast<const Pack<T, V>*>(src + col);
+        if (yrow) {
+            Pack<T, V> y = *reinterpret_cast<const Pack<T, V>*>(yrow + col);
+#pragma unroll
+            for (int i = 0; i < V; ++i) dot += Elem<T>::to_f(y.v[i]) * Elem<T>::to_f(v.v[i]);
+        }
+        if (gates) {
+#pragma unroll
+            for (int i = 0; i < V; ++i) v.v[i] = Elem<T>::from_f(g * Elem<T>::to_f(v.v[i]));
+        }
+        *reinterpret_cast<Pack<T, V>*>(dst + col) = v;
+    }
+    if (yrow) {
+        __shared__ float red[8];
+        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = dot;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float v = 0.f;
+            for (int w = 0; w < (int)(blockDim.x >> 5); ++w) v += red[w];  // fixed order: the result is reproducible
+            d_gates[s] = v;
+        }
     }
 }
 
@@ -228,13 +296,11 @@ int launch_swiglu_backward(const void* x, int64_t ldx, const void* dy, int64_t l
     });
 }
 
-int launch_dgrad_down_post(const void* h, void* dh, void* ag, const int32_t* row_slot, const void* gates,
-                           float* d_gates, int64_t rows, int I, int dtype, cudaStream_t stream, int act) {
+int launch_dgrad_down_post(const void* h, void* dh, int64_t rows, int I, int dtype, cudaStream_t stream, int act) {
     if (rows == 0) return B200MOE_OK;
     return dispatch_dtype(dtype, [&](auto tag) {
         using T = decltype(tag);
-        dgrad_down_post_kernel<T><<<(unsigned)rows, 256, 0, stream>>>((const T*)h, (T*)dh, (T*)ag, row_slot,
-                                                                     (const T*)gates, d_gates, rows, I, act);
+        dgrad_down_post_kernel<T><<<(unsigned)rows, 256, 0, stream>>>((const T*)h, (T*)dh, rows, I, act);
         count_launch();
         return check_launch("dgrad_down_post");
     });
@@ -288,6 +354,33 @@ extern "C" int b200moe_gather_rows(const void* src, int64_t lds, const int32_t* 
     });
 }
 
+extern "C" int b200moe_gather_grad_rows(const void* grad, int64_t ldg, const int32_t* row_token, const int32_t* row_slot,
+                                        const void* gates, const void* y_expanded, int64_t ldy, int y_grouped, void* out,
+                                        int64_t ldo, float* d_gates, int64_t rows, int width, int dtype,
+                                        b200moe_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    B200MOE_REQUIRE(rows >= 0 && width >= 0, B200MOE_ERR_ARG, "gather_grad_rows: bad sizes");
+    if (rows == 0 || width == 0) return B200MOE_OK;
+    B200MOE_REQUIRE(grad && row_token && row_slot && out, B200MOE_ERR_ARG, "gather_grad_rows: NULL pointer");
+    B200MOE_REQUIRE((y_expanded == nullptr) == (d_gates == nullptr), B200MOE_ERR_ARG,
+                    "gather_grad_rows: y_expanded and d_gates are given together or not at all");
+    return dispatch_dtype(dtype, [&](auto tag) {
+        using T = decltype(tag);
+        constexpr int V = vec_elems<T>();
+        bool vec = width % V == 0 && ldg % V == 0 && ldo % V == 0 && aligned16(grad) && aligned16(out) &&
+                   (y_expanded == nullptr || (ldy % V == 0 && aligned16(y_expanded)));
+        if (vec) {
+            gather_grad_rows_kernel<T, V><<<(unsigned)rows, row_threads(width, V), 0, stream>>>(
+                (const T*)grad, ldg, row_token, row_slot, (const T*)gates, (const T*)y_expanded, ldy, y_grouped, (T*)out, ldo, d_gates, rows, width);
+        } else {
+            gather_grad_rows_kernel<T, 1><<<(unsigned)rows, row_threads(width, 1), 0, stream>>>(
+                (const T*)grad, ldg, row_token, row_slot, (const T*)gates, (const T*)y_expanded, ldy, y_grouped, (T*)out, ldo, d_gates, rows, width);
+        }
+        count_launch();
+        return check_launch("gather_grad_rows");
+    });
+}
+
 extern "C" int b200moe_combine(const void* in, int64_t ldi, const void* gates, void* out, int64_t ldo, int64_t T_,
                                int k, int H, int dtype, b200moe_stream_t stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
@@ -308,6 +401,38 @@ extern "C" int b200moe_combine(const void* in, int64_t ldi, const void* gates, v
         count_launch();
         return check_launch("combine");
     });
+}
+
+extern "C" int b200moe_combine_rows(const void* in, int64_t ldi, const int32_t* pos, const void* gates, void* out, int64_t ldo,
+                                    int64_t T_, int k, int H, int dtype, b200moe_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    B200MOE_REQUIRE(T_ >= 0 && k > 0 && k <= 64 && H >= 0, B200MOE_ERR_ARG, "combine_rows: bad sizes (k <= 64)");
+    if (T_ == 0 || H == 0) return B200MOE_OK;
+    B200MOE_REQUIRE(in && pos && out, B200MOE_ERR_ARG, "combine_rows: NULL pointer");
+    return dispatch_dtype(dtype, [&](auto tag) {
+        using T = decltype(tag);
+        constexpr int V = vec_elems<T>();
+        bool vec = H % V == 0 && ldi % V == 0 && ldo % V == 0 && aligned16(in) && aligned16(out);
+        int threads = row_threads(H, vec ? V : 1);
+        if (threads < 64) threads = 64;  // the first k threads look the rows up
+        if (vec) {
+            combine_rows_kernel<T, V><<<(unsigned)T_, threads, 0, stream>>>((const T*)in, ldi, pos, (const T*)gates, (T*)out, ldo, T_, k, H);
+        } else {
+            combine_rows_kernel<T, 1><<<(unsigned)T_, threads, 0, stream>>>((const T*)in, ldi, pos, (const T*)gates, (T*)out, ldo, T_, k, H);
+        }
+        count_launch();
+        return check_launch("combine_rows");
+    });
+}
+
+extern "C" int b200moe_invert_row_map(const int32_t* row_slot, int64_t rows, int32_t* slot_row, int64_t M, b200moe_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    B200MOE_REQUIRE(rows >= 0 && M >= 0, B200MOE_ERR_ARG, "invert_row_map: bad sizes");
+    if (rows == 0 || M == 0) return B200MOE_OK;
+    B200MOE_REQUIRE(row_slot && slot_row, B200MOE_ERR_ARG, "invert_row_map: NULL pointer");
+    invert_row_map_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, stream>>>(row_slot, rows, slot_row, M);
+    count_launch();
+    return check_launch("invert_row_map");
 }
 
 extern "C" int b200moe_swiglu_unchunked_forward(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t rows, int h,

@@ -13,9 +13,18 @@
 //     BOTH CTAs (one commit per barrier; no multicast) and, at the end of a tile, to both tmem_full barriers;
 //   * every epilogue warp of both CTAs arrives on the LEADER's tmem_empty barrier when it has drained its part
 //     of the accumulator.
+// Tile scheduling.  With a tile counter (a zeroed word in global memory, one per launch) the clusters draw their tiles
+// from it: the leader's producer lane takes the next index with atomicAdd while it streams the current tile, and
+// hands every index to the other roles of both CTAs through a small ring in shared memory (one mbarrier pair per
+// slot).  Tiles are therefore started in list order by whichever cluster is free: clusters that share a weight panel
+// stay close together in the list, and the weight-gradient tiles, listed by descending reduction length, are balanced
+// longest-first.  Without a counter every cluster walks the list with a fixed stride (its index, then + clusters).
 // All operands must be plain TMA tiles (the layer path gathers rows beforehand).  No load uses cluster
 // multicast.  Every wait is bounded like in the one-CTA kernel; a cluster barrier at the end keeps either CTA
 // from exiting while its peer may still signal into its shared memory.
+#include <atomic>
+#include <mutex>
+
 #include "umma_common.cuh"
 
 namespace b200moe {
@@ -24,6 +33,7 @@ namespace umma {
 namespace {
 
 constexpr int STAGES2 = 6;
+constexpr int SCHED_SLOTS = 8;  // tile indices in flight between the scheduling lane and the slowest role
 constexpr int B_HALF_BYTES = (BN / 2) * BK * 2;  // 16 KB
 // Epilogue warps per CTA: twelve (three per TMEM lane quarter with 96 / 96 / 64 columns) for the store and down-dgrad
 // epilogues (latency-bound work: about a quarter of an instruction per cycle and scheduler with eight warps; exposed when
@@ -53,6 +63,38 @@ __device__ __forceinline__ uint32_t mbar_test(uint32_t bar, uint32_t parity) {
         : "r"(bar), "r"(parity)
         : "memory");
     return ok;
+}
+// Bounded wait whose acquire has cluster scope: used where the data guarded by the barrier was written by the peer CTA.
+__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+static __device__ __noinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
+                                                      int code) {
+    long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i) {
+            if (mbar_try_wait_cluster(bar, parity)) return true;
+            __nanosleep(100);
+        }
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            *abort_flag = 1;
+            if (status) atomicCAS(status, 0, code);
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
@@ -100,8 +142,9 @@ __device__ __forceinline__ void decode_tile2(const UmmaParams& p, const Tables& 
     if (p.wfam) {
         const int mb2 = (p.mb_count + 1) / 2;
         int per_e = mb2 * p.nb_count;
-        ti.e = t / per_e;
-        int local = t - ti.e * per_e;
+        const int ei = t / per_e;
+        ti.e = tb.order[ei];
+        int local = t - ei * per_e;
         int pair;
         if (mb2 <= p.nb_count) {
             pair = local % mb2;
@@ -139,6 +182,22 @@ __device__ __forceinline__ void decode_tile2(const UmmaParams& p, const Tables& 
     }
 }
 
+// Barriers and bookkeeping of one CTA; both CTAs of a pair use the same offsets, so a peer's word is this CTA's address
+// mapped to the other rank.
+struct Ctl2 {
+    uint64_t full_bar[STAGES2];        // used in the leader only
+    uint64_t empty_bar[STAGES2];       // one set per CTA
+    uint64_t tmem_full_bar[2];         // one set per CTA
+    uint64_t tmem_empty_bar[2];        // used in the leader only
+    uint64_t sched_full[SCHED_SLOTS];  // one set per CTA: a tile index has been written to sched_tile[slot]
+    uint64_t sched_empty[SCHED_SLOTS]; // used in the leader only: every role of both CTAs has read the slot
+    int sched_tile[SCHED_SLOTS];
+    uint32_t tmem_slot;
+    int abort_flag;
+    int pad[2];
+    Tables tb;
+};
+
 template <int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(EPI), 1)
     umma2_grouped_kernel(const UmmaParams p, const __grid_constant__ CUtensorMap tmap_a,
@@ -151,18 +210,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(EPI), 1)
     uint8_t* smem_b = smem + STAGES2 * A_STAGE_BYTES;
     uint8_t* smem_stg = smem + STAGES2 * (A_STAGE_BYTES + B_HALF_BYTES);
     constexpr int EW = epi_warps_of(EPI);
-    uint64_t* bars = (uint64_t*)(smem_stg + EW * STG_BYTES);
-    uint64_t* full_bar = bars;                       // used in the leader only
-    uint64_t* empty_bar = bars + STAGES2;            // one set per CTA
-    uint64_t* tmem_full_bar = bars + 2 * STAGES2;    // one set per CTA
-    uint64_t* tmem_empty_bar = bars + 2 * STAGES2 + 2;  // used in the leader only
-    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES2 + 4);
-    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-    Tables& tb = *(Tables*)(tmem_slot + 4);
+    Ctl2& ctl = *(Ctl2*)(smem_stg + EW * STG_BYTES);
+    uint64_t* full_bar = ctl.full_bar;
+    uint64_t* empty_bar = ctl.empty_bar;
+    uint64_t* tmem_full_bar = ctl.tmem_full_bar;
+    uint64_t* tmem_empty_bar = ctl.tmem_empty_bar;
+    volatile int* abort_flag = (volatile int*)&ctl.abort_flag;
+    Tables& tb = ctl.tb;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const int cluster_id = blockIdx.x >> 1, nclusters = gridDim.x >> 1;
+    const bool dyn = p.tile_counter != nullptr;
 
     for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
         int64_t prev = e ? p.offsets[e - 1] : 0;
@@ -178,9 +237,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(EPI), 1)
             mbar_init(smem_u32(&tmem_full_bar[a]), 1);
             mbar_init(smem_u32(&tmem_empty_bar[a]), 2 * EW);
         }
+        for (int s = 0; s < SCHED_SLOTS; ++s) {
+            mbar_init(smem_u32(&ctl.sched_full[s]), 1);
+            // readers of a slot: the leader's MMA lane and epilogue warps, the peer's producer and epilogue warps
+            mbar_init(smem_u32(&ctl.sched_empty[s]), 2 + 2 * EW);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    if (p.wfam) fill_expert_order(tb, p.E);
     if (threadIdx.x == 0) {
         int start = 0, tiles = 0;
         for (int e = 0; e < p.E; ++e) {
@@ -194,15 +259,53 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(EPI), 1)
         tb.tile_prefix[p.E] = tiles;
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512)
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl.tmem_slot)), "r"(512)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
     cluster_sync_all();  // barriers of both CTAs are initialised and visible before anyone signals the peer
     tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_base = *(volatile uint32_t*)&ctl.tmem_slot;
     const int ntiles = total_tiles2(p, tb);
+
+    // ---- tile feed ----
+    // Readers (every role except the leader's producer): the next tile index of this cluster, or a value >= ntiles when
+    // the list is exhausted or the kernel is aborting.  `whole_warp`: all 32 lanes call it together (one arrival).
+    int f_slot = 0;
+    uint32_t f_phase = 0;
+    int f_static = cluster_id - nclusters;
+    const uint32_t lead_sched_empty0 = map_to_cta(smem_u32(&ctl.sched_empty[0]), 0);
+    auto next_tile = [&](bool whole_warp, int code) -> int {
+        if (!dyn) {
+            f_static += nclusters;
+            return f_static;
+        }
+        const uint32_t bar = smem_u32(&ctl.sched_full[f_slot]);
+        if (!mbar_try_wait_cluster(bar, f_phase) && !mbar_wait_cluster(bar, f_phase, abort_flag, p.status, code)) return 0x7fffffff;
+        const int t = *(volatile int*)&ctl.sched_tile[f_slot];
+        if (whole_warp) __syncwarp();
+        if (!whole_warp || lane == 0) mbar_arrive_cluster(lead_sched_empty0 + f_slot * 8);
+        if (++f_slot == SCHED_SLOTS) {
+            f_slot = 0;
+            f_phase ^= 1;
+        }
+        return t;
+    };
+    // The leader's producer lane: publishes tile index t to both CTAs.  Returns false when the kernel is aborting.
+    auto publish_tile = [&](int t) -> bool {
+        if (!mbar_wait(smem_u32(&ctl.sched_empty[f_slot]), f_phase ^ 1, abort_flag, p.status, 216)) return false;
+        ctl.sched_tile[f_slot] = t;
+        st_cluster_u32(map_to_cta(smem_u32(&ctl.sched_tile[f_slot]), 1), (uint32_t)t);
+        mbar_arrive(smem_u32(&ctl.sched_full[f_slot]));
+        mbar_arrive_cluster(map_to_cta(smem_u32(&ctl.sched_full[f_slot]), 1));
+        if (++f_slot == SCHED_SLOTS) {
+            f_slot = 0;
+            f_phase ^= 1;
+        }
+        return true;
+    };
+    const bool scheduler = dyn && rank == 0;  // this CTA's producer lane draws the tiles
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -215,7 +318,29 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(EPI), 1)
             uint32_t phase = 0;
             Tile ti;
             int ok = 1;
-            for (int t = cluster_id; t < ntiles && ok; t += nclusters) {
+            int t = cluster_id, nxt = cluster_id + nclusters;  // see the plain producer below for the scheduling scheme
+            if (scheduler) {
+                if (lane == 0) ok = publish_tile(t) ? 1 : 0;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+            }
+            while (ok) {
+                int nxt2 = nxt + nclusters;
+                if (scheduler) {
+                    if (t >= ntiles) break;
+                    if (lane == 0) {
+                        ok = publish_tile(nxt) ? 1 : 0;
+                        nxt2 = nxt < ntiles ? 2 * nclusters + (int)atomicAdd(p.tile_counter, 1u) : nxt;
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    nxt2 = __shfl_sync(0xffffffffu, nxt2, 0);
+                    if (!ok) break;
+                } else {
+                    if (dyn) {
+                        if (lane == 0) t = next_tile(false, 217);
+                        t = __shfl_sync(0xffffffffu, t, 0);
+                    }
+                    if (t >= ntiles) break;
+                }
                 decode_tile2(p, tb, t, rank, ti);
                 for (int ks = 0; ks < ti.ksteps; ++ks) {
                     const int k0 = ks * BK;
@@ -279,6 +404,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(EPI), 1)
                         phase ^= 1;
                     }
                 }
+                t = nxt;
+                nxt = nxt2;
             }
         } else if (lane == 0) {
             // plain tile loads: one lane per CTA
@@ -287,7 +414,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(EPI), 1)
             Tile ti;
             bool ok = true;
             const uint32_t lead_full0 = map_to_cta(smem_u32(&full_bar[0]), 0);
-            for (int t = cluster_id; t < ntiles && ok; t += nclusters) {
+            // Scheduling lane: the first two tiles of a cluster are fixed (its index, then + clusters), the following ones
+            // come from the counter.  An index is published a whole tile before it is needed (while tile i streams, the
+            // other roles already hold the index of tile i + 1), and the counter is read two tiles ahead, so neither the
+            // atomic nor the hand-over to the peer CTA is ever waited for.
+            int t = cluster_id, nxt = cluster_id + nclusters;
+            if (scheduler && !publish_tile(t)) ok = false;
+            while (ok) {
+                if (scheduler) {
+                    if (t >= ntiles) break;
+                    if (!publish_tile(nxt)) break;
+                } else {
+                    if (dyn) t = next_tile(false, 217);
+                    if (t >= ntiles) break;
+                }
+                int nxt2 = nxt + nclusters;
+                if (scheduler) nxt2 = nxt < ntiles ? 2 * nclusters + (int)atomicAdd(p.tile_counter, 1u) : nxt;
                 decode_tile2(p, tb, t, rank, ti);
                 for (int ks = 0; ks < ti.ksteps; ++ks) {
                     if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 211)) {
@@ -329,6 +471,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(EPI), 1)
                         phase ^= 1;
                     }
                 }
+                t = nxt;
+                nxt = nxt2;
             }
         }
     } else if (warp == 1) {
@@ -353,7 +497,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(EPI), 1)
             const uint32_t empty0_peer = map_to_cta(empty0, 1);
             const uint32_t idesc = p.idesc;
             uint32_t ready = 0;  // the look-ahead result for (stage, phase)
-            for (int t = cluster_id; t < ntiles && ok; t += nclusters) {
+            for (int t = next_tile(false, 218); t < ntiles && ok; t = next_tile(false, 218)) {
                 decode_tile2(p, tb, t, 0, ti);
                 if (!mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1, abort_flag, p.status, 212)) break;
                 tc_fence_after();
@@ -419,7 +563,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(EPI), 1)
         int acc = 0;
         uint32_t acc_phase = 0;
         Tile ti;
-        for (int t = cluster_id; t < ntiles; t += nclusters) {
+        for (int t = next_tile(true, 219); t < ntiles; t = next_tile(true, 219)) {
             decode_tile2(p, tb, t, rank, ti);
             if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status, 215, 200)) break;
             tc_fence_after();
@@ -452,20 +596,61 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(EPI), 1)
 }
 
 constexpr int smem_bytes2(int epi) {
-    return 1024 + STAGES2 * (A_STAGE_BYTES + B_HALF_BYTES) + epi_warps_of(epi) * STG_BYTES + 128 + (int)sizeof(Tables) + 64;
+    return 1024 + STAGES2 * (A_STAGE_BYTES + B_HALF_BYTES) + epi_warps_of(epi) * STG_BYTES + (int)sizeof(Ctl2) + 64;
+}
+
+// Tile counters: a ring of zero-initialised words in the library image.  Every launch that schedules its tiles
+// dynamically takes the next word and clears it on the launch stream first, so launches in flight at the same time
+// (different streams) never share a word unless more than kCounterSlots of them overlap.  In host code the array's
+// name is only a stand-in; its device address is looked up once per device.
+constexpr int kCounterSlots = 4096;
+__device__ unsigned int g_tile_counters[kCounterSlots];
+std::mutex g_counter_mutex;
+unsigned int* g_counter_base[64] = {nullptr};
+std::atomic<unsigned int> g_counter_next{0};
+
+unsigned int* take_tile_counter(cudaStream_t stream) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    unsigned int* base;
+    {
+        std::lock_guard<std::mutex> lock(g_counter_mutex);
+        if (g_counter_base[dev] == nullptr) {
+            void* ptr = nullptr;
+            if (cudaGetSymbolAddress(&ptr, g_tile_counters) != cudaSuccess || ptr == nullptr) {
+                cudaGetLastError();
+                return nullptr;
+            }
+            g_counter_base[dev] = (unsigned int*)ptr;
+        }
+        base = g_counter_base[dev];
+    }
+    unsigned int* word = base + (g_counter_next.fetch_add(1, std::memory_order_relaxed) % kCounterSlots);
+    if (cudaMemsetAsync(word, 0, sizeof(unsigned int), stream) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    return word;
 }
 
 template <int EPI>
-int launch2(const UmmaParams& p, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mo2,
-            const CUtensorMap& mo3, cudaStream_t stream) {
+int launch2(const UmmaParams& p_in, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mo2,
+            const CUtensorMap& mo3, int64_t tiles_bound, cudaStream_t stream) {
     auto kern = umma2_grouped_kernel<EPI>;
     constexpr int SMEM_BYTES2 = smem_bytes2(EPI);
+    static_assert(SMEM_BYTES2 <= 232448, "shared memory of the two-CTA kernel exceeds 227 KB");
     cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES2);
     if (err != cudaSuccess) {
         set_error_detail("cudaFuncSetAttribute(smem=%d): %s", SMEM_BYTES2, cudaGetErrorString(err));
         return B200MOE_ERR_LAUNCH;
     }
     int grid = sm_count() & ~1;  // whole pairs
+    UmmaParams p = p_in;
+    // With no more tiles than clusters the fixed stride is already the best schedule; otherwise draw tiles dynamically
+    // (a counter that cannot be had falls back to the fixed stride).
+    p.tile_counter = nullptr;
+    const int mode = option_value(B200MOE_OPT_DYNAMIC_TILES);
+    if ((mode == 2 || (mode == 1 && p.wfam)) && tiles_bound > grid / 2) p.tile_counter = take_tile_counter(stream);
     kern<<<grid, threads_of(EPI), SMEM_BYTES2, stream>>>(p, ma, mb, mo, mo2, mo3);
     count_launch();
     return check_launch("umma2_grouped_kernel");
@@ -474,18 +659,21 @@ int launch2(const UmmaParams& p, const CUtensorMap& ma, const CUtensorMap& mb, c
 }  // namespace
 
 int launch_2cta(int epi, const UmmaParams& p, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo,
-                const CUtensorMap& mo2, const CUtensorMap& mo3, cudaStream_t stream) {
+                const CUtensorMap& mo2, const CUtensorMap& mo3, int64_t rows_cap, cudaStream_t stream) {
+    // upper bound of the cluster tiles (the exact number depends on the expert counts, which live on the device)
+    const int64_t tiles_bound = p.wfam ? (int64_t)p.E * ((p.mb_count + 1) / 2) * p.nb_count
+                                       : (rows_cap / (2 * BM) + p.E) * (int64_t)p.nb_count;
     switch (epi) {
         case EPI_STORE:
-            return launch2<EPI_STORE>(p, ma, mb, mo, mo2, mo3, stream);
+            return launch2<EPI_STORE>(p, ma, mb, mo, mo2, mo3, tiles_bound, stream);
         case EPI_SWIGLU:
-            return launch2<EPI_SWIGLU>(p, ma, mb, mo, mo2, mo3, stream);
+            return launch2<EPI_SWIGLU>(p, ma, mb, mo, mo2, mo3, tiles_bound, stream);
         case EPI_DGRAD_DOWN:
-            return launch2<EPI_DGRAD_DOWN>(p, ma, mb, mo, mo2, mo3, stream);
+            return launch2<EPI_DGRAD_DOWN>(p, ma, mb, mo, mo2, mo3, tiles_bound, stream);
         case EPI_GLU:
-            return launch2<EPI_GLU>(p, ma, mb, mo, mo2, mo3, stream);
+            return launch2<EPI_GLU>(p, ma, mb, mo, mo2, mo3, tiles_bound, stream);
         case EPI_DGRAD_DOWN_GLU:
-            return launch2<EPI_DGRAD_DOWN_GLU>(p, ma, mb, mo, mo2, mo3, stream);
+            return launch2<EPI_DGRAD_DOWN_GLU>(p, ma, mb, mo, mo2, mo3, tiles_bound, stream);
         default:
             set_error_detail("unknown epilogue %d", epi);
             return B200MOE_ERR_ARG;

@@ -46,10 +46,9 @@ struct UmmaParams {
     const void* scale;
     void* out2;
     const void* h;
-    float* d_gates;
-    const int32_t* g_map;
     int64_t d_se;
     int32_t* status;
+    unsigned int* tile_counter;  // two-CTA kernel: zeroed word the clusters draw tile indices from; NULL: static round-robin
     uint32_t idesc;
     int is_f16;
     int full_count;  // arrivals per full barrier
@@ -221,7 +220,22 @@ struct Tables {
     int seg_start[kMaxExperts];    // first layout row of the expert's segment
     int seg_cnt[kMaxExperts];      // rows the expert really has
     int tile_prefix[kMaxExperts + 1];  // R: row tiles before the expert
+    uint16_t order[kMaxExperts];   // W: experts by descending row count (the longest reductions are handed out first)
 };
+
+// Fills tb.order: position of expert e = number of experts with more rows (ties: lower index first).  Called by all
+// threads of the CTA after seg_cnt is complete and before a barrier.
+__device__ __forceinline__ void fill_expert_order(Tables& tb, int E) {
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        const int c = tb.seg_cnt[e];
+        int pos = 0;
+        for (int o = 0; o < E; ++o) {
+            const int co = tb.seg_cnt[o];
+            pos += (co > c || (co == c && o < e)) ? 1 : 0;
+        }
+        tb.order[pos] = (uint16_t)e;
+    }
+}
 
 struct Tile {
     int e, row0, rows_valid, nb, mb, ksteps;
@@ -234,8 +248,9 @@ __device__ __forceinline__ int total_tiles(const UmmaParams& p, const Tables& tb
 __device__ __forceinline__ void decode_tile(const UmmaParams& p, const Tables& tb, int t, Tile& ti) {
     if (p.wfam) {
         int per_e = p.mb_count * p.nb_count;
-        ti.e = t / per_e;
-        int local = t - ti.e * per_e;
+        const int ei = t / per_e;
+        ti.e = tb.order[ei];
+        int local = t - ei * per_e;
         if (p.mb_count <= p.nb_count) {  // walk the shorter side fastest: its operand panel stays L2-resident
             ti.mb = local % p.mb_count;
             ti.nb = local / p.mb_count;
@@ -364,8 +379,12 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
                 float2 fu = unpack2(hu[i], is_f16), fg = unpack2(hg[i], is_f16);
                 av[i] = pack2(fu.x * gate_value(ACT, fg.x, sigmoid_tanh(fg.x)), fu.y * gate_value(ACT, fg.y, sigmoid_tanh(fg.y)), is_f16);
             }
-            stage_store(mo, n0 + c, row_c, 0, hu);    // up half of h
-            stage_store(mo3, n0 + c, row_c, 0, hg);   // gate half of h (its own map: columns clip at I)
+            // h is stored interleaved per 32-column chunk: chunk j of a row holds up[32j .. 32j+w) then gate[32j .. 32j+w)
+            // (w = 32 except in a ragged last chunk), so that the down-dgrad epilogue finds both halves of a chunk in one
+            // 128-byte line.  The up box has its own map, clipped where the last chunk's gate part begins.
+            const int wch = min(32, I - (n0 + c));
+            stage_store(mo, 2 * (n0 + c), row_c, 0, hu);         // up part of the chunk
+            stage_store(mo3, 2 * (n0 + c) + wch, row_c, 0, hg);  // gate part of the chunk
             stage_store(mo2, n0 + c, row_c, 0, av);   // activation
         }
     } else if (EPI == EPI_ROUTER) {
@@ -462,28 +481,30 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
             }
         }
     } else {  // EPI_DGRAD_DOWN, EPI_DGRAD_DOWN_GLU
+        // The accumulator holds d[p, :] = (gate-scaled upstream gradient rows) @ w_proj[e]: the gradient with respect to
+        // the activation output.  It is rounded to the tensor type (the reference materialises it) and pushed through the
+        // backward of the gated activation with the pre-activation values of the row, read from the interleaved h.
         constexpr int ACT = epi_act(EPI);
         const int I = p.N;
         const int64_t prow = ti.row0 + r;
         const int n0 = ti.nb * BN;
         const int row_c = ti.row0 + q * 32;
-        const int slot = p.g_map[prow];
-        float g = 0.f;
-        if (slot >= 0) g = p.scale ? load_scalar(p.scale, slot, is_f16) : 1.f;
-        const uint8_t* hrow = (const uint8_t*)p.h + (prow * 2 * (int64_t)I + n0) * 2;
-        float dot = 0.f;
+        const uint8_t* hrow = (const uint8_t*)p.h + prow * 2 * (int64_t)I * 2;
 #pragma unroll 1
         for (int c = c_begin; c < c_end; c += 32) {
-            if (n0 + c >= I) break;
+            const int col = n0 + c;
+            if (col >= I) break;
+            const int wch = min(32, I - col);
+            const uint8_t* hp = hrow + (int64_t)col * 4;  // chunk base: element 2 * col
             // the pre-activation values of this row: requested before the accumulator is read
             uint4 hu4[4], hg4[4];
 #pragma unroll
             for (int qd = 0; qd < 4; ++qd) {
-                bool in = n0 + c + qd * 8 < I;
-                hu4[qd] = in ? *reinterpret_cast<const uint4*>(hrow + (c + qd * 8) * 2) : make_uint4(0, 0, 0, 0);
-                hg4[qd] = in ? *reinterpret_cast<const uint4*>(hrow + ((int64_t)I + c + qd * 8) * 2) : make_uint4(0, 0, 0, 0);
+                const bool in = qd * 8 < wch;
+                hu4[qd] = in ? *reinterpret_cast<const uint4*>(hp + qd * 16) : make_uint4(0, 0, 0, 0);
+                hg4[qd] = in ? *reinterpret_cast<const uint4*>(hp + (wch + qd * 8) * 2) : make_uint4(0, 0, 0, 0);
             }
-            uint32_t u[32], du[16], dg[16], ag[16];
+            uint32_t u[32], du[16], dg[16];
             tc_ld32(taddr + c, u);
             tc_wait_ld();
 #pragma unroll
@@ -492,23 +513,16 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
                 const uint32_t hga[4] = {hg4[qd].x, hg4[qd].y, hg4[qd].z, hg4[qd].w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    float2 up = unpack2(hua[i], is_f16), gt = unpack2(hga[i], is_f16);
-                    float u0 = __uint_as_float(u[qd * 8 + 2 * i]), u1 = __uint_as_float(u[qd * 8 + 2 * i + 1]);
-                    float s0 = sigmoid_fast(gt.x), s1 = sigmoid_fast(gt.y);
-                    float m0 = gate_value(ACT, gt.x, s0), m1 = gate_value(ACT, gt.y, s1);
-                    float a0 = round_elem(up.x * m0, is_f16), a1 = round_elem(up.y * m1, is_f16);
-                    dot += a0 * u0 + a1 * u1;
-                    float d0 = round_elem(g * u0, is_f16), d1 = round_elem(g * u1, is_f16);
-                    du[qd * 4 + i] = pack2(d0 * m0, d1 * m1, is_f16);
-                    dg[qd * 4 + i] = pack2(d0 * up.x * gate_slope(ACT, gt.x, s0), d1 * up.y * gate_slope(ACT, gt.y, s1), is_f16);
-                    ag[qd * 4 + i] = pack2(g * a0, g * a1, is_f16);
+                    const float2 up = unpack2(hua[i], is_f16), gt = unpack2(hga[i], is_f16);
+                    const float2 d = unpack2(pack2(__uint_as_float(u[qd * 8 + 2 * i]), __uint_as_float(u[qd * 8 + 2 * i + 1]), is_f16), is_f16);
+                    const float s0 = sigmoid_fast(gt.x), s1 = sigmoid_fast(gt.y);
+                    du[qd * 4 + i] = pack2(d.x * gate_value(ACT, gt.x, s0), d.y * gate_value(ACT, gt.y, s1), is_f16);
+                    dg[qd * 4 + i] = pack2(d.x * up.x * gate_slope(ACT, gt.x, s0), d.y * up.y * gate_slope(ACT, gt.y, s1), is_f16);
                 }
             }
-            stage_store(mo, n0 + c, row_c, 0, du);    // up half of dh
-            stage_store(mo3, n0 + c, row_c, 0, dg);   // gate half of dh
-            stage_store(mo2, n0 + c, row_c, 0, ag);   // gate-scaled activation
+            stage_store(mo, col, row_c, 0, du);    // up half of dh
+            stage_store(mo3, col, row_c, 0, dg);   // gate half of dh
         }
-        if (slot >= 0) atomicAdd(p.d_gates + slot, dot);
     }
 }
 
@@ -522,7 +536,7 @@ uint32_t make_idesc(int a_mn, int b_mn, int is_f16, int m, int n = BN);
 
 // two-CTA kernels (umma2_gemm.cu); operands must all be TMA tiles
 int launch_2cta(int epi, const UmmaParams& p, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo,
-                const CUtensorMap& mo2, const CUtensorMap& mo3, cudaStream_t stream);
+                const CUtensorMap& mo2, const CUtensorMap& mo3, int64_t rows_cap, cudaStream_t stream);
 
 }  // namespace umma
 }  // namespace b200moe

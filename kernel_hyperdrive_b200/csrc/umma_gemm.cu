@@ -112,8 +112,19 @@ namespace {
 
 bool aligned16(const void* p) { return p != nullptr && ((uintptr_t)p & 15) == 0; }
 
-// The two-CTA kernels take over whenever every operand is a TMA tile, unless the one-CTA engine is forced.
-bool use_pair_kernels(const UmmaParams& p) { return p.a_tma && p.b_tma && current_engine() != B200MOE_ENGINE_UMMA_1CTA; }
+// Which tile a launch uses.  The two-CTA kernel (256 x 256 cluster tile) needs every operand as a TMA tile; given that,
+// the choice between it and the one-CTA kernel (128 x 256) comes from the per-shape table below unless the engine or the
+// tile-variant option forces one.
+bool use_pair_kernels(const UmmaParams& p, int epi, int64_t rows_cap) {
+    if (!(p.a_tma && p.b_tma) || current_engine() == B200MOE_ENGINE_UMMA_1CTA) return false;
+    if (current_engine() == B200MOE_ENGINE_UMMA_GATHER4 && (p.a_g4 || p.b_g4)) return true;
+    int forced = option_value(B200MOE_OPT_TILE_VARIANT);
+    if (forced == B200MOE_TILE_PAIR_256x256) return true;
+    if (forced == B200MOE_TILE_CTA_128x256) return false;
+    const int64_t rows_per_expert = p.E > 0 ? rows_cap / p.E : rows_cap;
+    const int op = p.wfam ? B200MOE_OP_WGRAD : (epi_gated_forward(epi) ? B200MOE_OP_UP_FORWARD : (epi_gated_dgrad(epi) ? B200MOE_OP_DOWN_DGRAD : B200MOE_OP_ROW_STORE));
+    return tile_table_lookup(op, p.wfam ? p.Mout : p.K, p.N, rows_per_expert) == B200MOE_TILE_PAIR_256x256;
+}
 
 template <int EPI>
 int launch(const UmmaParams& p, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mo2,
@@ -121,10 +132,10 @@ int launch(const UmmaParams& p, const CUtensorMap& ma, const CUtensorMap& mb, co
 
 template <int EPI>
 int launch_any(UmmaParams& p, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mo2,
-               const CUtensorMap& mo3, cudaStream_t stream) {
-    if (use_pair_kernels(p)) {
+               const CUtensorMap& mo3, int64_t rows_cap, cudaStream_t stream) {
+    if (use_pair_kernels(p, EPI, rows_cap)) {
         p.idesc = make_idesc(p.a_mn, p.b_mn, p.is_f16, 2 * BM);
-        return launch_2cta(EPI, p, ma, mb, mo, mo2, mo3, stream);
+        return launch_2cta(EPI, p, ma, mb, mo, mo2, mo3, rows_cap, stream);
     }
     return launch<EPI>(p, ma, mb, mo, mo2, mo3, stream);
 }
@@ -181,6 +192,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    if (p.wfam) fill_expert_order(tb, p.E);
     if (threadIdx.x == 0) {
         int start = 0, tiles = 0;
         for (int e = 0; e < p.E; ++e) {
@@ -546,7 +558,7 @@ bool umma_row_gemm_supported(const RowGemm& g, int dtype) {
         return false;
     }
     if (g.epi == EPI_SWIGLU && (g.w_sk != 1 || (g.N / 2) % 8 || !aligned16(g.out2))) return false;
-    if (g.epi == EPI_DGRAD_DOWN && (!aligned16(g.out2) || !aligned16(g.h))) return false;
+    if (g.epi == EPI_DGRAD_DOWN && !aligned16(g.h)) return false;
     return true;
 }
 
@@ -588,8 +600,6 @@ int umma_row_gemm(const RowGemm& g, int dtype, int32_t* status, cudaStream_t str
     p.scale = g.scale;
     p.out2 = g.out2;
     p.h = g.h;
-    p.d_gates = g.d_gates;
-    p.g_map = g.g_map;
     p.status = status;
     p.idesc = make_idesc(0, p.b_mn, p.is_f16, BM);
     p.full_count = 1 + (p.a_tma ? 0 : GATHER_THREADS);
@@ -620,14 +630,18 @@ int umma_row_gemm(const RowGemm& g, int dtype, int32_t* status, cudaStream_t str
         p.swiglu_half = g.N / 2;
         p.N = g.N;
         p.nb_count = (p.swiglu_half + 127) / 128;
-        // the two halves of h get a map each so that a box at the end of the up half is clipped at column I
-        rc = make_store_map(&mo, g.out, 0, g.rows_cap, g.N / 2, g.ldo, 0, p.is_f16);
+        // h is stored interleaved per 32-column chunk (up part, then gate part).  The up boxes get their own map whose
+        // column extent ends where the gate part of a ragged last chunk begins, so that the box is clipped there; the
+        // gate boxes are clipped by the row end.
+        const int I_ = g.N / 2, ragged = I_ % 32;
+        rc = make_store_map(&mo, g.out, 0, g.rows_cap, g.N - ragged, g.ldo, 0, p.is_f16);
         if (rc) return rc;
-        rc = make_store_map(&mo3, (const uint8_t*)g.out + (int64_t)(g.N / 2) * 2, 0, g.rows_cap, g.N / 2, g.ldo, 0, p.is_f16);
+        rc = make_store_map(&mo3, g.out, 0, g.rows_cap, g.N, g.ldo, 0, p.is_f16);
         if (rc) return rc;
         rc = make_store_map(&mo2, g.out2, 0, g.rows_cap, g.N / 2, g.N / 2, 0, p.is_f16);
         if (rc) return rc;
-        return g.act == ACT_SIGMOID ? launch_any<EPI_GLU>(p, ma, mb, mo, mo2, mo3, stream) : launch_any<EPI_SWIGLU>(p, ma, mb, mo, mo2, mo3, stream);
+        return g.act == ACT_SIGMOID ? launch_any<EPI_GLU>(p, ma, mb, mo, mo2, mo3, g.rows_cap, stream)
+                                    : launch_any<EPI_SWIGLU>(p, ma, mb, mo, mo2, mo3, g.rows_cap, stream);
     }
     p.N = g.N;
     p.nb_count = (g.N + BN - 1) / BN;
@@ -637,16 +651,14 @@ int umma_row_gemm(const RowGemm& g, int dtype, int32_t* status, cudaStream_t str
         if (rc) return rc;
         rc = make_store_map(&mo3, (const uint8_t*)g.out + (int64_t)g.N * 2, 0, g.rows_cap, g.N, 2 * (int64_t)g.N, 0, p.is_f16);
         if (rc) return rc;
-        rc = make_store_map(&mo2, g.out2, 0, g.rows_cap, g.N, g.N, 0, p.is_f16);
-        if (rc) return rc;
-        return g.act == ACT_SIGMOID ? launch_any<EPI_DGRAD_DOWN_GLU>(p, ma, mb, mo, mo2, mo3, stream)
-                                    : launch_any<EPI_DGRAD_DOWN>(p, ma, mb, mo, mo2, mo3, stream);
+        return g.act == ACT_SIGMOID ? launch_any<EPI_DGRAD_DOWN_GLU>(p, ma, mb, mo, mo2, mo3, g.rows_cap, stream)
+                                    : launch_any<EPI_DGRAD_DOWN>(p, ma, mb, mo, mo2, mo3, g.rows_cap, stream);
     }
     if (g.o_map == nullptr && g.scale == nullptr) {
         rc = make_store_map(&mo, g.out, 0, g.rows_cap, g.N, g.ldo, 0, p.is_f16);
         if (rc) return rc;
     }
-    return launch_any<EPI_STORE>(p, ma, mb, mo, mo2, mo3, stream);
+    return launch_any<EPI_STORE>(p, ma, mb, mo, mo2, mo3, g.rows_cap, stream);
 }
 
 // Fused router: logits = x @ gate_wT on the tensor cores (one group of T rows, the experts are the tile's columns),
@@ -748,7 +760,7 @@ int umma_w_gemm(const WGemm& g, int dtype, int32_t* status, cudaStream_t stream)
     p.o3d = 1;
     rc = make_store_map(&mo, g.DW, g.E, g.Mout, g.Nout, g.d_sm, g.d_se, p.is_f16);
     if (rc) return rc;
-    return launch_any<EPI_STORE>(p, ma, mb, mo, mo, mo, stream);
+    return launch_any<EPI_STORE>(p, ma, mb, mo, mo, mo, g.rows_cap, stream);
 }
 
 }  // namespace b200moe

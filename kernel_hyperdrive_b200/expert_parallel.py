@@ -62,7 +62,9 @@ class CudaRowOps:
     @staticmethod
     def gate_grad(expanded: torch.Tensor, grad: torch.Tensor, k: int) -> torch.Tensor:
         """d_gates[t, j] = <expanded[t*k + j, :], grad[t, :]>."""
-        return _gate_grad(expanded, grad, k)
+        from .ops import gate_grad
+
+        return gate_grad(expanded, grad, k)
 
 
 class _AllToAllRows(torch.autograd.Function):
@@ -116,11 +118,7 @@ class _UnsortCombine(torch.autograd.Function):
         expanded, gates, ss = ctx.saved_tensors
         T, k = gates.shape
         grad = grad.contiguous()
-        gate_grad = getattr(ctx.ops, "gate_grad", None)  # optional in injected row operations
-        if gate_grad is not None:
-            d_gates = gate_grad(expanded, grad, k).to(gates.dtype)
-        else:
-            d_gates = torch.bmm(expanded.view(T, k, -1), grad.unsqueeze(2)).squeeze(-1).to(gates.dtype)
+        d_gates = _gate_grad_via(ctx.ops, expanded, grad, k).to(gates.dtype)
         # gradient of row n (sorted order) = gates[ss[n]] * grad[ss[n] // k]
         d_rows = ctx.ops.gather(grad, ss, k, gates.reshape(-1).contiguous())
         return d_rows, d_gates, None, None, None
@@ -168,11 +166,23 @@ def ep_experts(x, router_weights, selected_experts, num_experts: int, local_expe
 # exchange over peer memory: this package's kernels store to / load from the peers' buffers directly
 # --------------------------------------------------------------------------------------------------
 
+BARRIER_LIMIT_CYCLES = 4_000_000_000  # about two seconds of SM clock: a peer that never arrives ends the wait with status 302
+
+
+def _phase(name: str):
+    from .scattermoe import phase
+
+    return phase(name)
+
 
 class PeerExchange:
     """Four symmetric (cap_rows, H) buffers per rank, mapped into every rank of the group:
     "x" (dispatched tokens), "y" (expert outputs), "dy" (dispatched output gradients), "dx" (input gradients of the
-    received rows).  `barrier()` orders the ranks on the current stream through the symmetric-memory signal pads."""
+    received rows), plus a symmetric flag array for `barrier()`, which orders the ranks on the current stream with
+    this package's bounded barrier kernel (a missing peer gives status 302 after about two seconds instead of a hang).
+
+    The three methods `push`, `pull` and `barrier` are the whole interface the exchange logic uses; the CPU tests
+    substitute an object with the same methods that moves rows between per-rank host tensors."""
 
     def __init__(self, group, cap_rows: int, width: int, dtype: torch.dtype, device: torch.device):
         import ctypes
@@ -180,35 +190,69 @@ class PeerExchange:
         import torch.distributed._symmetric_memory as symm
 
         self.group, self.cap_rows, self.width = group, cap_rows, width
-        self.world = dist.get_world_size(group)
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.device = torch.device(device)
         self.bufs, self.peer_ptrs, self._handles = {}, {}, {}
         for name in ("x", "y", "dy", "dx"):
             t = symm.empty(cap_rows, width, dtype=dtype, device=device)
             hdl = symm.rendezvous(t, group)
             self.bufs[name], self._handles[name] = t, hdl
             self.peer_ptrs[name] = (ctypes.c_void_p * self.world)(*[int(p) for p in hdl.buffer_ptrs])
-        self._barrier_handle = self._handles["x"]
+        flags = symm.empty(64, dtype=torch.int32, device=device)
+        flags.zero_()
+        fh = symm.rendezvous(flags, group)
+        self._flags, self._flags_handle = flags, fh
+        self._flag_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in fh.buffer_ptrs])
+        self._epoch = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group)  # every rank's flags are zero before anyone publishes an epoch
         self.backward_reads_pending = False
-        self.host_rows = torch.empty(1, dtype=torch.int64).pin_memory()  # landing place of the per-pass host read
+        self.host_rows = torch.empty(2, dtype=torch.int64).pin_memory()  # landing place of the per-pass host read
 
     def barrier(self) -> None:
-        self._barrier_handle.barrier(channel=0)
+        from ._lib import check, lib, ptr, status_word, stream_ptr
+
+        self._epoch += 1
+        with _phase("ep_barrier"):
+            check(lib().b200moe_ep_barrier(self._flag_ptrs, self.rank, self.world, self._epoch, BARRIER_LIMIT_CYCLES, ptr(status_word(self.device)), stream_ptr(self.device)), "ep_barrier")
+
+    def push(self, name: str, src, idx, fan_out: int, coeff, plan: "_Plan") -> None:
+        from ._lib import check, dtype_code, lib, ptr, status_word, stream_ptr
+
+        with _phase("ep_push_" + name):
+            check(
+                lib().b200moe_ep_push_rows(ptr(src), src.stride(0), ptr(idx), fan_out, ptr(coeff), self.peer_ptrs[name], ptr(plan.start), ptr(plan.base),
+                                           self.world, plan.ss.numel(), src.size(1), self.cap_rows, dtype_code(src), ptr(status_word(src.device)), stream_ptr(src.device)),
+                "ep_push_rows",
+            )
+
+    def pull(self, name: str, gates, out, expanded, plan: "_Plan") -> None:
+        from ._lib import check, dtype_code, lib, ptr, stream_ptr
+
+        with _phase("ep_pull_" + name):
+            check(
+                lib().b200moe_ep_pull_combine(self.peer_ptrs[name], ptr(plan.inv), ptr(plan.start), ptr(plan.base), self.world, ptr(gates), ptr(out), out.stride(0),
+                                              ptr(expanded), out.size(0), plan.k, out.size(1), dtype_code(out), stream_ptr(out.device)),
+                "ep_pull_combine",
+            )
 
 
 class _Plan:
     """Where this rank's sorted rows go: computed once per pass from the all-gathered expert counts."""
 
-    __slots__ = ("ss", "inv", "start", "base", "m_recv", "local_ids", "k", "_recv_counts", "_host", "_event", "_e_local", "_world")
+    __slots__ = ("ss", "inv", "start", "base", "m_recv", "max_recv", "local_ids", "k", "_recv_counts", "_host", "_event", "_e_local", "_world")
 
     def resolve(self) -> None:
-        """Finish the plan with the one host read of the pass (the number of rows this rank receives sizes its local
-        tensors).  The copy was queued when the plan was made, before the dispatch kernel; called after that kernel and
-        its barrier are queued, the read returns while the GPU is still busy with them, so the device never waits for
-        the host to catch up."""
+        """Finish the plan with the one host read of the pass: the number of rows this rank receives (it sizes the local
+        tensors) and the largest number any rank receives (every rank sees the same value, so a buffer overflow is
+        refused by all ranks together).  The copy was queued when the plan was made, before the dispatch kernel; called
+        after that kernel and its barrier are queued, the read returns while the GPU is still busy with them, so the
+        device never waits for the host to catch up."""
         if self.m_recv is not None:
             return
-        self._event.synchronize()
-        self.m_recv = int(self._host.item())
+        if self._event is not None:
+            self._event.synchronize()
+        self.m_recv, self.max_recv = int(self._host[0].item()), int(self._host[1].item())
         global last_received_rows
         last_received_rows = self.m_recv
         dev = self._recv_counts.device
@@ -226,71 +270,43 @@ def _make_plan(selected_experts, num_experts: int, world: int, rank: int, group,
     plan.ss = ss
     plan.inv = torch.empty_like(ss)
     plan.inv[ss] = torch.arange(ss.numel(), device=ss.device)
-    counts_all = torch.empty(world, num_experts, dtype=counts.dtype, device=counts.device)
+    counts_all = torch.empty(world * num_experts, dtype=counts.dtype, device=counts.device)
     dist.all_gather_into_tensor(counts_all, counts.contiguous(), group=group)
+    counts_all = counts_all.view(world, num_experts)
     to_rank = counts_all.view(world, world, e_local).sum(-1)  # [source, destination]
     zero = torch.zeros(1, dtype=torch.int64, device=ss.device)
     plan.start = torch.cat([zero, to_rank[rank].cumsum(0)]).to(torch.int32)
     plan.base = (to_rank.cumsum(0) - to_rank)[rank].to(torch.int32)  # rows of lower-ranked sources in each destination
     recv_counts = counts_all[:, rank * e_local : (rank + 1) * e_local]
     plan._recv_counts, plan._e_local, plan._world = recv_counts, e_local, world
-    plan.m_recv, plan.local_ids = None, None
-    plan._host = host_rows if host_rows is not None else torch.empty(1, dtype=torch.int64).pin_memory()
-    plan._host.copy_(recv_counts.sum().to(torch.int64).reshape(1), non_blocking=True)
-    plan._event = torch.cuda.Event()
-    plan._event.record()
+    plan.m_recv, plan.max_recv, plan.local_ids = None, None, None
+    received = to_rank.sum(0).to(torch.int64)  # rows every rank receives: identical on all ranks
+    summary = torch.stack([received[rank], received.max()])
+    if ss.is_cuda:
+        plan._host = host_rows if host_rows is not None else torch.empty(2, dtype=torch.int64).pin_memory()
+        plan._host.copy_(summary, non_blocking=True)
+        plan._event = torch.cuda.Event()
+        plan._event.record()
+    else:
+        plan._host, plan._event = summary.clone(), None
     return plan
 
 
-def _push(xc: PeerExchange, name: str, src, idx, fan_out: int, coeff, plan: "_Plan") -> None:
-    from .scattermoe import _launch
-
-    _launch("ep_push_" + name, _push_impl, xc, name, src, idx, fan_out, coeff, plan)
-
-
-def _pull(xc: PeerExchange, name: str, gates, out, expanded, plan: "_Plan") -> None:
-    from .scattermoe import _launch
-
-    _launch("ep_pull_" + name, _pull_impl, xc, name, gates, out, expanded, plan)
-
-
-def _push_impl(xc: PeerExchange, name: str, src, idx, fan_out: int, coeff, plan: "_Plan") -> None:
-    from ._lib import check, dtype_code, lib, ptr, status_word, stream_ptr
-
-    M = plan.ss.numel()
-    check(
-        lib().b200moe_ep_push_rows(ptr(src), src.stride(0), ptr(idx), fan_out, ptr(coeff), xc.peer_ptrs[name], ptr(plan.start), ptr(plan.base),
-                                   xc.world, M, src.size(1), xc.cap_rows, dtype_code(src), ptr(status_word(src.device)), stream_ptr(src.device)),
-        "ep_push_rows",
-    )
-
-
-def _pull_impl(xc: PeerExchange, name: str, gates, out, expanded, plan: "_Plan") -> None:
-    from ._lib import check, dtype_code, lib, ptr, stream_ptr
-
-    check(
-        lib().b200moe_ep_pull_combine(xc.peer_ptrs[name], ptr(plan.inv), ptr(plan.start), ptr(plan.base), xc.world, ptr(gates), ptr(out), out.stride(0),
-                                      ptr(expanded), out.size(0), plan.k, out.size(1), dtype_code(out), stream_ptr(out.device)),
-        "ep_pull_combine",
-    )
-
-
-def _gate_grad(expanded: torch.Tensor, grad_y: torch.Tensor, k: int) -> torch.Tensor:
-    """d_gates (T, k): dot products of the kept expert rows with the output gradient of their token."""
-    from ._lib import check, dtype_code, lib, ptr, stream_ptr
-
-    T = grad_y.size(0)
-    d_gates = torch.empty(T, k, dtype=grad_y.dtype, device=grad_y.device)
-    check(
-        lib().b200moe_ep_gate_grad(ptr(expanded), expanded.stride(0), ptr(grad_y), grad_y.stride(0), ptr(d_gates), T, k, grad_y.size(1), dtype_code(grad_y), stream_ptr(grad_y.device)),
-        "ep_gate_grad",
-    )
-    return d_gates
+def _gate_grad_via(ops, expanded: torch.Tensor, grad: torch.Tensor, k: int) -> torch.Tensor:
+    """d_gates (T, k) through the row operations' `gate_grad` when they have one (the CUDA kernels do), else as the
+    batched product of the reference (injected torch doubles on CPU)."""
+    fn = getattr(ops, "gate_grad", None)
+    if fn is not None:
+        return fn(expanded, grad, k)
+    return torch.bmm(expanded.view(grad.size(0), k, -1), grad.unsqueeze(2)).squeeze(-1)
 
 
 class _PeerDispatch(torch.autograd.Function):
     """Forward: every rank stores its routed rows into the owners' "x" buffers.  Backward: the owners publish the
-    input gradients of the rows they received in "dx"; the source pulls them and sums the k slots of a token."""
+    input gradients of the rows they received in "dx"; the source pulls them and sums the k slots of a token.
+
+    The backward's barrier is part of the protocol on every rank: the layer's input must require a gradient on all
+    ranks or on none (`ep_experts_p2p` checks this across the group when `check_uniform` is set)."""
 
     @staticmethod
     def forward(ctx, x, xc, plan):
@@ -302,11 +318,13 @@ class _PeerDispatch(torch.autograd.Function):
         if xc.backward_reads_pending:
             xc.barrier()
         xc.backward_reads_pending = torch.is_grad_enabled()
-        _push(xc, "x", x.contiguous(), plan.ss, plan.k, None, plan)
+        xc.push("x", x.contiguous(), plan.ss, plan.k, None, plan)
         xc.barrier()  # all rows have landed
         plan.resolve()
-        if plan.m_recv > xc.cap_rows:  # the push kernel skipped the rows that did not fit and raised status 301
-            raise RuntimeError(f"expert-parallel exchange buffer too small: {plan.m_recv} rows arrive, capacity {xc.cap_rows}")
+        # The decision is the same on every rank (the largest receive count of the group), so either all ranks go on to
+        # the next barrier or none does.  Rows that did not fit were skipped by the push kernel (status 301).
+        if plan.max_recv > xc.cap_rows:
+            raise RuntimeError(f"expert-parallel exchange buffer too small: a rank receives {plan.max_recv} rows (this one {plan.m_recv}), capacity {xc.cap_rows}")
         return xc.bufs["x"][: plan.m_recv]
 
     @staticmethod
@@ -318,7 +336,7 @@ class _PeerDispatch(torch.autograd.Function):
         xc.barrier()  # every rank's "dx" rows are written
         xc.backward_reads_pending = False
         dx = torch.empty(ctx.shape, dtype=grad_recv.dtype, device=grad_recv.device)
-        _pull(xc, "dx", None, dx, None, plan)
+        xc.pull("dx", None, dx, None, plan)
         # the next write into "dx" comes after the next pass's barriers, which no rank passes before it finished this pull
         return dx, None, None
 
@@ -328,7 +346,7 @@ class _PeerCombine(torch.autograd.Function):
     gate-weighted sum.  Backward: gate gradients locally, gate-scaled output gradients stored into the owners' "dy"."""
 
     @staticmethod
-    def forward(ctx, out_rows, gates, xc, plan):
+    def forward(ctx, out_rows, gates, xc, plan, ops):
         T, k = gates.shape
         buf = xc.bufs["y"][: plan.m_recv]
         if out_rows.data_ptr() != buf.data_ptr():
@@ -337,9 +355,9 @@ class _PeerCombine(torch.autograd.Function):
         y = torch.empty(T, out_rows.size(1), dtype=out_rows.dtype, device=out_rows.device)
         expanded = torch.empty(T * k, out_rows.size(1), dtype=out_rows.dtype, device=out_rows.device)
         gates = gates.contiguous()
-        _pull(xc, "y", gates, y, expanded, plan)
+        xc.pull("y", gates, y, expanded, plan)
         ctx.save_for_backward(expanded, gates)
-        ctx.xc, ctx.plan = xc, plan
+        ctx.xc, ctx.plan, ctx.ops = xc, plan, ops
         return y
 
     @staticmethod
@@ -348,34 +366,74 @@ class _PeerCombine(torch.autograd.Function):
         xc, plan = ctx.xc, ctx.plan
         T, k = gates.shape
         grad_y = grad_y.contiguous()
-        d_gates = _gate_grad(expanded, grad_y, k)
-        _push(xc, "dy", grad_y, plan.ss, k, gates.reshape(-1), plan)
+        with _phase("ep_gate_grad"):
+            d_gates = _gate_grad_via(ctx.ops, expanded, grad_y, k).to(gates.dtype)
+        xc.push("dy", grad_y, plan.ss, k, gates.reshape(-1), plan)
         xc.barrier()  # all gradient rows have landed
-        return xc.bufs["dy"][: plan.m_recv], d_gates, None, None
+        return xc.bufs["dy"][: plan.m_recv], d_gates, None, None, None
 
 
-def ep_experts_p2p(x, router_weights, selected_experts, num_experts: int, local_experts_fn: Callable, xc: PeerExchange, ops=CudaRowOps):
+def ep_experts_p2p(x, router_weights, selected_experts, num_experts: int, local_experts_fn: Callable, xc, ops=CudaRowOps):
     """Routed experts over an expert-parallel group with the row exchange done by this package's kernels on peer
-    memory (see PeerExchange).  Same contract as `ep_experts`."""
+    memory (see PeerExchange).  Same contract as `ep_experts`.  `x.requires_grad` must agree across the ranks."""
     world, rank = xc.world, dist.get_rank(xc.group)
-    with torch.no_grad():
-        plan = _make_plan(selected_experts, num_experts, world, rank, xc.group, ops, xc.host_rows)
+    with torch.no_grad(), _phase("ep_plan"):
+        plan = _make_plan(selected_experts, num_experts, world, rank, xc.group, ops, getattr(xc, "host_rows", None))
     recv = _PeerDispatch.apply(x, xc, plan)
     out_rows = local_experts_fn(recv, plan.local_ids)
-    return _PeerCombine.apply(out_rows, router_weights.to(x.dtype), xc, plan)
+    return _PeerCombine.apply(out_rows, router_weights.to(x.dtype), xc, plan, ops)
+
+
+# --------------------------------------------------------------------------------------------------
+# expert -> rank placement
+# --------------------------------------------------------------------------------------------------
+
+
+def make_placement(kind, num_experts: int, world: int, expected_load=None) -> torch.Tensor | None:
+    """slot_of_expert (int64, E): the position of every expert in the rank-major order (rank = slot // (E / R)).
+
+    "contiguous" (None): expert e at slot e, i.e. rank r owns experts [r*E/R, (r+1)*E/R).
+    "strided": expert e on rank e % R.
+    "balanced": greedy longest-first assignment of `expected_load` (one non-negative number per expert, e.g. running
+        token counts) to the rank with the smallest load that still has a free slot, so that a skewed routing does not
+        pile the popular experts onto one rank.
+    A tensor / sequence of E distinct slots is taken as given.
+    """
+    e_local = num_experts // world
+    if kind is None or (isinstance(kind, str) and kind == "contiguous"):
+        return None
+    if isinstance(kind, str) and kind == "strided":
+        e = torch.arange(num_experts)
+        return (e % world) * e_local + e // world
+    if isinstance(kind, str) and kind == "balanced":
+        assert expected_load is not None and len(expected_load) == num_experts
+        load = torch.as_tensor(expected_load, dtype=torch.float64)
+        order = torch.argsort(load, descending=True, stable=True).tolist()
+        rank_load, rank_used = [0.0] * world, [0] * world
+        slot = torch.empty(num_experts, dtype=torch.int64)
+        for e in order:
+            r = min((r_ for r_ in range(world) if rank_used[r_] < e_local), key=lambda r_: (rank_load[r_], r_))
+            slot[e] = r * e_local + rank_used[r]
+            rank_used[r] += 1
+            rank_load[r] += float(load[e])
+        return slot
+    slot = torch.as_tensor(kind, dtype=torch.int64).clone()
+    assert slot.numel() == num_experts and torch.equal(slot.sort().values, torch.arange(num_experts)), "placement must be a permutation of the expert slots"
+    return slot
 
 
 class MoE_B200_EP(nn.Module):
-    """Expert-parallel MoE layer.  The gate is replicated; rank r holds experts [r*E/R, (r+1)*E/R).
+    """Expert-parallel MoE layer.  The gate is replicated; rank r holds the E/R experts whose slots
+    (`make_placement`; default: expert e at slot e) fall into [r*E/R, (r+1)*E/R).
 
     Weights are drawn expert by expert from a seed shared by all ranks, so the union of the shards equals
-    the single-GPU layer built from the same seed with `full_state_dict`-style gathering.
+    the single-GPU layer built from the same seed with `full_state_dict`-style gathering, whatever the placement.
     """
 
     def __init__(self, num_experts, num_experts_per_tok, hidden_size, intermediate_size, activation_function, is_glu, add_bias, std,
                  group=None, device=None, dtype=torch.float32, seed: int = 0, ops=CudaRowOps, local_experts_fn=None,
                  num_shared_experts: int = 0, shared_intermediate_size: int | None = None, router_scoring: str = "softmax",
-                 exchange: str = "nccl", exchange_rows: int | None = None):
+                 exchange: str = "nccl", exchange_rows: int | None = None, placement=None, expected_load=None):
         super().__init__()
         assert is_glu, "the expert-parallel layer implements GLU experts"
         assert router_scoring in ("softmax", "sigmoid")
@@ -385,6 +443,11 @@ class MoE_B200_EP(nn.Module):
         self.num_experts, self.top_k = num_experts, num_experts_per_tok
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
         self.e_local = num_experts // self.world
+        # expert -> slot in the rank-major order; the routing sees slots, so everything after it is placement-agnostic
+        slot_of_expert = make_placement(placement, num_experts, self.world, expected_load)
+        self.register_buffer("slot_of_expert", None if slot_of_expert is None else slot_of_expert.to(device), persistent=False)
+        expert_of_slot = torch.arange(num_experts) if slot_of_expert is None else torch.argsort(slot_of_expert)
+        self.expert_of_slot = expert_of_slot.tolist()
         self.ops = ops
         self._local_experts_fn = local_experts_fn
         self.act = activation_function
@@ -404,8 +467,9 @@ class MoE_B200_EP(nn.Module):
         with torch.no_grad():
             self.gate.weight.copy_(draw((num_experts, hidden_size), seed * 100003 + 1, hidden_size**-0.5))
         lo = self.rank * self.e_local
-        fc = [draw((2 * intermediate_size, hidden_size), seed * 100003 + 17 + 2 * e, std) for e in range(lo, lo + self.e_local)]
-        proj = [draw((hidden_size, intermediate_size), seed * 100003 + 18 + 2 * e, std) for e in range(lo, lo + self.e_local)]
+        mine = self.expert_of_slot[lo : lo + self.e_local]  # global ids of this rank's experts, in slot order
+        fc = [draw((2 * intermediate_size, hidden_size), seed * 100003 + 17 + 2 * e, std) for e in mine]
+        proj = [draw((hidden_size, intermediate_size), seed * 100003 + 18 + 2 * e, std) for e in mine]
         self.c_fc_weight = nn.Parameter(torch.stack(fc).to(device))
         self.c_proj_weight = nn.Parameter(torch.stack(proj).to(device))
         del fc, proj
@@ -455,6 +519,8 @@ class MoE_B200_EP(nn.Module):
                 dist.all_reduce(p.grad, group=self.group)
 
     def _compute_experts(self, hidden_states, router_weights, selected_experts):
+        if self.slot_of_expert is not None:
+            selected_experts = self.slot_of_expert[selected_experts]
         if self.exchange is not None:
             return ep_experts_p2p(hidden_states, router_weights, selected_experts, self.num_experts, self.local_experts, self.exchange, self.ops)
         return ep_experts(hidden_states, router_weights, selected_experts, self.num_experts, self.local_experts, self.group, self.ops)
@@ -470,11 +536,20 @@ class MoE_B200_EP(nn.Module):
         proj = [torch.empty_like(self.c_proj_weight) for _ in range(self.world)]
         dist.all_gather(fc, self.c_fc_weight.detach().contiguous(), group=self.group)
         dist.all_gather(proj, self.c_proj_weight.detach().contiguous(), group=self.group)
-        return {"gate.weight": self.gate.weight.detach().clone(), "c_fc.weight": torch.cat(fc), "c_proj.weight": torch.cat(proj)}
+        fc, proj = torch.cat(fc), torch.cat(proj)  # slot order
+        if self.slot_of_expert is not None:
+            fc, proj = fc[self.slot_of_expert], proj[self.slot_of_expert]  # expert order
+        return {"gate.weight": self.gate.weight.detach().clone(), "c_fc.weight": fc, "c_proj.weight": proj}
 
     def load_full_state_dict(self, sd: dict) -> None:
         lo, hi = self.rank * self.e_local, (self.rank + 1) * self.e_local
+        mine = torch.as_tensor(self.expert_of_slot[lo:hi], device=sd["c_fc.weight"].device)
         with torch.no_grad():
             self.gate.weight.copy_(sd["gate.weight"])
-            self.c_fc_weight.copy_(sd["c_fc.weight"][lo:hi])
-            self.c_proj_weight.copy_(sd["c_proj.weight"][lo:hi])
+            self.c_fc_weight.copy_(sd["c_fc.weight"][mine])
+            self.c_proj_weight.copy_(sd["c_proj.weight"][mine])
+
+    def expert_grads_in_expert_order(self):
+        """(d_c_fc, d_c_proj) of this rank's experts together with their global expert ids (int64, e_local)."""
+        lo = self.rank * self.e_local
+        return self.c_fc_weight.grad, self.c_proj_weight.grad, torch.as_tensor(self.expert_of_slot[lo : lo + self.e_local])

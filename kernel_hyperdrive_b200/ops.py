@@ -166,6 +166,26 @@ def combine(expanded: torch.Tensor, gates: torch.Tensor | None, out: torch.Tenso
 # ---- SwiGLU on a fused tensor ---------------------------------------------------------------------
 
 
+@b200_op("gate_grad", mutates_args={"d_gates"})
+def _gate_grad_op(expanded: torch.Tensor, grad: torch.Tensor, d_gates: torch.Tensor, k: int) -> None:
+    check(
+        lib().b200moe_ep_gate_grad(ptr(expanded), expanded.stride(0), ptr(grad), grad.stride(0), ptr(d_gates), grad.size(0), k, grad.size(1), dtype_code(grad), stream_ptr(grad.device)),
+        "gate_grad",
+    )
+
+
+def gate_grad(expanded: torch.Tensor, grad: torch.Tensor, k: int) -> torch.Tensor:
+    """d_gates[t, j] = <expanded[t*k + j, :], grad[t, :]> (fp32 sums in a fixed order, stored in the tensor type): the
+    gate gradient the reference forms with a batched product
+    (cute_kernels/kernels/scattermoe/triton_implementation/ops.py:204)."""
+    _require_cuda(expanded, grad)
+    _row_major(expanded, "expanded")
+    _row_major(grad, "grad")
+    d_gates = torch.empty(grad.size(0), k, dtype=grad.dtype, device=grad.device)
+    _gate_grad_op(expanded, grad, d_gates, k)
+    return d_gates
+
+
 def swiglu_unchunked_torch(x: torch.Tensor) -> torch.Tensor:
     """Eager definition: first half of the last dimension times silu of the second half."""
     up, gate = x.chunk(2, dim=-1)

@@ -26,7 +26,7 @@ from . import _lib
 from ._lib import check, dtype_code, lib, ptr, status_word, stream_ptr
 from .custom_op import b200_op
 from .router import fused_router, fused_router_supported
-from .ops import _workspace, combine, contiguous_count_cute, group, group_bwd_W, scatter2scatter, swiglu_unchunked_cute, swiglu_unchunked_torch
+from .ops import _workspace, combine, contiguous_count_cute, gate_grad, group, group_bwd_W, scatter2scatter, swiglu_unchunked_cute, swiglu_unchunked_torch
 
 # --------------------------------------------------------------------------------------------------
 # routing
@@ -112,7 +112,7 @@ class _ScatteredExperts(torch.autograd.Function):
         d_gates = None
         if gates is not None:
             # d_gates[t, j] = <expanded[t, j, :], grad_out[t, :]>
-            d_gates = torch.bmm(expanded.view(gates.size(0), gates.size(1), -1), grad_out.unsqueeze(2)).squeeze(-1)
+            d_gates = gate_grad(expanded, grad_out, gates.size(1))
 
         if grouped_out:
             grouped_grad_out = grad_out
@@ -167,6 +167,28 @@ def set_timing_sink(sink: list | None) -> None:
     _timing_sink = sink
 
 
+class phase:
+    """Context manager: with a timing sink installed, brackets the kernels queued inside it with two CUDA events on the
+    current stream and records them under `name` (no synchronisation); otherwise does nothing."""
+
+    def __init__(self, name: str):
+        self.name, self.start = name, None
+
+    def __enter__(self):
+        if _timing_sink is not None:
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.start.record()
+        return self
+
+    def __exit__(self, *exc):
+        sink = _timing_sink
+        if self.start is not None and sink is not None:
+            end = torch.cuda.Event(enable_timing=True)
+            end.record()
+            sink.append((self.name, self.start, end))
+        return False
+
+
 def _launch(name: str, fn, *args) -> None:
     sink = _timing_sink
     if sink is None:
@@ -199,7 +221,7 @@ def _up_forward(x: torch.Tensor, w_fc: torch.Tensor, expert_offsets: torch.Tenso
 
 
 @b200_op("down_forward", mutates_args={"y_expanded"})
-def _down_forward(a: torch.Tensor, w_proj: torch.Tensor, expert_offsets: torch.Tensor, row_slot: torch.Tensor, gates: torch.Tensor | None, y_expanded: torch.Tensor) -> None:
+def _down_forward(a: torch.Tensor, w_proj: torch.Tensor, expert_offsets: torch.Tensor, row_slot: torch.Tensor | None, gates: torch.Tensor | None, y_expanded: torch.Tensor) -> None:
     E, H, I = w_proj.shape
     check(
         lib().b200moe_down_forward(ptr(a), ptr(w_proj), ptr(expert_offsets), ptr(row_slot), ptr(gates), ptr(y_expanded), y_expanded.stride(0), y_expanded.size(0), H, I, E, a.size(0), dtype_code(a), ptr(status_word(a.device)), stream_ptr(a.device)),
@@ -207,14 +229,39 @@ def _down_forward(a: torch.Tensor, w_proj: torch.Tensor, expert_offsets: torch.T
     )
 
 
-@b200_op("down_dgrad", mutates_args={"dh", "ag", "d_gates"})
-def _down_dgrad(grad_out: torch.Tensor, w_proj: torch.Tensor, expert_offsets: torch.Tensor, row_token: torch.Tensor | None, row_slot: torch.Tensor, gates: torch.Tensor | None, h: torch.Tensor, dh: torch.Tensor, ag: torch.Tensor, d_gates: torch.Tensor, activation: int = 0) -> None:
+@b200_op("gather_grad_rows", mutates_args={"out", "d_gates"})
+def _gather_grad_rows(grad: torch.Tensor, row_token: torch.Tensor, row_slot: torch.Tensor, gates: torch.Tensor | None, y_expanded: torch.Tensor | None, out: torch.Tensor, d_gates: torch.Tensor | None, y_grouped: bool = False) -> None:
+    """out[p, :] = gates[row_slot[p]] * grad[row_token[p], :] (zeros on filler rows) and, when the unweighted expert
+    outputs are given, d_gates[s] = <y_expanded[s, :], grad[t, :]> in the same pass (`y_grouped`: the outputs are in
+    the padded grouped order, row p instead of row s)."""
+    check(
+        lib().b200moe_gather_grad_rows(ptr(grad), grad.stride(0), ptr(row_token), ptr(row_slot), ptr(gates), ptr(y_expanded), y_expanded.stride(0) if y_expanded is not None else 0,
+                                       int(y_grouped), ptr(out), out.stride(0), ptr(d_gates), out.size(0), grad.size(1), dtype_code(grad), stream_ptr(grad.device)),
+        "gather_grad_rows",
+    )
+
+
+@b200_op("combine_rows", mutates_args={"out"})
+def _combine_rows(rows: torch.Tensor, pos: torch.Tensor, gates: torch.Tensor | None, out: torch.Tensor, k: int) -> None:
+    """out[t, :] = sum_j gates[t, j] * rows[pos[t*k + j], :] (gates None: plain sum)."""
+    check(
+        lib().b200moe_combine_rows(ptr(rows), rows.stride(0), ptr(pos), ptr(gates), ptr(out), out.stride(0), out.size(0), k, out.size(1), dtype_code(rows), stream_ptr(rows.device)),
+        "combine_rows",
+    )
+
+
+@b200_op("invert_row_map", mutates_args={"slot_row"})
+def _invert_row_map(row_slot: torch.Tensor, slot_row: torch.Tensor) -> None:
+    """slot_row[row_slot[p]] = p for the real rows of the padded grouped order."""
+    check(lib().b200moe_invert_row_map(ptr(row_slot), row_slot.numel(), ptr(slot_row), slot_row.numel(), stream_ptr(row_slot.device)), "invert_row_map")
+
+
+@b200_op("down_dgrad", mutates_args={"dh"})
+def _down_dgrad(grad_rows: torch.Tensor, w_proj: torch.Tensor, expert_offsets: torch.Tensor, row_token: torch.Tensor | None, h: torch.Tensor, dh: torch.Tensor, activation: int = 0) -> None:
     E, H, I = w_proj.shape
     check(
-        lib().b200moe_down_dgrad(
-            ptr(grad_out), grad_out.stride(0), ptr(w_proj), ptr(expert_offsets), ptr(row_token), ptr(row_slot), ptr(gates), ptr(h), ptr(dh), ptr(ag), ptr(d_gates),
-            d_gates.numel(), H, I, E, h.size(0), activation, dtype_code(h), ptr(status_word(h.device)), stream_ptr(h.device),
-        ),
+        lib().b200moe_down_dgrad(ptr(grad_rows), grad_rows.stride(0), ptr(w_proj), ptr(expert_offsets), ptr(row_token), ptr(h), ptr(dh),
+                                 grad_rows.size(0), H, I, E, h.size(0), activation, dtype_code(h), ptr(status_word(h.device)), stream_ptr(h.device)),
         "down_dgrad",
     )
 
@@ -229,7 +276,7 @@ def _wgrad(P: torch.Tensor, p_map: torch.Tensor | None, Q: torch.Tensor, q_map: 
 
 
 @b200_op("up_dgrad", mutates_args={"dx_expanded"})
-def _up_dgrad(dh: torch.Tensor, w_fc: torch.Tensor, expert_offsets: torch.Tensor, row_slot: torch.Tensor, dx_expanded: torch.Tensor) -> None:
+def _up_dgrad(dh: torch.Tensor, w_fc: torch.Tensor, expert_offsets: torch.Tensor, row_slot: torch.Tensor | None, dx_expanded: torch.Tensor) -> None:
     E, I2, H = w_fc.shape
     check(
         lib().b200moe_up_dgrad(ptr(dh), ptr(w_fc), ptr(expert_offsets), ptr(row_slot), ptr(dx_expanded), dx_expanded.stride(0), dx_expanded.size(0), H, I2 // 2, E, dh.size(0), dtype_code(dh), ptr(status_word(dh.device)), stream_ptr(dh.device)),
@@ -272,14 +319,26 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
         _launch("up_forward", _up_forward, x_rows, w_fc, offsets, None, h, a, activation)
         if not KEEP_GATHERED_INPUT:
             x_rows = None
-        y_expanded = y_out[:M] if (k == 1 and y_out is not None) else torch.empty(M, H, device=x.device, dtype=x.dtype)
-        _launch("down_forward", _down_forward, a, w_proj, offsets, row_slot, gates, y_expanded)
-        if k == 1:
-            y = y_expanded
+        need_gate_grad = ctx.needs_input_grad[3]
+        if k == 1 and y_out is not None and not need_gate_grad:
+            # the rows must land in a caller's buffer in their original order (expert-parallel exchange): the epilogue
+            # scatters them there and applies the gate
+            y = y_out[:M]
+            _launch("down_forward", _down_forward, a, w_proj, offsets, row_slot, gates, y)
+            slot_row = y_rows = None
         else:
-            y = torch.empty(T, H, device=x.device, dtype=x.dtype)
-            combine(y_expanded, None, y, k)
-        ctx.save_for_backward(x, w_fc, w_proj, gates, offsets, row_token, row_slot, h, x_rows)
+            # The rows leave the down projection unweighted and in the padded grouped order (whole tiles stored by TMA);
+            # the combine pass un-sorts them while it forms the gate-weighted sum over the slots, which is the
+            # reference's bmm over its `output_expanded`.  The backward forms the gate gradient from the kept rows.
+            y_rows = torch.empty(cap, H, device=x.device, dtype=x.dtype)
+            _launch("down_forward", _down_forward, a, w_proj, offsets, None, None, y_rows)
+            slot_row = torch.empty(M, device=x.device, dtype=torch.int32)
+            _invert_row_map(row_slot, slot_row)
+            y = y_out[:T] if (k == 1 and y_out is not None) else torch.empty(T, H, device=x.device, dtype=x.dtype)
+            _combine_rows(y_rows, slot_row, gates, y, k)
+            if not need_gate_grad:
+                y_rows = None
+        ctx.save_for_backward(x, w_fc, w_proj, gates, offsets, row_token, row_slot, h, a, x_rows, y_rows, slot_row)
         ctx.k = k
         ctx.activation = activation
         ctx.rw_dtype = router_weights.dtype
@@ -288,27 +347,30 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_y):
-        x, w_fc, w_proj, gates, offsets, row_token, row_slot, h, x_rows = ctx.saved_tensors
+        x, w_fc, w_proj, gates, offsets, row_token, row_slot, h, a, x_rows, y_rows, slot_row = ctx.saved_tensors
         k = ctx.k
         T, H = x.shape
         E, I2, _ = w_fc.shape
-        I = I2 // 2
         M, cap = T * k, h.size(0)
         grad_y = grad_y.contiguous()
         need_x, need_w1, need_w2, need_g = ctx.needs_input_grad[:4]
 
-        dh = torch.empty(cap, I2, device=x.device, dtype=x.dtype)
-        ag = torch.empty(cap, I, device=x.device, dtype=x.dtype)
-        d_gates = torch.empty(M, device=x.device, dtype=torch.float32)
+        # upstream gradient rows in the padded grouped order, scaled by their gates (the reference's
+        # `group(grad_out, coeff=gates)`), and the gate gradient <unweighted expert output, upstream gradient>
         g_rows = torch.empty(cap, H, device=x.device, dtype=x.dtype)
-        _gather_rows(grad_y, row_token, g_rows)
-        _launch("down_dgrad", _down_dgrad, g_rows, w_proj, offsets, None, row_slot, gates, h, dh, ag, d_gates, ctx.activation)
+        d_gates = torch.empty(M, device=x.device, dtype=torch.float32) if (need_g and y_rows is not None) else None
+        _gather_grad_rows(grad_y, row_token, row_slot, gates, y_rows if d_gates is not None else None, g_rows, d_gates, True)
+        del y_rows
 
         d_w_proj = d_w_fc = d_x = d_rw = None
+        dh = None
+        if need_w1 or need_x:
+            dh = torch.empty(cap, I2, device=x.device, dtype=x.dtype)
+            _launch("down_dgrad", _down_dgrad, g_rows, w_proj, offsets, None, h, dh, ctx.activation)
         if need_w2:
             d_w_proj = torch.empty_like(w_proj)
-            _launch("down_wgrad", _wgrad, g_rows, None, ag, None, offsets, d_w_proj, cap)
-        del ag
+            _launch("down_wgrad", _wgrad, g_rows, None, a, None, offsets, d_w_proj, cap)
+        del a
         if need_w1:
             d_w_fc = torch.empty_like(w_fc)
             if x_rows is None:
@@ -317,14 +379,18 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
             _launch("up_wgrad", _wgrad, dh, None, x_rows, None, offsets, d_w_fc, cap)
         del g_rows
         if need_x:
-            dx_expanded = ctx.dx_out[:M] if ctx.dx_out is not None else torch.empty(M, H, device=x.device, dtype=x.dtype)
-            _launch("up_dgrad", _up_dgrad, dh, w_fc, offsets, row_slot, dx_expanded)
-            if k == 1:
-                d_x = dx_expanded
+            if ctx.dx_out is not None:  # k == 1: the rows go straight into the caller's buffer, in their original order
+                d_x = ctx.dx_out[:M]
+                _launch("up_dgrad", _up_dgrad, dh, w_fc, offsets, row_slot, d_x)
             else:
+                dx_rows = torch.empty(cap, H, device=x.device, dtype=x.dtype)
+                _launch("up_dgrad", _up_dgrad, dh, w_fc, offsets, None, dx_rows)
+                if slot_row is None:
+                    slot_row = torch.empty(M, device=x.device, dtype=torch.int32)
+                    _invert_row_map(row_slot, slot_row)
                 d_x = torch.empty(T, H, device=x.device, dtype=x.dtype)
-                combine(dx_expanded, None, d_x, k)
-        if need_g:
+                _combine_rows(dx_rows, slot_row, None, d_x, k)
+        if d_gates is not None:
             d_rw = d_gates.view(T, k).to(ctx.rw_dtype)
         return d_x, d_w_fc, d_w_proj, d_rw, None, None, None
 

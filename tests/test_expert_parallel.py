@@ -1,7 +1,10 @@
 """Expert-parallel exchange logic over gloo on CPU (world size 2 and 4): counts exchange, split sizes, row
-order, autograd through both all-to-alls, shard/gather of the state dict.  The CUDA row kernels and the
-fused expert kernels are replaced by torch-indexing doubles here (there is no GPU in this run); the GPU
-test-suite runs the real kernels on one rank."""
+order, autograd through both exchanges, shard/gather of the state dict, expert placement.  The CUDA row kernels and
+the fused expert kernels are replaced by torch-indexing doubles here (there is no GPU in this run).  Both exchanges
+are covered: the all-to-all one, and the peer-memory one, whose push / pull kernels are replaced by doubles that move
+rows between per-rank shared host tensors with the same placement arithmetic as the kernels
+(destination = the range of `start` a row falls in, position = base[d] + n - start[d]).  The GPU test-suite runs the
+real kernels on one rank, and on two ranks where two GPUs are visible."""
 
 import os
 import socket
@@ -33,6 +36,48 @@ class TorchRowOps:
         return e3.sum(1) if gates is None else (e3 * gates.view(-1, k, 1)).sum(1)
 
 
+class TorchPeerExchange:
+    """Stand-in for `PeerExchange` on CPU: every rank's buffers are shared host tensors visible to all ranks, `push`
+    and `pull` follow the kernels of csrc/ep.cu row by row, `barrier` is the process-group barrier."""
+
+    def __init__(self, group, shared, cap_rows):
+        self.group, self.world, self.rank = group, dist.get_world_size(group), dist.get_rank(group)
+        self.shared, self.cap_rows = shared, cap_rows
+        self.bufs = {name: shared[name][self.rank] for name in shared}
+        self.backward_reads_pending = False
+        self.barriers = 0
+        self.skipped = 0
+
+    def barrier(self):
+        self.barriers += 1
+        dist.barrier(self.group)
+
+    def _dest(self, plan, n):
+        d = torch.searchsorted(plan.start[1 : self.world].long().contiguous(), n, right=True)
+        return d, plan.base.long()[d] + n - plan.start.long()[d]
+
+    def push(self, name, src, idx, fan_out, coeff, plan):
+        n = torch.arange(plan.ss.numel())
+        d, pos = self._dest(plan, n)
+        s_ = idx if idx is not None else n
+        rows = src[s_ // fan_out]
+        if coeff is not None:
+            rows = rows * coeff[s_].unsqueeze(-1)
+        for dest in range(self.world):
+            sel = (d == dest) & (pos < self.cap_rows)
+            self.skipped += int(((d == dest) & (pos >= self.cap_rows)).sum())
+            self.shared[name][dest][pos[sel]] = rows[sel].detach()
+
+    def pull(self, name, gates, out, expanded, plan):
+        T, k = out.size(0), plan.k
+        d, pos = self._dest(plan, plan.inv)
+        rows = torch.stack([self.shared[name][int(di)][int(pi)] for di, pi in zip(d.tolist(), pos.tolist())]) if d.numel() else out.new_zeros(0, out.size(1))
+        if expanded is not None:
+            expanded.copy_(rows)
+        r3 = rows.view(T, k, -1)
+        out.copy_(r3.sum(1) if gates is None else (r3 * gates.view(T, k, 1)).sum(1))
+
+
 def eager_local_experts(rows, local_ids, w_fc, w_proj):
     out = torch.zeros(rows.size(0), w_proj.size(1), dtype=rows.dtype)
     for e in range(w_fc.size(0)):
@@ -48,12 +93,16 @@ def free_port():
         return s.getsockname()[1]
 
 
-def worker(rank, world, port, E, k, H, I, T, result_queue):
+def worker(rank, world, port, E, k, H, I, T, result_queue, shared=None, cap_rows=0, placement=None):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         torch.manual_seed(0)
-        layer = ep.MoE_B200_EP(E, k, H, I, kh.swiglu_unchunked_torch, True, False, 0.05, ops=TorchRowOps, local_experts_fn=eager_local_experts, seed=3)
+        load = [1.0 / (e + 1) for e in range(E)] if placement == "balanced" else None
+        layer = ep.MoE_B200_EP(E, k, H, I, kh.swiglu_unchunked_torch, True, False, 0.05, ops=TorchRowOps, local_experts_fn=eager_local_experts, seed=3,
+                               placement=placement, expected_load=load)
+        if shared is not None:
+            layer.exchange = TorchPeerExchange(dist.group.WORLD, shared, cap_rows)
         full = kh.MoE_Torch(E, k, H, I, kh.swiglu_unchunked_torch, True, False, 0.05)
         full.load_state_dict(layer.full_state_dict())
         # every rank draws all ranks' tokens so that it can evaluate the single-process layer on the union
@@ -70,14 +119,17 @@ def worker(rank, world, port, E, k, H, I, T, result_queue):
         y_all.backward(torch.cat(gs))
         lo = sum(t.size(0) for t in xs[:rank])
         hi = lo + xs[rank].size(0)
-        e0, e1 = rank * layer.e_local, (rank + 1) * layer.e_local
+        d_fc, d_proj, mine = layer.expert_grads_in_expert_order()
         errs = dict(
             y=(y - y_all[lo:hi]).abs().max().item(),
             dx=(x.grad - x_all.grad[lo:hi]).abs().max().item(),
-            d_fc=(layer.c_fc_weight.grad - full.c_fc.weight.grad[e0:e1]).abs().max().item(),
-            d_proj=(layer.c_proj_weight.grad - full.c_proj.weight.grad[e0:e1]).abs().max().item(),
+            d_fc=(d_fc - full.c_fc.weight.grad[mine]).abs().max().item(),
+            d_proj=(d_proj - full.c_proj.weight.grad[mine]).abs().max().item(),
             d_gate=(layer.gate.weight.grad - full.gate.weight.grad).abs().max().item(),
         )
+        if shared is not None:
+            errs["skipped_rows"] = float(layer.exchange.skipped)
+            errs["barriers_not_4"] = float(layer.exchange.barriers != 4)  # rows landed, y written, dy landed, dx written
         # state dict round trip
         sd = layer.full_state_dict()
         layer.load_full_state_dict(sd)
@@ -88,12 +140,20 @@ def worker(rank, world, port, E, k, H, I, T, result_queue):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,E,k", [(2, 8, 2), (4, 8, 3), (2, 6, 1)])
-def test_expert_parallel_matches_single_process_layer(world, E, k):
+def shared_exchange_buffers(world, cap_rows, H):
+    return {name: [torch.zeros(cap_rows, H).share_memory_() for _ in range(world)] for name in ("x", "y", "dy", "dx")}
+
+
+@pytest.mark.parametrize("exchange", ["all_to_all", "peer"])
+@pytest.mark.parametrize("world,E,k,placement", [(2, 8, 2, None), (4, 8, 3, None), (2, 6, 1, None), (4, 8, 2, "strided"), (2, 8, 3, "balanced")])
+def test_expert_parallel_matches_single_process_layer(world, E, k, placement, exchange):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = free_port()
-    procs = [ctx.Process(target=worker, args=(r, world, port, E, k, 32, 48, 40, q)) for r in range(world)]
+    T, H = 40, 32
+    cap_rows = (T + 3 * world) * k * world  # every row of every rank could land on one rank
+    shared = shared_exchange_buffers(world, cap_rows, H) if exchange == "peer" else None
+    procs = [ctx.Process(target=worker, args=(r, world, port, E, k, H, 48, T, q, shared, cap_rows, placement)) for r in range(world)]
     for p in procs:
         p.start()
     results = [q.get(timeout=180) for _ in range(world)]
@@ -103,6 +163,60 @@ def test_expert_parallel_matches_single_process_layer(world, E, k):
     for rank, errs in results:
         for name, v in errs.items():
             assert v < 2e-5, (rank, name, v)
+
+
+def overflow_worker(rank, world, port, q, shared, cap_rows):
+    """Exchange buffers too small for the busiest rank: every rank must refuse the pass (no rank may go on to a
+    barrier the others never reach), and the rows that did not fit must have been skipped, not written."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import datetime
+
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=30))
+    try:
+        E, k, H, I, T = 4, 2, 16, 24, 24
+        layer = ep.MoE_B200_EP(E, k, H, I, kh.swiglu_unchunked_torch, True, False, 0.05, ops=TorchRowOps, local_experts_fn=eager_local_experts, seed=1)
+        layer.exchange = TorchPeerExchange(dist.group.WORLD, shared, cap_rows)
+        x = torch.randn(T, H, generator=torch.Generator().manual_seed(rank))
+        # every token of every rank picks experts 0 and 1: rank 0 receives all 2 * T * world rows
+        sel = torch.tensor([[0, 1]]).expand(T, 2).contiguous()
+        rw = torch.full((T, 2), 0.5)
+        try:
+            layer._compute_experts(x, rw, sel)
+            q.put((rank, "no error", layer.exchange.barriers))
+        except RuntimeError as exc:
+            q.put((rank, "refused" if "exchange buffer too small" in str(exc) else repr(exc), layer.exchange.barriers))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_exchange_overflow_is_refused_by_every_rank_together():
+    world, cap_rows = 2, 40  # rank 0 would receive 2 * 24 * 2 = 96 rows
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = free_port()
+    shared = shared_exchange_buffers(world, cap_rows, 16)
+    procs = [ctx.Process(target=overflow_worker, args=(r, world, port, q, shared, cap_rows)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(r[1] == "refused" for r in results), results
+    assert len({r[2] for r in results}) == 1, results  # the ranks passed the same number of barriers
+
+
+def test_placement_helpers():
+    assert ep.make_placement(None, 8, 2) is None
+    strided = ep.make_placement("strided", 8, 4)
+    assert (strided // 2).tolist() == [0, 1, 2, 3, 0, 1, 2, 3]  # expert e on rank e % 4
+    load = [100.0] + [1.0] * 15
+    bal = ep.make_placement("balanced", 16, 4, load)
+    assert sorted(bal.tolist()) == list(range(16))
+    per_rank = [sum(load[e] for e in range(16) if bal[e] // 4 == r) for r in range(4)]
+    assert max(per_rank) == 103.0 and min(per_rank) == 4.0  # the heavy expert sits with three light ones
+    with pytest.raises(AssertionError):
+        ep.make_placement([0, 0, 1, 2], 4, 2)
 
 
 def mismatched_worker(rank, world, port, q):

@@ -180,7 +180,7 @@ def test_tma_row_gather_engine(E, k, T, K, N):
 def test_gate_grad_row_dots(dtype, T, k, H):
     """Gate gradient of the expert-parallel return path: row dots against the bmm of the reference
     (cute_kernels/kernels/scattermoe/triton_implementation/ops.py:204)."""
-    from kernel_hyperdrive_b200.expert_parallel import _gate_grad
+    from kernel_hyperdrive_b200.ops import gate_grad as _gate_grad
 
     torch.manual_seed(T + k)
     expanded = torch.randn(T * k, H, device="cuda").to(dtype)
