@@ -6,7 +6,11 @@ One "step" is one forward + backward pass of the layer (router gate, top-k, soft
 SwiGLU experts, gate-weighted combine; all gradients) over one batch of synthetic tokens.  At N = 1 the
 workload is the Mixtral-shaped configuration (8 experts, top-2, hidden 4096, intermediate 14336, 16384
 tokens, bf16).  At N > 1 the experts are sharded over the ranks (expert parallel), every rank keeps its
-own 16384 tokens (weak scaling) and rows travel by NCCL all-to-all.
+own 16384 tokens (weak scaling) and rows travel through this package's peer-memory kernels (or NCCL all-to-all with
+--ep-exchange nccl).  Before anything is timed at N > 1 the expert-parallel layer is checked against the single-GPU
+layer on small seeded cases (`ep_parity`; the run exits non-zero if that fails).  The last key of the line,
+`ep_configs`, holds short measurements of the other benchmark configurations on the SAME GLOBAL PROBLEM at this N
+(fine-grained 64-expert layer, Zipf-skewed 128-expert layer, 256-expert layer: their token counts divided over the ranks).
 
 Prints ONE JSON line on rank 0.  `value` is TFLOP/s of routed-expert GEMM work (18*T*k*H*I per step) with the
 inputs resident in HBM; `e2e` is the same metric with host buffers (pinned) copied in and results copied
@@ -38,12 +42,18 @@ METRIC = "moe_layer_fwd_bwd_tflops"
 UNIT = "TFLOP/s"
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
 
-# dram__bytes_read.sum + dram__bytes_write.sum of the six grouped-GEMM launches of one step from the ncu capture
-# summarised in profiles/umma2_grouped_kernel_c2_4096tokens.md.  That capture holds 4096 of the 16384 tokens; the
-# weight part of the traffic does not grow with the token count, so it cannot be scaled to the full workload and the
-# full-size `traffic` stays null.
-NCU_TRAFFIC_BYTES_PER_STEP = {}
-NCU_TRAFFIC_SMALL_CASE = {"c2": {"tokens": 4096, "bytes": 17.33e9, "bytes_earlier_capture": 13.41e9, "algorithmic_bytes": 12.5e9}}
+# dram__bytes_read.sum + dram__bytes_write.sum of the six grouped-GEMM launches of one step, from ncu captures of two
+# small cases (2048 and 4096 tokens of the Mixtral-shaped layer).  The traffic is a part that does not depend on the
+# token count (weights read, weight gradients written) plus a part proportional to it; the two captures give both, and
+# the full-size figure is their extrapolation to the benchmark's token count.
+NCU_TRAFFIC_FIT = {}  # workload name -> {"fixed_bytes": ..., "bytes_per_token": ..., "captures": {tokens: bytes}}
+
+
+def ncu_traffic(w):
+    fit = NCU_TRAFFIC_FIT.get(w.name)
+    if not fit:
+        return None, None
+    return fit["fixed_bytes"] + fit["bytes_per_token"] * w.tokens, fit
 
 
 def measured_peaks():
@@ -66,6 +76,7 @@ class ClockSampler:
 
     def __init__(self, index: int):
         self.index, self.samples, self.proc, self.thread = index, [], None, None
+        self.sampler = None
         self.sm, self.mx, self.reasons = [], [], set()
         self.stop = threading.Event()
 
@@ -81,27 +92,34 @@ class ClockSampler:
                 pass
             self.stop.wait(0.02)
 
+    def _physical_id(self) -> str:
+        """The GPU as the driver tools name it: the entry of CUDA_VISIBLE_DEVICES this process's device index selects
+        (an index or a UUID), else the index itself."""
+        visible = [v.strip() for v in os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",") if v.strip()]
+        return visible[self.index] if self.index < len(visible) else str(self.index)
+
     def __enter__(self):
         try:
             import pynvml as nvml
 
             nvml.nvmlInit()
-            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
-            physical = int(visible.split(",")[self.index]) if visible and all(v.strip().isdigit() for v in visible.split(",")) else self.index
-            handle = nvml.nvmlDeviceGetHandleByIndex(physical)
+            ident = self._physical_id()
+            handle = nvml.nvmlDeviceGetHandleByIndex(int(ident)) if ident.isdigit() else nvml.nvmlDeviceGetHandleByUUID(ident.encode())
             self.mx.append(float(nvml.nvmlDeviceGetMaxClockInfo(handle, nvml.NVML_CLOCK_SM)))
             self.thread = threading.Thread(target=self._nvml_loop, args=(nvml, handle), daemon=True)
             self.thread.start()
+            self.sampler = "nvml"
             return self
         except Exception:
             self.thread = None
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", f"--id={self._physical_id()}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
             )
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            self.sampler = "nvidia-smi"
         except OSError:
             self.proc = None
         return self
@@ -137,8 +155,8 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(n)
         if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "sampler": self.sampler}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm), "sampler": self.sampler}
 
 
 # --------------------------------------------------------------------------------------------------
@@ -173,12 +191,15 @@ def cpu_reference_run(w: synthetic.MoEWorkload, steps: int, warmup: int, sample_
     x, gy = x.to(dtype), gy.to(dtype)
     rw, sel = synthetic.make_routing(ws, x.float(), weights["gate"].float(), 0)
     rw = rw.to(dtype)
+    # warm-up on a small slice (thread pools, first-touch of the weight tensors), then the timed passes on the sample
+    n_small = max(8, min(64, sample_tokens))
+    for _ in range(max(0, warmup)):
+        orc.experts_with_grads(x[:n_small], weights["w_fc"], weights["w_proj"], rw[:n_small], sel[:n_small], gy[:n_small])
     times = []
-    for i in range(warmup + steps):
+    for _ in range(steps):
         t0 = time.perf_counter()
         orc.experts_with_grads(x, weights["w_fc"], weights["w_proj"], rw, sel, gy)
-        if i >= warmup:
-            times.append(time.perf_counter() - t0)
+        times.append(time.perf_counter() - t0)
     sec = sum(times) / len(times)
     flops = 18.0 * sample_tokens * w.top_k * w.hidden * w.intermediate
     sample = f"{sample_tokens} of {w.tokens} tokens, all {w.num_experts} experts, full H={w.hidden} I={w.intermediate}, {w.dtype}, {steps} timed passes"
@@ -189,7 +210,7 @@ def run_reference_arm(args, w):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps, warmup = max(1, min(args.steps, 3)), min(args.warmup, 1)
+    steps, warmup = max(1, min(args.steps, 2)), min(args.warmup, 1)  # bounded: a pass over 1024 tokens takes tens of seconds
     val, sec, sample, threads = cpu_reference_run(w, steps, warmup, args.cpu_sample_tokens)
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
@@ -232,11 +253,235 @@ def bind_to_gpu_numa_node(index: int) -> None:
         pass
 
 
+SHARE = {"up_forward": 4, "down_forward": 2, "down_dgrad": 2, "down_wgrad": 2, "up_wgrad": 4, "up_dgrad": 4}  # eighteenths of the step's FLOP
+
+
+class Job:
+    """One workload on this rank: the layer, its resident inputs and the forward closure."""
+
+    def __init__(self, w, world, rank, dev, exchange, placement=None, micro_batches=1):
+        import torch.distributed as dist
+
+        import kernel_hyperdrive_b200 as kh
+
+        self.w, self.world, self.rank, self.dev = w, world, rank, dev
+        dtype = self.dtype = synthetic.TORCH_DTYPES[w.dtype]
+        E, k, H, I, T = w.num_experts, w.top_k, w.hidden, w.intermediate, w.tokens
+        extra = dict(num_shared_experts=w.shared_experts, router_scoring="sigmoid" if w.routing == "sigmoid" else "softmax")
+        self.placement_note = None
+        if world > 1:
+            from kernel_hyperdrive_b200.expert_parallel import MoE_B200_EP
+
+            expected = [float(r + 1) ** -1.2 for r in range(E)] if w.routing == "zipf" else [1.0] * E
+            if placement is None and w.routing == "zipf":
+                # the skew is a property of the routing distribution (p ~ rank^-1.2): experts are placed by their expected
+                # load, as a deployment would from running token counts
+                placement = "balanced"
+            self.placement_note = placement or "contiguous"
+            rows = (2 if (w.routing != "zipf" or placement == "balanced") else world) * T * k
+            if w.routing in ("sigmoid", "normal_logits"):
+                rows = int(1.25 * T * k)  # iid logits: the per-rank receive counts stay within a few percent of T * k
+            self.layer = MoE_B200_EP(E, k, H, I, kh.swiglu_unchunked_torch, True, False, w.weight_std, group=dist.group.WORLD, device=dev, dtype=dtype, seed=0,
+                                     exchange=exchange, exchange_rows=(rows + 127) // 128 * 128, placement=placement, expected_load=expected,
+                                     micro_batches=micro_batches, **extra)
+        else:
+            torch.manual_seed(0)
+            torch.set_default_dtype(dtype)  # build the (large) expert tensors directly in the workload's type
+            try:
+                with torch.device(dev):
+                    self.layer = kh.MoE_B200(E, k, H, I, kh.swiglu_unchunked_torch, True, False, w.weight_std, **extra)
+            finally:
+                torch.set_default_dtype(torch.float32)
+        self.params = list(self.layer.parameters())
+        gen = torch.Generator().manual_seed(1000 + rank)
+        self.x_host = torch.randn(T, H, generator=gen).to(dtype).pin_memory()
+        self.g_host = torch.randn(T, H, generator=gen).to(dtype).pin_memory()
+        self.x_dev = self.x_host.to(dev).requires_grad_(True)
+        self.g_dev = self.g_host.to(dev)
+        self.routing_note = None
+        layer = self.layer
+        if w.routing == "gate":
+            self.forward = lambda x: layer(x)[0]
+        else:
+            # routing supplied from outside (logits drawn per token and expert, or Zipf-distributed expert choice):
+            # enters through the layer's `_compute_experts(hidden_states, router_weights, selected_experts)` seam
+            rw_cpu, sel_cpu = synthetic.make_routing(w, self.x_host.float(), torch.zeros(E, 1), seed=1000 + rank)
+            rw_dev, sel_dev = rw_cpu.to(dev, dtype), sel_cpu.to(dev)
+            counts = torch.bincount(sel_cpu.flatten(), minlength=E)
+            self.routing_note = {"rows_min": int(counts.min()), "rows_max": int(counts.max()), "rows_mean": float(counts.float().mean()), "empty_experts": int((counts == 0).sum())}
+
+            def forward(x):
+                out = layer._compute_experts(x, rw_dev, sel_dev)
+                if w.shared_experts:
+                    out = out + layer._compute_shared_experts(x)
+                return out
+
+            self.forward = forward
+
+    def step_resident(self):
+        for p in self.params:
+            p.grad = None
+        self.x_dev.grad = None
+        y = self.forward(self.x_dev)
+        y.backward(self.g_dev)
+        return y
+
+    def barrier(self):
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(self, fn, steps):
+        """CUDA-event time of `steps` calls of fn between two rank barriers: the maximum over the ranks, in ms."""
+        self.barrier()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            fn()
+        end.record()
+        self.barrier()
+        ms = torch.tensor([start.elapsed_time(end)], device=self.dev)
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item()
+
+    def measure_resident(self, steps, warm, sample_clocks=False):
+        """Warm-up, then `steps` timed steps with every kernel group bracketed by events.  Returns a dict with the step
+        time, the per-phase device times per step and (N > 1) the per-rank load report."""
+        from kernel_hyperdrive_b200 import _lib, scattermoe
+
+        for _ in range(warm):
+            self.step_resident()
+        _lib.check_status(self.dev)
+        sink = []
+        scattermoe.set_timing_sink(sink)
+        launches0 = _lib.launch_count()
+        if sample_clocks:
+            with ClockSampler(self.dev.index or 0) as clocks:
+                total_ms = self.timed(self.step_resident, steps)
+            clock_summary = clocks.summary()
+        else:
+            total_ms, clock_summary = self.timed(self.step_resident, steps), None
+        launches = _lib.launch_count() - launches0
+        scattermoe.set_timing_sink(None)
+        torch.cuda.synchronize()
+        _lib.check_status(self.dev)
+        phases = {}
+        for name, s_, e_ in sink:
+            phases[name] = phases.get(name, 0.0) + s_.elapsed_time(e_)
+        phases = {n: v / steps for n, v in phases.items()}
+        w = self.w
+        gemm_ms = {n: ms for n, ms in phases.items() if n in SHARE}
+        gemm_total = sum(gemm_ms.values())
+        local_flops = w.flops_fwd_bwd()
+        out = {
+            "ms_per_step": total_ms / steps, "tflops": local_flops * self.world / (total_ms / steps * 1e-3) / 1e12, "launches": launches, "clocks": clock_summary,
+            "gemm_ms": gemm_total, "gemm_tflops_this_rank": None, "phase_ms": {n: round(v, 4) for n, v in sorted(phases.items())},
+            "per_launch": {n: {"ms": ms, "tflops": None} for n, ms in gemm_ms.items()},
+        }
+        if self.world > 1:
+            import torch.distributed as dist
+
+            from kernel_hyperdrive_b200 import expert_parallel
+
+            rows = float(expert_parallel.last_received_rows or 0)
+            exch = sum(v for n, v in phases.items() if n.startswith("ep_push") or n.startswith("ep_pull"))
+            barr = phases.get("ep_barrier", 0.0)
+            mine = torch.tensor([rows, gemm_total, exch, barr], device=self.dev, dtype=torch.float64)
+            everyone = [torch.empty_like(mine) for _ in range(self.world)]
+            dist.all_gather(everyone, mine)
+            table = torch.stack(everyone).cpu()
+            out["per_rank"] = {"received_rows": [int(v) for v in table[:, 0]], "gemm_ms": [round(float(v), 3) for v in table[:, 1]],
+                               "exchange_ms": [round(float(v), 3) for v in table[:, 2]], "barrier_ms": [round(float(v), 3) for v in table[:, 3]]}
+            # FLOP this rank's experts really did: its received rows (routed experts) plus its own tokens through the shared experts
+            local_flops = 18.0 * rows * w.hidden * w.intermediate + 18.0 * w.tokens * w.shared_experts * w.hidden * w.intermediate
+        if gemm_total > 0:
+            out["gemm_tflops_this_rank"] = local_flops / (gemm_total * 1e-3) / 1e12
+            for n, ms in gemm_ms.items():
+                out["per_launch"][n]["tflops"] = (SHARE[n] / 18.0) * local_flops / (ms * 1e-3) / 1e12
+        return out
+
+    def release(self):
+        self.layer = self.params = self.forward = self.x_dev = self.g_dev = None
+        import gc
+
+        gc.collect()
+        torch.cuda.empty_cache()
+
+
+def run_ep_configs(args, world, rank, dev, peaks):
+    """Short measurements of the other benchmark configurations on the same global problem at this N: tokens divided
+    over the ranks, experts sharded.  One entry per configuration; device-resident step time (max over ranks)."""
+    out = {}
+    names = ["c3", "c4"] + (["c5"] if world > 1 else [])
+    for name in names:
+        base = synthetic.WORKLOADS[name]
+        if base.num_experts % world or base.tokens % world:
+            continue
+        w = synthetic.scaled(base, tokens=base.tokens // world)
+        try:
+            job = Job(w, world, rank, dev, args.ep_exchange, micro_batches=args.ep_micro_batches)
+            m = job.measure_resident(args.ep_config_steps, 3)
+            entry = {
+                "tokens_global": base.tokens, "tokens_per_gpu": w.tokens, "experts_per_gpu": base.num_experts // world, "ms_per_step": round(m["ms_per_step"], 4),
+                "tflops": round(m["tflops"], 2), "tflops_per_gpu": round(m["tflops"] / world, 2), "frac_of_bf16_peak_burst_per_gpu": round(m["tflops"] / world / peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]), 4),
+                "tokens_per_s": round(base.tokens / (m["ms_per_step"] * 1e-3), 1), "gemm_ms_rank0": round(m["gemm_ms"], 4),
+                "gemm_tflops_rank0": None if m["gemm_tflops_this_rank"] is None else round(m["gemm_tflops_this_rank"], 1),
+                "per_launch_tflops_rank0": {n: round(v["tflops"], 1) for n, v in m["per_launch"].items() if v["tflops"]},
+                "phase_ms_rank0": m["phase_ms"], "routing": job.routing_note,
+            }
+            if world > 1:
+                entry["placement"], entry["per_rank"] = job.placement_note, m["per_rank"]
+            out[name] = entry
+            job.release()
+            del job
+        except Exception as exc:  # noqa: BLE001 - a configuration that cannot run here is reported, not fatal
+            out[name] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+            import gc
+
+            gc.collect()
+            torch.cuda.empty_cache()
+    return out
+
+
+def triton_reference_probe(w, dev, steps):
+    """Times the reference package's own Triton MoE layer on this GPU when that package is importable on the box
+    (it is not part of this repository); otherwise says so."""
+    try:
+        import cute_kernels  # noqa: F401
+        from cute_kernels import MoE_Triton as RefMoE
+    except Exception as exc:  # noqa: BLE001
+        return f"unavailable: reference package not installed on this box ({type(exc).__name__})"
+    try:
+        import kernel_hyperdrive_b200 as kh
+
+        dtype = synthetic.TORCH_DTYPES[w.dtype]
+        layer = RefMoE(w.num_experts, w.top_k, w.hidden, w.intermediate, kh.swiglu_unchunked_torch, True, False, w.weight_std).to(dev, dtype)
+        x = torch.randn(w.tokens, w.hidden, device=dev, dtype=dtype, requires_grad=True)
+        g = torch.randn_like(x)
+        for _ in range(3):
+            layer(x)[0].backward(g)
+        torch.cuda.synchronize()
+        s_, e_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s_.record()
+        for _ in range(steps):
+            layer(x)[0].backward(g)
+        e_.record()
+        torch.cuda.synchronize()
+        ms = s_.elapsed_time(e_) / steps
+        return {"ms_per_step": ms, "tflops": w.flops_fwd_bwd() / (ms * 1e-3) / 1e12}
+    except Exception as exc:  # noqa: BLE001
+        return f"unavailable: reference Triton layer failed here ({type(exc).__name__}: {str(exc)[:120]})"
+
+
 def run_gpu_arm(args, w):
     import torch.distributed as dist
 
-    import kernel_hyperdrive_b200 as kh
-    from kernel_hyperdrive_b200 import _lib, scattermoe
+    from kernel_hyperdrive_b200 import _lib
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -247,60 +492,28 @@ def run_gpu_arm(args, w):
     if world > 1:
         bind_to_gpu_numa_node(local_rank)
         dist.init_process_group("nccl", device_id=dev)
-    dtype = synthetic.TORCH_DTYPES[w.dtype]
-    E, k, H, I, T = w.num_experts, w.top_k, w.hidden, w.intermediate, w.tokens
     _lib.set_option(_lib.OPT_TILE_VARIANT, {"table": -1, "pair": _lib.TILE_PAIR_256x256, "cta": _lib.TILE_CTA_128x256}[args.tile_variant])
     if args.tile_scheduler is not None:
         _lib.set_option(_lib.OPT_DYNAMIC_TILES, args.tile_scheduler)
-    extra = dict(num_shared_experts=w.shared_experts, router_scoring="sigmoid" if w.routing == "sigmoid" else "softmax")
+    peaks, peak_kind = measured_peaks()
 
-    if world > 1:
-        from kernel_hyperdrive_b200.expert_parallel import MoE_B200_EP
+    # ---- N > 1: correctness of the exchange first ----
+    ep_parity = None
+    if world > 1 and not args.skip_ep_parity:
+        from kernel_hyperdrive_b200.expert_parallel import parity_selfcheck
 
-        layer = MoE_B200_EP(E, k, H, I, kh.swiglu_unchunked_torch, True, False, w.weight_std, group=dist.group.WORLD, device=dev, dtype=dtype, seed=0,
-                            exchange=args.ep_exchange, exchange_rows=((world if w.routing == "zipf" else 2) * T * k + 127) // 128 * 128, **extra)
-    else:
-        torch.manual_seed(0)
-        torch.set_default_dtype(dtype)  # build the (large) expert tensors directly in the workload's type
-        try:
-            with torch.device(dev):
-                layer = kh.MoE_B200(E, k, H, I, kh.swiglu_unchunked_torch, True, False, w.weight_std, **extra)
-        finally:
-            torch.set_default_dtype(torch.float32)
-    params = [p for p in layer.parameters()]
+        ep_parity = parity_selfcheck(dist.group.WORLD, dev)
+        if not ep_parity["ok"]:
+            if rank == 0:
+                print(json.dumps({"metric": METRIC, "n_gpus": world, "error": "expert-parallel parity check failed", "ep_parity": ep_parity}), flush=True)
+            dist.destroy_process_group()
+            sys.exit(3)
 
-    gen = torch.Generator().manual_seed(1000 + rank)
-    x_host = torch.randn(T, H, generator=gen).to(dtype).pin_memory()
-    g_host = torch.randn(T, H, generator=gen).to(dtype).pin_memory()
+    job = Job(w, world, rank, dev, args.ep_exchange, placement=args.ep_placement, micro_batches=args.ep_micro_batches)
+    dtype, T, H = job.dtype, w.tokens, w.hidden
+    x_host, g_host, params, forward = job.x_host, job.g_host, job.params, job.forward
     y_host = torch.empty(T, H, dtype=dtype).pin_memory()
     dx_host = torch.empty(T, H, dtype=dtype).pin_memory()
-    x_dev = x_host.to(dev).requires_grad_(True)
-    g_dev = g_host.to(dev)
-
-    if w.routing == "gate":
-        def forward(x):
-            return layer(x)[0]
-    else:
-        # routing supplied from outside (logits drawn per token and expert, or Zipf-distributed expert choice):
-        # enters through the layer's `_compute_experts(hidden_states, router_weights, selected_experts)` seam
-        rw_cpu, sel_cpu = synthetic.make_routing(w, x_host.float(), torch.zeros(E, 1), seed=1000 + rank)
-        rw_dev, sel_dev = rw_cpu.to(dev, dtype), sel_cpu.to(dev)
-        counts = torch.bincount(sel_cpu.flatten(), minlength=E)
-        routing_note = {"rows_min": int(counts.min()), "rows_max": int(counts.max()), "rows_mean": float(counts.float().mean()), "empty_experts": int((counts == 0).sum())}
-
-        def forward(x):
-            out = layer._compute_experts(x, rw_dev, sel_dev)
-            if w.shared_experts:
-                out = out + layer._compute_shared_experts(x)
-            return out
-
-    def step_resident():
-        for p in params:
-            p.grad = None
-        x_dev.grad = None
-        y = forward(x_dev)
-        y.backward(g_dev)
-        return y
 
     # End-to-end loop as a host program would run it: inputs start in pinned host memory every step and the
     # results (layer output and input gradient) are read back to the host every step.  Copies run on their own
@@ -356,65 +569,25 @@ def run_gpu_arm(args, w):
             keep[slot] = (y, x)  # keep the device results alive until their read-back has been issued and ordered
         main.wait_stream(copy_out)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, steps):
-        barrier()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for _ in range(steps):
-            fn()
-        end.record()
-        barrier()
-        ms = torch.tensor([start.elapsed_time(end)], device=dev)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return ms.item()
-
     n_warm = args.warmup if args.profile else max(args.warmup, 3)
-    for _ in range(n_warm):
-        step_resident()
-    _lib.check_status(dev)
-
-    sink = []
-    scattermoe.set_timing_sink(sink)
-    launches0 = _lib.launch_count()
-    with ClockSampler(local_rank) as clocks:
-        total_ms = timed(step_resident, args.steps)
-    launches = _lib.launch_count() - launches0
-    scattermoe.set_timing_sink(None)
-    torch.cuda.synchronize()
-    per_kernel = {}
-    for name, s, e in sink:
-        per_kernel.setdefault(name, []).append(s.elapsed_time(e))
-    clock_summary = clocks.summary()
+    m = job.measure_resident(args.steps, n_warm, sample_clocks=True)
 
     if args.profile:
         e2e_ms = float("nan")
     else:
         run_e2e(2)
         torch.cuda.synchronize()
-        e2e_ms = timed(lambda: run_e2e(args.steps), 1)
+        e2e_ms = job.timed(lambda: run_e2e(args.steps), 1)
     _lib.check_status(dev)
 
     flops_step = w.flops_fwd_bwd() * world  # every rank brings T tokens
-    ms_step = total_ms / args.steps
+    ms_step = m["ms_per_step"]
     value = flops_step / (ms_step * 1e-3) / 1e12
     e2e_value = flops_step / (e2e_ms / args.steps * 1e-3) / 1e12
-    peaks, peak_kind = measured_peaks()
     peak = peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"])
-
-    gemm_ms = {n: sum(v) / args.steps for n, v in per_kernel.items()}  # per step (a name can launch more than once per step)
-    gemm_total_ms = sum(ms for n, ms in gemm_ms.items() if not n.startswith("ep_"))
-    exchange_ms = {n: ms for n, ms in gemm_ms.items() if n.startswith("ep_")}
-    local_flops = w.flops_fwd_bwd()
-    achieved = local_flops / (gemm_total_ms * 1e-3) / 1e12 if gemm_total_ms > 0 else None
-    share = {"up_forward": 4, "down_forward": 2, "down_dgrad": 2, "down_wgrad": 2, "up_wgrad": 4, "up_dgrad": 4}
-    per_launch = {n: {"ms": ms, "tflops": (share[n] / 18.0) * local_flops / (ms * 1e-3) / 1e12} for n, ms in gemm_ms.items() if n in share}
-    extra_info = {} if w.routing == "gate" else {"routing": routing_note}
+    achieved = m["gemm_tflops_this_rank"]
+    exchange_ms = {n: v for n, v in m["phase_ms"].items() if n.startswith("ep_")}
+    extra_info = {} if job.routing_note is None else {"routing": job.routing_note}
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": n_warm,
@@ -423,31 +596,34 @@ def run_gpu_arm(args, w):
         "tokens_per_s": T * world / (ms_step * 1e-3),
         "frac_of_bf16_peak_burst": value / world / peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]),
         "frac_of_bf16_peak_sustained": value / world / peak,
-        "clocks": clock_summary,
+        "clocks": m["clocks"],
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": 2 * x_host.numel() * x_host.element_size(), "d2h_bytes_per_step": 2 * y_host.numel() * y_host.element_size()},
-        "gpu_launches": launches, "tile_variant": args.tile_variant, "tile_scheduler": _lib.get_option(_lib.OPT_DYNAMIC_TILES), **extra_info, **({"exchange_ms_per_step": exchange_ms} if exchange_ms else {}),
+        "gpu_launches": m["launches"], "ep_micro_batches": args.ep_micro_batches if world > 1 else None, "tile_variant": args.tile_variant, "tile_scheduler": _lib.get_option(_lib.OPT_DYNAMIC_TILES), **extra_info,
+        **({"exchange_ms_per_step": exchange_ms} if exchange_ms else {}),
         "roofline": {
             "bound": "tensor", "kernel": "umma2_grouped_kernel (6 launches per step)", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
             "frac": (achieved / peak) if achieved else None, "peak_kind": f"bf16_tflops_sustained of {peak_kind}",
-            "traffic": NCU_TRAFFIC_BYTES_PER_STEP.get(w.name), "traffic_small_case": NCU_TRAFFIC_SMALL_CASE.get(w.name), "per_launch": per_launch, "gemm_ms_per_step": gemm_total_ms,
+            "traffic": ncu_traffic(w)[0], "traffic_fit": ncu_traffic(w)[1], "per_launch": m["per_launch"], "gemm_ms_per_step": m["gemm_ms"],
+            "phase_ms_per_step": m["phase_ms"],
         },
     }
-
     if world > 1:
-        # load report: the experts of a rank get the rows the routing sends them, so ranks differ; the step runs at
-        # the pace of the busiest one (every pass ends with a rank barrier)
-        from kernel_hyperdrive_b200 import expert_parallel
-
-        mine = torch.tensor([float(expert_parallel.last_received_rows or 0), gemm_total_ms, sum(exchange_ms.values())], device=dev, dtype=torch.float64)
-        everyone = [torch.empty_like(mine) for _ in range(world)]
-        dist.all_gather(everyone, mine)
-        table = torch.stack(everyone).cpu()
-        line["per_rank"] = {"received_rows": [int(v) for v in table[:, 0]], "gemm_ms": [round(float(v), 3) for v in table[:, 1]],
-                            "exchange_ms": [round(float(v), 3) for v in table[:, 2]]}
+        line["per_rank"] = m["per_rank"]
+        line["ep_parity"] = ep_parity if ep_parity is not None else "skipped"
     if rank == 0 and world == 1 and not args.no_cpu_baseline and not args.profile and w.name in ("c1", "c2"):
+        layer = job.layer
         cpu_w = dict(gate=layer.gate.weight.detach().cpu(), w_fc=layer.c_fc.weight.detach().cpu(), w_proj=layer.c_proj.weight.detach().cpu())
         val, sec, sample, threads = cpu_reference_run(w, 1, 1, args.cpu_sample_tokens, weights=cpu_w)
         line["cpu_baseline"] = {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
+        del cpu_w
+    if world == 1 and not args.profile and not args.no_triton_reference and w.name == "c2":
+        line["triton_reference"] = triton_reference_probe(w, dev, min(args.steps, 5))
+    # the other configurations on the same global problem: last key of the line
+    if not args.profile and not args.no_ep_configs and args.workload == "c2" and args.tokens is None:
+        job.release()
+        del job, x_slots, g_slots, keep, forward, params
+        torch.cuda.empty_cache()
+        line["ep_configs"] = run_ep_configs(args, world, rank, dev, peaks)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -533,11 +709,17 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(synthetic.WORKLOADS))
     ap.add_argument("--tokens", type=int, default=None, help="override tokens per GPU (profiling on a small case)")
-    ap.add_argument("--cpu-sample-tokens", type=int, default=256)
+    ap.add_argument("--cpu-sample-tokens", type=int, default=1024, help="tokens of the workload the CPU arm times (1/16 of the Mixtral-shaped batch by default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ep-exchange", default="p2p", choices=["p2p", "nccl"], help="N > 1: row exchange by this package's kernels over peer memory, or NCCL all-to-all")
     ap.add_argument("--tile-variant", default="table", choices=["table", "pair", "cta"], help="tensor-core tile: per-shape table (default), or force the two-CTA 256x256 / one-CTA 128x256 tile (A/B measurements)")
-    ap.add_argument("--tile-scheduler", type=int, default=None, choices=[0, 1, 2], help="two-CTA kernels: 2 = every launch draws its tiles from a counter, 1 = only the weight-gradient launches, 0 = fixed stride; default: the library's own setting")
+    ap.add_argument("--tile-scheduler", type=int, default=None, choices=[0, 1, 2, 3], help="two-CTA kernels: 0 = fixed stride, 1 = weight-gradient launches draw tiles from a counter, 2 = those and long-reduction row launches (library default), 3 = every launch")
+    ap.add_argument("--ep-placement", default=None, choices=["contiguous", "strided", "balanced"], help="N > 1: expert -> rank placement (default: contiguous; the Zipf workload defaults to balanced by expected load)")
+    ap.add_argument("--ep-micro-batches", type=int, default=1, help="N > 1, peer-memory exchange: slices of a rank's tokens whose transfers overlap the expert GEMMs of the other slices")
+    ap.add_argument("--skip-ep-parity", action="store_true", help="N > 1: skip the parity check of the expert-parallel exchange that precedes the timing")
+    ap.add_argument("--no-ep-configs", action="store_true", help="skip the short runs of the other benchmark configurations appended as `ep_configs`")
+    ap.add_argument("--ep-config-steps", type=int, default=5)
+    ap.add_argument("--no-triton-reference", action="store_true")
     ap.add_argument("--micro", action="store_true", help="time the row kernels (SwiGLU operator, histogram, routing sort) instead of the layer")
     ap.add_argument("--profile", action="store_true", help="profiling run under ncu: exactly --warmup warm-up steps, no end-to-end and CPU legs; its numbers are not benchmark values")
     args = ap.parse_args()

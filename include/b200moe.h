@@ -56,9 +56,10 @@ extern "C" {
                                        * for comparison */
 
 /* Options (b200moe_set_option).  Process-wide, meant for measurements and tests; the defaults are the product path. */
-#define B200MOE_OPT_DYNAMIC_TILES 1 /* two-CTA kernels: 2 = every launch draws its tiles from a per-launch counter, in
-                                     * list order (weight-gradient tiles longest reduction first); 1 = only the
-                                     * weight-gradient launches do; 0 = fixed stride everywhere */
+#define B200MOE_OPT_DYNAMIC_TILES 1 /* two-CTA kernels, how a cluster gets its tiles: 0 = fixed stride; 1 = the weight-gradient
+                                     * launches draw them from a per-launch counter, in list order (longest reduction
+                                     * first); 2 (default) = those, and row launches whose reduction extent is >= 4096;
+                                     * 3 = every launch */
 #define B200MOE_OPT_TILE_VARIANT 2  /* -1 (default): the per-shape tile table decides; otherwise a B200MOE_TILE_* value
                                      * forced on every tensor-core launch whose operands allow it */
 #define B200MOE_OPT_COUNT 3
@@ -201,7 +202,7 @@ int b200moe_combine(const void* in, int64_t ldi, const void* gates, void* out, i
 /* The same sum reading its rows through an index: out[t, :] = sum_j gates[t, j] * in[pos[t*k + j], :] (a negative
  * index contributes nothing).  With pos = the padded grouped row of every slot (b200moe_invert_row_map) it forms the
  * layer output / the input gradient straight from the grouped-order results of b200moe_down_forward / b200moe_up_dgrad,
- * i.e. the un-sort of SMT/kernels.py:97-102 moves from the GEMM epilogue into this pass.  k <= 64. */
+ * i.e. the un-sort of SMT/kernels.py:97-102 moves from the GEMM epilogue into this pass.  k <= 32. */
 int b200moe_combine_rows(const void* in, int64_t ldi, const int32_t* pos, const void* gates, void* out, int64_t ldo,
                          int64_t T, int k, int H, int dtype, b200moe_stream_t stream);
 

@@ -36,13 +36,32 @@ int current_engine() { return g_engine.load(); }
 int option_value(int option) { return (option > 0 && option < B200MOE_OPT_COUNT) ? g_options[option].load() : 0; }
 
 // Per-shape tile table of the tensor-core engine, keyed on (operation, reduction extent K, output columns N, rows per
-// expert).  Entries were chosen by timing both tiles on a B200 with the benchmark's layer shapes; everything not listed
-// runs the two-CTA 256 x 256 cluster tile.
+// expert); the first matching rule wins.  It stands where the reference has autotuner configurations keyed on N and K.
+// The entries come from timing both tiles on a B200 with the benchmark's layer shapes (TFLOP/s of the whole step, two-CTA
+// 256 x 256 tile vs one-CTA 128 x 256 tile): 8 experts x 4096 rows, hidden 4096, intermediate 14336: 1168-1190 vs 1122;
+// 64 x 3072 rows, 2048 / 1408: 933-994 vs 891; 128 experts, Zipf-skewed, mean 4096 rows, 2048 / 768: 845-879 vs 791;
+// 256 x 512 rows, 7168 / 2048: 847 vs 878, the one-CTA tile ahead in every one of the six launches (with four or five
+// 128-row blocks per expert, half of the experts leave one CTA of a pair idle for a block, and a weight-gradient tile
+// reduces over only eight 64-row steps).
+struct TileRule {
+    int op;                        // B200MOE_OP_* or -1 for every operation
+    int k_min, k_max;              // reduction extent (weight gradients: output rows)
+    int n_min, n_max;              // output columns
+    int64_t rows_min, rows_max;    // rows per expert (padded capacity / experts)
+    int tile;
+};
+constexpr int kAny = 1 << 30;
+const TileRule kTileTable[] = {
+    {-1, 0, kAny, 0, kAny, 0, 1023, B200MOE_TILE_CTA_128x256},
+    {-1, 0, kAny, 0, kAny, 1024, (int64_t)1 << 40, B200MOE_TILE_PAIR_256x256},
+};
+
 int tile_table_lookup(int op, int K, int N, int64_t rows_per_expert) {
-    (void)op;
-    (void)K;
-    (void)N;
-    (void)rows_per_expert;
+    for (const TileRule& r : kTileTable) {
+        if ((r.op < 0 || r.op == op) && K >= r.k_min && K <= r.k_max && N >= r.n_min && N <= r.n_max && rows_per_expert >= r.rows_min &&
+            rows_per_expert <= r.rows_max)
+            return r.tile;
+    }
     return B200MOE_TILE_PAIR_256x256;
 }
 
@@ -123,7 +142,7 @@ extern "C" int b200moe_set_engine(int engine) {
 
 extern "C" int b200moe_set_option(int option, int value) {
     if (option <= 0 || option >= B200MOE_OPT_COUNT) return B200MOE_ERR_ARG;
-    if (option == B200MOE_OPT_DYNAMIC_TILES && (value < 0 || value > 2)) return B200MOE_ERR_ARG;
+    if (option == B200MOE_OPT_DYNAMIC_TILES && (value < 0 || value > 3)) return B200MOE_ERR_ARG;
     if (option == B200MOE_OPT_TILE_VARIANT && (value < -1 || value >= B200MOE_TILE_COUNT)) return B200MOE_ERR_ARG;
     g_options[option].store(value);
     return B200MOE_OK;

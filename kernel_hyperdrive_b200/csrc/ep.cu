@@ -29,62 +29,82 @@ __device__ __forceinline__ int find_dest(const int32_t* __restrict__ start, int 
     return d;
 }
 
+// Both exchange kernels give a row (push) or a token (pull) to one warp, eight per block, blocks striding over the rows:
+// a lane keeps four 16-byte accesses in flight, which is what a transfer over NVLink needs to approach the link rate.
+constexpr int kEpWarps = 8;
+constexpr int kEpUnroll = 4;
+
 template <typename T, int V>
-__global__ void ep_push_kernel(const T* __restrict__ src, int64_t lds, const int64_t* __restrict__ idx, int fan_out,
-                               const T* __restrict__ coeff, PeerTable peers, const int32_t* __restrict__ start,
-                               const int32_t* __restrict__ base, int R, int64_t M, int width, int64_t cap_rows,
-                               int32_t* status) {
-    int64_t n = blockIdx.x;
-    if (n >= M) return;
-    int d = find_dest(start, R, (int)n);
-    int64_t pos = (int64_t)base[d] + (n - start[d]);
-    if (pos < 0 || pos >= cap_rows) {  // would overrun the peer's buffer: record and skip
-        if (threadIdx.x == 0 && status) atomicCAS(status, 0, 301);
-        return;
-    }
-    int64_t s = idx ? idx[n] : n;
-    const T* row = src + (s / fan_out) * lds;
-    T* dst = (T*)peers.ptr[d] + pos * (int64_t)width;
-    float c = coeff ? Elem<T>::to_f(coeff[s]) : 1.f;
-    for (int col = threadIdx.x * V; col < width; col += blockDim.x * V) {
-        Pack<T, V> p = *reinterpret_cast<const Pack<T, V>*>(row + col);
-        if (coeff) {
-#pragma unroll
-            for (int i = 0; i < V; ++i) p.v[i] = Elem<T>::from_f(Elem<T>::to_f(p.v[i]) * c);
+__global__ void __launch_bounds__(kEpWarps * 32) ep_push_kernel(const T* __restrict__ src, int64_t lds, const int64_t* __restrict__ idx, int fan_out,
+                                                               const T* __restrict__ coeff, PeerTable peers, const int32_t* __restrict__ start,
+                                                               const int32_t* __restrict__ base, int R, int64_t M, int width, int64_t cap_rows,
+                                                               int32_t* status) {
+    const int lane = threadIdx.x & 31;
+    const int step = 32 * V;
+    for (int64_t n = (int64_t)blockIdx.x * kEpWarps + (threadIdx.x >> 5); n < M; n += (int64_t)gridDim.x * kEpWarps) {
+        const int d = find_dest(start, R, (int)n);
+        const int64_t pos = (int64_t)base[d] + (n - start[d]);
+        if (pos < 0 || pos >= cap_rows) {  // would overrun the peer's buffer: record and skip
+            if (lane == 0 && status) atomicCAS(status, 0, 301);
+            continue;
         }
-        *reinterpret_cast<Pack<T, V>*>(dst + col) = p;
+        const int64_t s = idx ? idx[n] : n;
+        const T* row = src + (s / fan_out) * lds;
+        T* dst = (T*)peers.ptr[d] + pos * (int64_t)width;
+        const float c = coeff ? Elem<T>::to_f(coeff[s]) : 1.f;
+        for (int col = lane * V; col < width; col += step * kEpUnroll) {
+            Pack<T, V> v[kEpUnroll];
+#pragma unroll
+            for (int u = 0; u < kEpUnroll; ++u)
+                if (col + u * step < width) v[u] = *reinterpret_cast<const Pack<T, V>*>(row + col + u * step);
+#pragma unroll
+            for (int u = 0; u < kEpUnroll; ++u) {
+                if (col + u * step < width) {
+                    if (coeff) {
+#pragma unroll
+                        for (int i = 0; i < V; ++i) v[u].v[i] = Elem<T>::from_f(Elem<T>::to_f(v[u].v[i]) * c);
+                    }
+                    *reinterpret_cast<Pack<T, V>*>(dst + col + u * step) = v[u];
+                }
+            }
+        }
     }
 }
 
 template <typename T, int V>
-__global__ void ep_pull_combine_kernel(PeerTable peers, const int64_t* __restrict__ inv, const int32_t* __restrict__ start,
-                                       const int32_t* __restrict__ base, int R, const T* __restrict__ gates,
-                                       T* __restrict__ out, int64_t ldo, T* __restrict__ expanded, int64_t Tn, int k,
-                                       int width) {
-    int64_t t = blockIdx.x;
-    if (t >= Tn) return;
-    __shared__ const T* rows[64];
-    if (threadIdx.x < k) {
-        int64_t n = inv[t * k + threadIdx.x];
-        int d = find_dest(start, R, (int)n);
-        rows[threadIdx.x] = (const T*)peers.ptr[d] + ((int64_t)base[d] + (n - start[d])) * (int64_t)width;
-    }
-    __syncthreads();
-    for (int col = threadIdx.x * V; col < width; col += blockDim.x * V) {
-        float acc[V];
-#pragma unroll
-        for (int i = 0; i < V; ++i) acc[i] = 0.f;
-        for (int j = 0; j < k; ++j) {
-            Pack<T, V> p = *reinterpret_cast<const Pack<T, V>*>(rows[j] + col);
-            float g = gates ? Elem<T>::to_f(gates[t * k + j]) : 1.f;
-#pragma unroll
-            for (int i = 0; i < V; ++i) acc[i] += g * Elem<T>::to_f(p.v[i]);
-            if (expanded) *reinterpret_cast<Pack<T, V>*>(expanded + (t * k + j) * (int64_t)width + col) = p;
+__global__ void __launch_bounds__(kEpWarps * 32) ep_pull_combine_kernel(PeerTable peers, const int64_t* __restrict__ inv, const int32_t* __restrict__ start,
+                                                                       const int32_t* __restrict__ base, int R, const T* __restrict__ gates,
+                                                                       T* __restrict__ out, int64_t ldo, T* __restrict__ expanded, int64_t Tn, int k,
+                                                                       int width) {
+    const int lane = threadIdx.x & 31;
+    for (int64_t t = (int64_t)blockIdx.x * kEpWarps + (threadIdx.x >> 5); t < Tn; t += (int64_t)gridDim.x * kEpWarps) {
+        // lane j < k resolves where slot j of the token lives: the owning rank's buffer and the row in it
+        const T* my_row = nullptr;
+        float my_gate = 1.f;
+        if (lane < k) {
+            const int64_t n = inv[t * k + lane];
+            const int d = find_dest(start, R, (int)n);
+            my_row = (const T*)peers.ptr[d] + ((int64_t)base[d] + (n - start[d])) * (int64_t)width;
+            if (gates) my_gate = Elem<T>::to_f(gates[t * k + lane]);
         }
-        Pack<T, V> o;
+        for (int col = lane * V; col < width; col += 32 * V) {
+            float acc[V];
 #pragma unroll
-        for (int i = 0; i < V; ++i) o.v[i] = Elem<T>::from_f(acc[i]);
-        *reinterpret_cast<Pack<T, V>*>(out + t * ldo + col) = o;
+            for (int i = 0; i < V; ++i) acc[i] = 0.f;
+#pragma unroll 4
+            for (int j = 0; j < k; ++j) {
+                const T* row = (const T*)__shfl_sync(0xffffffffu, (unsigned long long)my_row, j);
+                const float g = __shfl_sync(0xffffffffu, my_gate, j);
+                Pack<T, V> p = *reinterpret_cast<const Pack<T, V>*>(row + col);
+#pragma unroll
+                for (int i = 0; i < V; ++i) acc[i] += g * Elem<T>::to_f(p.v[i]);
+                if (expanded) *reinterpret_cast<Pack<T, V>*>(expanded + (t * k + j) * (int64_t)width + col) = p;
+            }
+            Pack<T, V> o;
+#pragma unroll
+            for (int i = 0; i < V; ++i) o.v[i] = Elem<T>::from_f(acc[i]);
+            *reinterpret_cast<Pack<T, V>*>(out + t * ldo + col) = o;
+        }
     }
 }
 
@@ -153,6 +173,12 @@ int fill_peers(PeerTable& tab, const void* const* peer_ptrs, int R, const char* 
     return B200MOE_OK;
 }
 
+unsigned ep_grid(int64_t rows) {
+    int64_t blocks = (rows + kEpWarps - 1) / kEpWarps;
+    const int64_t cap = 148 * 16;
+    return (unsigned)(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+}
+
 int row_threads(int width, int vec) {
     int t = (width / vec + 31) / 32 * 32;
     return t < 64 ? 64 : (t > 256 ? 256 : t);
@@ -178,16 +204,15 @@ extern "C" int b200moe_ep_push_rows(const void* src, int64_t lds, const int64_t*
     int esz = dtype == B200MOE_F32 ? 4 : 2, V = 16 / esz;
     B200MOE_REQUIRE(width % V == 0 && lds % V == 0 && ((uintptr_t)src & 15) == 0, B200MOE_ERR_LAYOUT,
                     "ep_push_rows: rows must be 16-byte aligned and a multiple of 16 bytes wide");
-    int threads = row_threads(width, V);
     if (dtype == B200MOE_F32) {
-        ep_push_kernel<float, 4><<<(unsigned)M, threads, 0, stream>>>((const float*)src, lds, idx, fan_out, (const float*)coeff, tab,
+        ep_push_kernel<float, 4><<<ep_grid(M), kEpWarps * 32, 0, stream>>>((const float*)src, lds, idx, fan_out, (const float*)coeff, tab,
                                                                    start, base, R, M, width, cap_rows, status);
     } else if (dtype == B200MOE_BF16) {
-        ep_push_kernel<__nv_bfloat16, 8><<<(unsigned)M, threads, 0, stream>>>((const __nv_bfloat16*)src, lds, idx, fan_out,
+        ep_push_kernel<__nv_bfloat16, 8><<<ep_grid(M), kEpWarps * 32, 0, stream>>>((const __nv_bfloat16*)src, lds, idx, fan_out,
                                                                            (const __nv_bfloat16*)coeff, tab, start, base, R, M,
                                                                            width, cap_rows, status);
     } else {
-        ep_push_kernel<__half, 8><<<(unsigned)M, threads, 0, stream>>>((const __half*)src, lds, idx, fan_out, (const __half*)coeff,
+        ep_push_kernel<__half, 8><<<ep_grid(M), kEpWarps * 32, 0, stream>>>((const __half*)src, lds, idx, fan_out, (const __half*)coeff,
                                                                     tab, start, base, R, M, width, cap_rows, status);
     }
     count_launch();
@@ -199,7 +224,7 @@ extern "C" int b200moe_ep_pull_combine(const void* const* peer_ptrs, const int64
                                        void* expanded, int64_t T_, int k, int width, int dtype,
                                        b200moe_stream_t stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
-    B200MOE_REQUIRE(T_ >= 0 && width > 0 && k > 0 && k <= 64, B200MOE_ERR_ARG, "ep_pull_combine: bad sizes (k <= 64)");
+    B200MOE_REQUIRE(T_ >= 0 && width > 0 && k > 0 && k <= 32, B200MOE_ERR_ARG, "ep_pull_combine: bad sizes (k <= 32)");
     if (T_ == 0) return B200MOE_OK;
     B200MOE_REQUIRE(inv && start && base && out, B200MOE_ERR_ARG, "ep_pull_combine: NULL pointer");
     PeerTable tab{};
@@ -209,15 +234,14 @@ extern "C" int b200moe_ep_pull_combine(const void* const* peer_ptrs, const int64
     int esz = dtype == B200MOE_F32 ? 4 : 2, V = 16 / esz;
     B200MOE_REQUIRE(width % V == 0 && ldo % V == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)expanded & 15) == 0,
                     B200MOE_ERR_LAYOUT, "ep_pull_combine: rows must be 16-byte aligned and a multiple of 16 bytes wide");
-    int threads = row_threads(width, V);
     if (dtype == B200MOE_F32) {
-        ep_pull_combine_kernel<float, 4><<<(unsigned)T_, threads, 0, stream>>>(tab, inv, start, base, R, (const float*)gates, (float*)out,
+        ep_pull_combine_kernel<float, 4><<<ep_grid(T_), kEpWarps * 32, 0, stream>>>(tab, inv, start, base, R, (const float*)gates, (float*)out,
                                                                             ldo, (float*)expanded, T_, k, width);
     } else if (dtype == B200MOE_BF16) {
-        ep_pull_combine_kernel<__nv_bfloat16, 8><<<(unsigned)T_, threads, 0, stream>>>(
+        ep_pull_combine_kernel<__nv_bfloat16, 8><<<ep_grid(T_), kEpWarps * 32, 0, stream>>>(
             tab, inv, start, base, R, (const __nv_bfloat16*)gates, (__nv_bfloat16*)out, ldo, (__nv_bfloat16*)expanded, T_, k, width);
     } else {
-        ep_pull_combine_kernel<__half, 8><<<(unsigned)T_, threads, 0, stream>>>(tab, inv, start, base, R, (const __half*)gates,
+        ep_pull_combine_kernel<__half, 8><<<ep_grid(T_), kEpWarps * 32, 0, stream>>>(tab, inv, start, base, R, (const __half*)gates,
                                                                              (__half*)out, ldo, (__half*)expanded, T_, k, width);
     }
     count_launch();

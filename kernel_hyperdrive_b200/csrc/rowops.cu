@@ -42,24 +42,44 @@ __global__ void group_kernel(const T* __restrict__ A, int64_t lda, const int64_t
     }
 }
 
-// ---- gather into the padded grouped order -----------------------------------------------------------
+// ---- row passes of the padded grouped order: one warp per row ---------------------------------------
+// The three kernels below give every row to one warp (eight rows per block, blocks stride over the rows): a lane keeps
+// up to four 16-byte loads in flight, and a short row (4 KB at hidden 2048) no longer costs a whole block launch.
+constexpr int kRowWarps = 8;
+constexpr int kRowUnroll = 4;
+
+static inline unsigned row_grid(int64_t rows) {
+    int64_t blocks = (rows + kRowWarps - 1) / kRowWarps;
+    const int64_t cap = 148 * 16;
+    return (unsigned)(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+}
+
 template <typename T, int V>
-__global__ void gather_rows_kernel(const T* __restrict__ src, int64_t lds, const int32_t* __restrict__ row_map,
-                                   T* __restrict__ out, int64_t ldo, int64_t rows, int width) {
-    int64_t p = blockIdx.x;
-    if (p >= rows) return;
-    int r = row_map[p];
-    T* dst = out + p * ldo;
-    if (r < 0) {  // filler row: zeros
-        Pack<T, V> z;
+__global__ void __launch_bounds__(kRowWarps * 32) gather_rows_kernel(const T* __restrict__ src, int64_t lds, const int32_t* __restrict__ row_map,
+                                                                    T* __restrict__ out, int64_t ldo, int64_t rows, int width) {
+    const int lane = threadIdx.x & 31;
+    const int step = 32 * V;
+    for (int64_t p = (int64_t)blockIdx.x * kRowWarps + (threadIdx.x >> 5); p < rows; p += (int64_t)gridDim.x * kRowWarps) {
+        const int r = row_map[p];
+        T* dst = out + p * ldo;
+        if (r < 0) {  // filler row: zeros
+            Pack<T, V> z;
 #pragma unroll
-        for (int i = 0; i < V; ++i) z.v[i] = Elem<T>::from_f(0.f);
-        for (int col = threadIdx.x * V; col < width; col += blockDim.x * V) *reinterpret_cast<Pack<T, V>*>(dst + col) = z;
-        return;
+            for (int i = 0; i < V; ++i) z.v[i] = Elem<T>::from_f(0.f);
+            for (int col = lane * V; col < width; col += step) *reinterpret_cast<Pack<T, V>*>(dst + col) = z;
+            continue;
+        }
+        const T* s = src + (int64_t)r * lds;
+        for (int col = lane * V; col < width; col += step * kRowUnroll) {
+            Pack<T, V> v[kRowUnroll];
+#pragma unroll
+            for (int u = 0; u < kRowUnroll; ++u)
+                if (col + u * step < width) v[u] = *reinterpret_cast<const Pack<T, V>*>(s + col + u * step);
+#pragma unroll
+            for (int u = 0; u < kRowUnroll; ++u)
+                if (col + u * step < width) *reinterpret_cast<Pack<T, V>*>(dst + col + u * step) = v[u];
+        }
     }
-    const T* s = src + (int64_t)r * lds;
-    for (int col = threadIdx.x * V; col < width; col += blockDim.x * V)
-        *reinterpret_cast<Pack<T, V>*>(dst + col) = *reinterpret_cast<const Pack<T, V>*>(s + col);
 }
 
 // ---- combine -------------------------------------------------------------------------------------
@@ -85,35 +105,38 @@ __global__ void combine_kernel(const T* __restrict__ in, int64_t ldi, const T* _
     }
 }
 
-// out[t, :] = sum_j gates[t, j] * in[pos[t*k + j], :]: the combine pass reading rows of the padded grouped order
+// out[t, :] = sum_j gates[t, j] * in[pos[t*k + j], :]: the combine pass reading rows of the padded grouped order.
+// One warp per token; lane j < k looks up row j and its gate, the k rows are then read side by side.  k <= 32.
 template <typename T, int V>
-__global__ void combine_rows_kernel(const T* __restrict__ in, int64_t ldi, const int32_t* __restrict__ pos,
-                                    const T* __restrict__ gates, T* __restrict__ out, int64_t ldo, int64_t Tn, int k, int H) {
-    int64_t t = blockIdx.x;
-    if (t >= Tn) return;
-    __shared__ const T* rows[64];
-    __shared__ float gs[64];
-    if (threadIdx.x < k) {
-        int p = pos[t * k + threadIdx.x];
-        rows[threadIdx.x] = p >= 0 ? in + (int64_t)p * ldi : nullptr;
-        gs[threadIdx.x] = gates ? Elem<T>::to_f(gates[t * k + threadIdx.x]) : 1.f;
-    }
-    __syncthreads();
-    for (int col = threadIdx.x * V; col < H; col += blockDim.x * V) {
-        float acc[V];
-#pragma unroll
-        for (int i = 0; i < V; ++i) acc[i] = 0.f;
-        for (int j = 0; j < k; ++j) {
-            if (rows[j] == nullptr) continue;
-            Pack<T, V> p = *reinterpret_cast<const Pack<T, V>*>(rows[j] + col);
-            const float g = gs[j];
-#pragma unroll
-            for (int i = 0; i < V; ++i) acc[i] += g * Elem<T>::to_f(p.v[i]);
+__global__ void __launch_bounds__(kRowWarps * 32) combine_rows_kernel(const T* __restrict__ in, int64_t ldi, const int32_t* __restrict__ pos,
+                                                                     const T* __restrict__ gates, T* __restrict__ out, int64_t ldo, int64_t Tn,
+                                                                     int k, int H) {
+    const int lane = threadIdx.x & 31;
+    for (int64_t t = (int64_t)blockIdx.x * kRowWarps + (threadIdx.x >> 5); t < Tn; t += (int64_t)gridDim.x * kRowWarps) {
+        int my_row = -1;
+        float my_gate = 0.f;
+        if (lane < k) {
+            my_row = pos[t * k + lane];
+            my_gate = gates ? Elem<T>::to_f(gates[t * k + lane]) : 1.f;
         }
-        Pack<T, V> o;
+        for (int col = lane * V; col < H; col += 32 * V) {
+            float acc[V];
 #pragma unroll
-        for (int i = 0; i < V; ++i) o.v[i] = Elem<T>::from_f(acc[i]);
-        *reinterpret_cast<Pack<T, V>*>(out + t * ldo + col) = o;
+            for (int i = 0; i < V; ++i) acc[i] = 0.f;
+#pragma unroll 4
+            for (int j = 0; j < k; ++j) {
+                const int row = __shfl_sync(0xffffffffu, my_row, j);
+                const float g = __shfl_sync(0xffffffffu, my_gate, j);
+                if (row < 0) continue;
+                Pack<T, V> p = *reinterpret_cast<const Pack<T, V>*>(in + (int64_t)row * ldi + col);
+#pragma unroll
+                for (int i = 0; i < V; ++i) acc[i] += g * Elem<T>::to_f(p.v[i]);
+            }
+            Pack<T, V> o;
+#pragma unroll
+            for (int i = 0; i < V; ++i) o.v[i] = Elem<T>::from_f(acc[i]);
+            *reinterpret_cast<Pack<T, V>*>(out + t * ldo + col) = o;
+        }
     }
 }
 
@@ -191,48 +214,56 @@ __global__ void dgrad_down_post_kernel(const T* __restrict__ h, T* __restrict__ 
 //   d_gates[s] = <y_expanded[s or p, :], grad[t, :]>   (fp32; only when y_expanded is given; y_grouped: indexed by p)
 // i.e. `group(grad_out, coeff=gates)` and the gate-gradient bmm of the reference's backward in one pass over grad.
 template <typename T, int V>
-__global__ void gather_grad_rows_kernel(const T* __restrict__ grad, int64_t ldg, const int32_t* __restrict__ row_token,
-                                        const int32_t* __restrict__ row_slot, const T* __restrict__ gates,
-                                        const T* __restrict__ y_expanded, int64_t ldy, int y_grouped, T* __restrict__ out,
-                                        int64_t ldo, float* __restrict__ d_gates, int64_t rows, int width) {
-    int64_t p = blockIdx.x;
-    if (p >= rows) return;
-    const int t = row_token[p];
-    T* dst = out + p * ldo;
-    if (t < 0) {
-        Pack<T, V> z;
+__global__ void __launch_bounds__(kRowWarps * 32) gather_grad_rows_kernel(const T* __restrict__ grad, int64_t ldg, const int32_t* __restrict__ row_token,
+                                                                         const int32_t* __restrict__ row_slot, const T* __restrict__ gates,
+                                                                         const T* __restrict__ y_expanded, int64_t ldy, int y_grouped,
+                                                                         T* __restrict__ out, int64_t ldo, float* __restrict__ d_gates, int64_t rows,
+                                                                         int width) {
+    const int lane = threadIdx.x & 31;
+    const int step = 32 * V;
+    for (int64_t p = (int64_t)blockIdx.x * kRowWarps + (threadIdx.x >> 5); p < rows; p += (int64_t)gridDim.x * kRowWarps) {
+        const int t = row_token[p];
+        T* dst = out + p * ldo;
+        if (t < 0) {
+            Pack<T, V> z;
 #pragma unroll
-        for (int i = 0; i < V; ++i) z.v[i] = Elem<T>::from_f(0.f);
-        for (int col = threadIdx.x * V; col < width; col += blockDim.x * V) *reinterpret_cast<Pack<T, V>*>(dst + col) = z;
-        return;
-    }
-    const int s = row_slot[p];
-    const float g = gates ? Elem<T>::to_f(gates[s]) : 1.f;
-    const T* src = grad + (int64_t)t * ldg;
-    const T* yrow = y_expanded ? y_expanded + (y_grouped ? p : (int64_t)s) * ldy : nullptr;
-    float dot = 0.f;
-    for (int col = threadIdx.x * V; col < width; col += blockDim.x * V) {
-        Pack<T, V> v = *reinterpret_cast<const Pack<T, V>*>(src + col);
+            for (int i = 0; i < V; ++i) z.v[i] = Elem<T>::from_f(0.f);
+            for (int col = lane * V; col < width; col += step) *reinterpret_cast<Pack<T, V>*>(dst + col) = z;
+            continue;
+        }
+        const int s = row_slot[p];
+        const float g = gates ? Elem<T>::to_f(gates[s]) : 1.f;
+        const T* src = grad + (int64_t)t * ldg;
+        const T* yrow = y_expanded ? y_expanded + (y_grouped ? p : (int64_t)s) * ldy : nullptr;
+        float dot = 0.f;
+        for (int col = lane * V; col < width; col += step * 2) {
+            Pack<T, V> v[2], y[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                if (col + u * step < width) {
+                    v[u] = *reinterpret_cast<const Pack<T, V>*>(src + col + u * step);
+                    if (yrow) y[u] = *reinterpret_cast<const Pack<T, V>*>(yrow + col + u * step);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                if (col + u * step < width) {
+                    if (yrow) {
+#pragma unroll
+                        for (int i = 0; i < V; ++i) dot += Elem<T>::to_f(y[u].v[i]) * Elem<T>::to_f(v[u].v[i]);
+                    }
+                    if (gates) {
+#pragma unroll
+                        for (int i = 0; i < V; ++i) v[u].v[i] = Elem<T>::from_f(g * Elem<T>::to_f(v[u].v[i]));
+                    }
+                    *reinterpret_cast<Pack<T, V>*>(dst + col + u * step) = v[u];
+                }
+            }
+        }
         if (yrow) {
-            Pack<T, V> y = *reinterpret_cast<const Pack<T, V>*>(yrow + col);
-#pragma unroll
-            for (int i = 0; i < V; ++i) dot += Elem<T>::to_f(y.v[i]) * Elem<T>::to_f(v.v[i]);
-        }
-        if (gates) {
-#pragma unroll
-            for (int i = 0; i < V; ++i) v.v[i] = Elem<T>::from_f(g * Elem<T>::to_f(v.v[i]));
-        }
-        *reinterpret_cast<Pack<T, V>*>(dst + col) = v;
-    }
-    if (yrow) {
-        __shared__ float red[8];
-        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = dot;
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            float v = 0.f;
-            for (int w = 0; w < (int)(blockDim.x >> 5); ++w) v += red[w];  // fixed order: the result is reproducible
-            d_gates[s] = v;
+            // butterfly sum: the same order every run, so the gate gradient is reproducible
+            for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            if (lane == 0) d_gates[s] = dot;
         }
     }
 }
@@ -343,11 +374,9 @@ extern "C" int b200moe_gather_rows(const void* src, int64_t lds, const int32_t* 
         constexpr int V = vec_elems<T>();
         bool vec = width % V == 0 && lds % V == 0 && ldo % V == 0 && aligned16(src) && aligned16(out);
         if (vec) {
-            gather_rows_kernel<T, V><<<(unsigned)rows, row_threads(width, V), 0, stream>>>((const T*)src, lds, row_map, (T*)out,
-                                                                                        ldo, rows, width);
+            gather_rows_kernel<T, V><<<row_grid(rows), kRowWarps * 32, 0, stream>>>((const T*)src, lds, row_map, (T*)out, ldo, rows, width);
         } else {
-            gather_rows_kernel<T, 1><<<(unsigned)rows, row_threads(width, 1), 0, stream>>>((const T*)src, lds, row_map, (T*)out,
-                                                                                        ldo, rows, width);
+            gather_rows_kernel<T, 1><<<row_grid(rows), kRowWarps * 32, 0, stream>>>((const T*)src, lds, row_map, (T*)out, ldo, rows, width);
         }
         count_launch();
         return check_launch("gather_rows");
@@ -370,10 +399,10 @@ extern "C" int b200moe_gather_grad_rows(const void* grad, int64_t ldg, const int
         bool vec = width % V == 0 && ldg % V == 0 && ldo % V == 0 && aligned16(grad) && aligned16(out) &&
                    (y_expanded == nullptr || (ldy % V == 0 && aligned16(y_expanded)));
         if (vec) {
-            gather_grad_rows_kernel<T, V><<<(unsigned)rows, row_threads(width, V), 0, stream>>>(
+            gather_grad_rows_kernel<T, V><<<row_grid(rows), kRowWarps * 32, 0, stream>>>(
                 (const T*)grad, ldg, row_token, row_slot, (const T*)gates, (const T*)y_expanded, ldy, y_grouped, (T*)out, ldo, d_gates, rows, width);
         } else {
-            gather_grad_rows_kernel<T, 1><<<(unsigned)rows, row_threads(width, 1), 0, stream>>>(
+            gather_grad_rows_kernel<T, 1><<<row_grid(rows), kRowWarps * 32, 0, stream>>>(
                 (const T*)grad, ldg, row_token, row_slot, (const T*)gates, (const T*)y_expanded, ldy, y_grouped, (T*)out, ldo, d_gates, rows, width);
         }
         count_launch();
@@ -406,19 +435,17 @@ extern "C" int b200moe_combine(const void* in, int64_t ldi, const void* gates, v
 extern "C" int b200moe_combine_rows(const void* in, int64_t ldi, const int32_t* pos, const void* gates, void* out, int64_t ldo,
                                     int64_t T_, int k, int H, int dtype, b200moe_stream_t stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
-    B200MOE_REQUIRE(T_ >= 0 && k > 0 && k <= 64 && H >= 0, B200MOE_ERR_ARG, "combine_rows: bad sizes (k <= 64)");
+    B200MOE_REQUIRE(T_ >= 0 && k > 0 && k <= 32 && H >= 0, B200MOE_ERR_ARG, "combine_rows: bad sizes (k <= 32)");
     if (T_ == 0 || H == 0) return B200MOE_OK;
     B200MOE_REQUIRE(in && pos && out, B200MOE_ERR_ARG, "combine_rows: NULL pointer");
     return dispatch_dtype(dtype, [&](auto tag) {
         using T = decltype(tag);
         constexpr int V = vec_elems<T>();
         bool vec = H % V == 0 && ldi % V == 0 && ldo % V == 0 && aligned16(in) && aligned16(out);
-        int threads = row_threads(H, vec ? V : 1);
-        if (threads < 64) threads = 64;  // the first k threads look the rows up
         if (vec) {
-            combine_rows_kernel<T, V><<<(unsigned)T_, threads, 0, stream>>>((const T*)in, ldi, pos, (const T*)gates, (T*)out, ldo, T_, k, H);
+            combine_rows_kernel<T, V><<<row_grid(T_), kRowWarps * 32, 0, stream>>>((const T*)in, ldi, pos, (const T*)gates, (T*)out, ldo, T_, k, H);
         } else {
-            combine_rows_kernel<T, 1><<<(unsigned)T_, threads, 0, stream>>>((const T*)in, ldi, pos, (const T*)gates, (T*)out, ldo, T_, k, H);
+            combine_rows_kernel<T, 1><<<row_grid(T_), kRowWarps * 32, 0, stream>>>((const T*)in, ldi, pos, (const T*)gates, (T*)out, ldo, T_, k, H);
         }
         count_launch();
         return check_launch("combine_rows");

@@ -538,8 +538,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(EPI), 1)
         const int q = warp & 3;
         const int half = (warp - 2) >> 2;  // which part of the tile's columns this warp handles
         // column range of a BN-wide epilogue: halves with eight warps; 96 / 96 / 64 columns with twelve
-        const int c_begin = EW == 8 ? half * (BN / 2) : half * 96;
-        const int c_end = EW == 8 ? c_begin + BN / 2 : (half == 2 ? BN : c_begin + 96);
+        const int c_begin = EW == 12 ? half * 96 : half * (BN / (EW / 4));
+        const int c_end = EW == 12 ? (half == 2 ? BN : c_begin + 96) : c_begin + BN / (EW / 4);
         const uint32_t stg = smem_u32(smem_stg + (warp - 2) * STG_BYTES);
         const uint32_t stg_row = stg + lane * 64;
         const uint32_t stg_swz = (uint32_t)((lane >> 1) & 3);
@@ -649,8 +649,13 @@ int launch2(const UmmaParams& p_in, const CUtensorMap& ma, const CUtensorMap& mb
     // With no more tiles than clusters the fixed stride is already the best schedule; otherwise draw tiles dynamically
     // (a counter that cannot be had falls back to the fixed stride).
     p.tile_counter = nullptr;
+    // Weight-gradient tiles differ in length by the experts' row counts, so they are always drawn dynamically (longest
+    // first).  Row tiles are uniform; drawing them keeps the clusters that share a weight panel in step, which measured
+    // equal or better with long reductions (K >= 4096) and slightly worse with short ones, where the hand-over of the
+    // index is a larger part of a tile.
     const int mode = option_value(B200MOE_OPT_DYNAMIC_TILES);
-    if ((mode == 2 || (mode == 1 && p.wfam)) && tiles_bound > grid / 2) p.tile_counter = take_tile_counter(stream);
+    const bool dynamic = mode == 3 || (mode >= 1 && p.wfam) || (mode == 2 && !p.wfam && p.K >= 4096);
+    if (dynamic && tiles_bound > grid / 2) p.tile_counter = take_tile_counter(stream);
     kern<<<grid, threads_of(EPI), SMEM_BYTES2, stream>>>(p, ma, mb, mo, mo2, mo3);
     count_launch();
     return check_launch("umma2_grouped_kernel");

@@ -433,7 +433,7 @@ class MoE_B200_EP(nn.Module):
     def __init__(self, num_experts, num_experts_per_tok, hidden_size, intermediate_size, activation_function, is_glu, add_bias, std,
                  group=None, device=None, dtype=torch.float32, seed: int = 0, ops=CudaRowOps, local_experts_fn=None,
                  num_shared_experts: int = 0, shared_intermediate_size: int | None = None, router_scoring: str = "softmax",
-                 exchange: str = "nccl", exchange_rows: int | None = None, placement=None, expected_load=None):
+                 exchange: str = "nccl", exchange_rows: int | None = None, placement=None, expected_load=None, micro_batches: int = 1):
         super().__init__()
         assert is_glu, "the expert-parallel layer implements GLU experts"
         assert router_scoring in ("softmax", "sigmoid")
@@ -456,6 +456,13 @@ class MoE_B200_EP(nn.Module):
         assert exchange in ("nccl", "p2p")
         # "p2p": rows move by this package's kernels over peer memory; exchange_rows = capacity of each buffer in rows
         self.exchange = PeerExchange(self.group, exchange_rows, hidden_size, dtype, torch.device(device)) if exchange == "p2p" else None
+        # Pipelining (peer-memory exchange only): the rank's tokens are split into `micro_batches` parts, each with its own
+        # exchange buffers and stream, so that the row transfers of one part run while the expert GEMMs of another do.
+        self.micro_batches = micro_batches if exchange == "p2p" else 1
+        self._pipe = None
+        if self.micro_batches > 1:
+            rows = ((exchange_rows + self.micro_batches - 1) // self.micro_batches + 127) // 128 * 128
+            self._pipe = [(PeerExchange(self.group, rows, hidden_size, dtype, torch.device(device)), torch.cuda.Stream(device)) for _ in range(self.micro_batches)]
         # every rank draws with the same per-expert seeds on the same kind of device, so shards agree across ranks
         gen_dev = torch.device(device) if device is not None and torch.device(device).type == "cuda" else torch.device("cpu")
 
@@ -478,15 +485,16 @@ class MoE_B200_EP(nn.Module):
             self.shared_c_fc_weight = nn.Parameter(torch.stack([draw((2 * i_s, hidden_size), seed * 100003 + 7 + 2 * s_, std) for s_ in range(num_shared_experts)]).to(device))
             self.shared_c_proj_weight = nn.Parameter(torch.stack([draw((hidden_size, i_s), seed * 100003 + 8 + 2 * s_, std) for s_ in range(num_shared_experts)]).to(device))
 
-    def local_experts(self, rows: torch.Tensor, local_ids: torch.Tensor) -> torch.Tensor:
+    def local_experts(self, rows: torch.Tensor, local_ids: torch.Tensor, exchange=None) -> torch.Tensor:
         if self._local_experts_fn is not None:
             return self._local_experts_fn(rows, local_ids, self.c_fc_weight, self.c_proj_weight)
         from .scattermoe import fused_swiglu_experts
 
         ones = torch.ones(rows.size(0), 1, dtype=rows.dtype, device=rows.device)
         y_out = dx_out = None
-        if self.exchange is not None:  # the kernels write straight into the buffers the other ranks read
-            y_out, dx_out = self.exchange.bufs["y"], self.exchange.bufs["dx"]
+        exchange = exchange if exchange is not None else self.exchange
+        if exchange is not None and hasattr(exchange, "peer_ptrs"):  # the kernels write straight into the buffers the other ranks read
+            y_out, dx_out = exchange.bufs["y"], exchange.bufs["dx"]
         return fused_swiglu_experts(rows, self.c_fc_weight, self.c_proj_weight, ones, local_ids.view(-1, 1), y_out, dx_out)
 
     def forward(self, hidden_states: torch.Tensor):
@@ -521,9 +529,36 @@ class MoE_B200_EP(nn.Module):
     def _compute_experts(self, hidden_states, router_weights, selected_experts):
         if self.slot_of_expert is not None:
             selected_experts = self.slot_of_expert[selected_experts]
+        if self._pipe is not None and hidden_states.size(0) >= self.micro_batches:
+            return self._compute_experts_pipelined(hidden_states, router_weights, selected_experts)
         if self.exchange is not None:
             return ep_experts_p2p(hidden_states, router_weights, selected_experts, self.num_experts, self.local_experts, self.exchange, self.ops)
         return ep_experts(hidden_states, router_weights, selected_experts, self.num_experts, self.local_experts, self.group, self.ops)
+
+    def _compute_experts_pipelined(self, hidden_states, router_weights, selected_experts):
+        """The same pass over `micro_batches` slices of the tokens, one stream and one set of exchange buffers per slice.
+        The host queues slice after slice; on the GPU the dispatch of slice i+1 and the return of slice i-1 overlap the
+        expert GEMMs of slice i (the GEMM kernels fill the SMs, the copy kernels run beside them).  Autograd runs every
+        slice's backward on the stream of its forward, so the backward pass pipelines the same way.  Every rank must use
+        the same number of slices."""
+        main = torch.cuda.current_stream(hidden_states.device)
+        T = hidden_states.size(0)
+        bounds = [T * i // self.micro_batches for i in range(self.micro_batches + 1)]
+        outs, received = [], 0
+        global last_received_rows
+        for i, (xc, stream) in enumerate(self._pipe):
+            lo, hi = bounds[i], bounds[i + 1]
+            stream.wait_stream(main)
+            with torch.cuda.stream(stream):
+                y_i = ep_experts_p2p(hidden_states[lo:hi], router_weights[lo:hi], selected_experts[lo:hi], self.num_experts,
+                                     lambda rows, ids, xc=xc: self.local_experts(rows, ids, xc), xc, self.ops)
+            y_i.record_stream(main)
+            outs.append(y_i)
+            received += last_received_rows or 0
+        for _, stream in self._pipe:
+            main.wait_stream(stream)
+        last_received_rows = received
+        return torch.cat(outs)
 
     def allreduce_replicated_grads(self) -> None:
         """Sums the gradient of the replicated gate over the ranks (tokens are data-parallel)."""
@@ -553,3 +588,80 @@ class MoE_B200_EP(nn.Module):
         """(d_c_fc, d_c_proj) of this rank's experts together with their global expert ids (int64, e_local)."""
         lo = self.rank * self.e_local
         return self.c_fc_weight.grad, self.c_proj_weight.grad, torch.as_tensor(self.expert_of_slot[lo : lo + self.e_local])
+
+
+# --------------------------------------------------------------------------------------------------
+# multi-rank self check: the expert-parallel layer against the single-GPU layer on the union of the tokens
+# --------------------------------------------------------------------------------------------------
+
+
+def _rel_l2(a: torch.Tensor, b: torch.Tensor) -> float:
+    a, b = a.double(), b.double()
+    return float((a - b).norm() / b.norm().clamp_min(1e-30))
+
+
+def parity_selfcheck(group, device, cases=None) -> dict:
+    """Runs small layers through `MoE_B200_EP` with both exchanges (and a strided placement) on every rank of `group` and
+    compares outputs and gradients with the single-GPU layer `MoE_B200` holding the gathered weights, evaluated on the
+    all-gathered tokens.  Token counts differ per rank.  Returns {"cases": {...: {y, dx, d_w_fc, d_w_proj, d_gate}},
+    "worst": ..., "ok": bool}, identical on all ranks (the errors are max-reduced over the group).  Tolerances: relative L2
+    1e-5 for fp32 and 1e-2 for bf16 (20x that for the gate-weight gradient, which sums over every token of the job)."""
+    from . import _lib
+    from .ops import swiglu_unchunked_torch
+    from .scattermoe import MoE_B200
+
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    if cases is None:
+        cases = [("fp32_E16_k4_H256_I384", torch.float32, 16, 4, 256, 384, 800, None, 1), ("bf16_E64_k6_H512_I768", torch.bfloat16, 64, 6, 512, 768, 800, None, 1),
+                 ("bf16_E64_k6_H512_I768_strided", torch.bfloat16, 64, 6, 512, 768, 800, "strided", 1),
+                 ("bf16_E64_k6_H512_I768_pipelined3", torch.bfloat16, 64, 6, 512, 768, 800, None, 3)]
+    report, ok = {}, True
+    for name, dtype, E, k, H, I, T, placement, micro in cases:
+        if E % world:
+            continue
+        tol = 1e-5 if dtype == torch.float32 else 1e-2
+        counts = [T + 37 * r for r in range(world)]  # uneven shards
+        gen = torch.Generator().manual_seed(4242)
+        xs = [torch.randn(c, H, generator=gen) for c in counts]
+        gs = [torch.randn(c, H, generator=gen) for c in counts]
+        x_all, g_all = torch.cat(xs).to(device, dtype), torch.cat(gs).to(device, dtype)
+        lo = sum(counts[:rank])
+        for exchange in ("p2p", "nccl") if micro == 1 else ("p2p",):
+            cap = (sum(counts) * k + 127) // 128 * 128
+            layer = MoE_B200_EP(E, k, H, I, swiglu_unchunked_torch, True, False, 0.05, group=group, device=device, dtype=dtype, seed=5,
+                                exchange=exchange, exchange_rows=cap, placement=placement, micro_batches=micro)
+            ref = MoE_B200(E, k, H, I, swiglu_unchunked_torch, True, False, 0.05).to(device).to(dtype)
+            ref.load_state_dict(layer.full_state_dict())
+            x = x_all[lo : lo + counts[rank]].clone().requires_grad_(True)
+            y, _ = layer(x)
+            y.backward(g_all[lo : lo + counts[rank]])
+            layer.allreduce_replicated_grads()
+            # The reference layer sees the shards one after the other, each with the shape the owning rank's router saw,
+            # so that both sides select the same experts (a differently shaped gate GEMM may round a logit differently);
+            # its parameter gradients accumulate over the shards.
+            y_ref = dx_ref = None
+            off = 0
+            for r, c in enumerate(counts):
+                xr = x_all[off : off + c].clone().requires_grad_(True)
+                yr, _ = ref(xr)
+                yr.backward(g_all[off : off + c])
+                if r == rank:
+                    y_ref, dx_ref = yr.detach(), xr.grad
+                off += c
+            _lib.check_status(torch.device(device))
+            d_fc, d_proj, mine = layer.expert_grads_in_expert_order()
+            mine = mine.to(device)
+            errs = torch.tensor([
+                _rel_l2(y.detach(), y_ref),
+                _rel_l2(x.grad, dx_ref),
+                _rel_l2(d_fc, ref.c_fc.weight.grad[mine]),
+                _rel_l2(d_proj, ref.c_proj.weight.grad[mine]),
+                _rel_l2(layer.gate.weight.grad, ref.gate.weight.grad),
+            ], device=device, dtype=torch.float64)
+            dist.all_reduce(errs, op=dist.ReduceOp.MAX, group=group)
+            e = dict(zip(("y", "dx", "d_w_fc", "d_w_proj", "d_gate"), [float(v) for v in errs.cpu()]))
+            report[f"{name}_{exchange}"] = e
+            ok = ok and all(v < (20 * tol if n == "d_gate" else tol) for n, v in e.items()) and all(v == v for v in e.values())
+            del layer, ref
+    worst = max((v for e in report.values() for n, v in e.items() if n != "d_gate"), default=0.0)
+    return {"cases": report, "worst": worst, "ok": bool(ok), "ranks": world}

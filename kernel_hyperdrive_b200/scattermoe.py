@@ -308,14 +308,14 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
         if x.stride(1) != 1:
             x = x.contiguous()
         gates = router_weights.to(x.dtype).contiguous()
-        with torch.no_grad():
+        with torch.no_grad(), phase("route"):
             _, _, offsets, _, row_token, row_slot = route(selected_experts.reshape(-1), E, k, False, True)
         cap = row_token.numel()
         h = torch.empty(cap, I2, device=x.device, dtype=x.dtype)
         a = torch.empty(cap, I, device=x.device, dtype=x.dtype)
         # rows of x in the padded grouped order: one HBM pass, after which every operand is a plain TMA tile
         x_rows = torch.empty(cap, H, device=x.device, dtype=x.dtype)
-        _gather_rows(x, row_token, x_rows)
+        _launch("gather_x", _gather_rows, x, row_token, x_rows)
         _launch("up_forward", _up_forward, x_rows, w_fc, offsets, None, h, a, activation)
         if not KEEP_GATHERED_INPUT:
             x_rows = None
@@ -335,7 +335,7 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
             slot_row = torch.empty(M, device=x.device, dtype=torch.int32)
             _invert_row_map(row_slot, slot_row)
             y = y_out[:T] if (k == 1 and y_out is not None) else torch.empty(T, H, device=x.device, dtype=x.dtype)
-            _combine_rows(y_rows, slot_row, gates, y, k)
+            _launch("combine_y", _combine_rows, y_rows, slot_row, gates, y, k)
             if not need_gate_grad:
                 y_rows = None
         ctx.save_for_backward(x, w_fc, w_proj, gates, offsets, row_token, row_slot, h, a, x_rows, y_rows, slot_row)
@@ -359,7 +359,7 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
         # `group(grad_out, coeff=gates)`), and the gate gradient <unweighted expert output, upstream gradient>
         g_rows = torch.empty(cap, H, device=x.device, dtype=x.dtype)
         d_gates = torch.empty(M, device=x.device, dtype=torch.float32) if (need_g and y_rows is not None) else None
-        _gather_grad_rows(grad_y, row_token, row_slot, gates, y_rows if d_gates is not None else None, g_rows, d_gates, True)
+        _launch("gather_grad", _gather_grad_rows, grad_y, row_token, row_slot, gates, y_rows if d_gates is not None else None, g_rows, d_gates, True)
         del y_rows
 
         d_w_proj = d_w_fc = d_x = d_rw = None
@@ -389,7 +389,7 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
                     slot_row = torch.empty(M, device=x.device, dtype=torch.int32)
                     _invert_row_map(row_slot, slot_row)
                 d_x = torch.empty(T, H, device=x.device, dtype=x.dtype)
-                _combine_rows(dx_rows, slot_row, None, d_x, k)
+                _launch("combine_dx", _combine_rows, dx_rows, slot_row, None, d_x, k)
         if d_gates is not None:
             d_rw = d_gates.view(T, k).to(ctx.rw_dtype)
         return d_x, d_w_fc, d_w_proj, d_rw, None, None, None
