@@ -354,6 +354,15 @@ int b200moe_ep_gate_grad(const void* expanded, int64_t lde, const void* grad, in
 int b200moe_router_forward(const void* x, int64_t ldx, const void* gate_w, int64_t ldw, int64_t T, int H, int E, int k,
                            int scoring, void* logits, int64_t ldl, void* weights, int64_t* indices, int32_t* counts,
                            int dtype, int32_t* status, b200moe_stream_t stream);
+/* The same router with a per-row factor on the logits: logits[t, :] = row_scale[t] * (x[t, :] @ gate_w^T), rounded after
+ * the scaling.  With x the un-normalised hidden states, row_scale = the rstd of b200moe_rmsnorm_forward and gate_w the
+ * gate weight multiplied column-wise by the norm weight, these are the logits of the RMSNorm that feeds the layer
+ * (cute_kernels/kernels/rmsnorm/triton_implementation/kernels_forward.py:19-60 followed by
+ * cute_kernels/kernels/scattermoe/torch_implementation.py:120-122): the normalisation is folded into the gate
+ * projection instead of being read back from memory.  row_scale: device fp32 (T), NULL = 1. */
+int b200moe_router_forward_scaled(const void* x, int64_t ldx, const void* gate_w, int64_t ldw, const float* row_scale, int64_t T,
+                                  int H, int E, int k, int scoring, void* logits, int64_t ldl, void* weights, int64_t* indices,
+                                  int32_t* counts, int dtype, int32_t* status, b200moe_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
  * RMSNorm (the normalisation feeding the layer's input in a transformer block): replaces `rmsnorm_cute`

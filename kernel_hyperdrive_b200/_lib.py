@@ -130,6 +130,7 @@ def _declare(lib):
         "b200moe_ep_gate_grad": (i32, [vp, i64, vp, i64, vp, i64, i32, i32, i32, vp]),
         "b200moe_up_dgrad": (i32, [vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, i64, i32, vp, vp]),
         "b200moe_router_forward": (i32, [vp, i64, vp, i64, i64, i32, i32, i32, i32, vp, i64, vp, vp, vp, i32, vp, vp]),
+        "b200moe_router_forward_scaled": (i32, [vp, i64, vp, i64, vp, i64, i32, i32, i32, i32, vp, i64, vp, vp, vp, i32, vp, vp]),
         "b200moe_rmsnorm_workspace_bytes": (i64, [i64, i32, i32]),
         "b200moe_rmsnorm_forward": (i32, [vp, i64, vp, vp, i64, vp, i64, i32, f32, i32, vp]),
         "b200moe_rmsnorm_backward": (i32, [vp, i64, vp, vp, i64, vp, vp, i64, vp, vp, i64, i64, i32, f32, i32, vp]),

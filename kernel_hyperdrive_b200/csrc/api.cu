@@ -438,9 +438,10 @@ extern "C" int b200moe_up_dgrad(const void* dh, const void* w_fc, const int64_t*
 
 // ---- fused router ---------------------------------------------------------------------------------
 
-extern "C" int b200moe_router_forward(const void* x, int64_t ldx, const void* gate_w, int64_t ldw, int64_t T, int H, int E,
-                                      int k, int scoring, void* logits, int64_t ldl, void* weights, int64_t* indices,
-                                      int32_t* counts, int dtype, int32_t* status, b200moe_stream_t stream_) {
+extern "C" int b200moe_router_forward_scaled(const void* x, int64_t ldx, const void* gate_w, int64_t ldw, const float* row_scale,
+                                             int64_t T, int H, int E, int k, int scoring, void* logits, int64_t ldl, void* weights,
+                                             int64_t* indices, int32_t* counts, int dtype, int32_t* status,
+                                             b200moe_stream_t stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     B200MOE_REQUIRE(dtype == B200MOE_BF16 || dtype == B200MOE_F16, B200MOE_ERR_DTYPE,
                     "router_forward: 16-bit tensors only (dtype %d); route fp32 tensors with the eager router", dtype);
@@ -456,5 +457,12 @@ extern "C" int b200moe_router_forward(const void* x, int64_t ldx, const void* ga
     B200MOE_REQUIRE(H % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && ldx >= H && ldw >= H && ldl >= E &&
                         ((uintptr_t)x & 15) == 0 && ((uintptr_t)gate_w & 15) == 0,
                     B200MOE_ERR_LAYOUT, "router_forward: rows of x and of the gate weight must be 16-byte aligned multiples of 16 bytes");
-    return umma_router(x, ldx, gate_w, ldw, T, H, E, k, scoring, logits, ldl, weights, indices, counts, dtype, status, stream);
+    return umma_router(x, ldx, gate_w, ldw, T, H, E, k, scoring, row_scale, logits, ldl, weights, indices, counts, dtype, status, stream);
+}
+
+extern "C" int b200moe_router_forward(const void* x, int64_t ldx, const void* gate_w, int64_t ldw, int64_t T, int H, int E,
+                                      int k, int scoring, void* logits, int64_t ldl, void* weights, int64_t* indices,
+                                      int32_t* counts, int dtype, int32_t* status, b200moe_stream_t stream) {
+    return b200moe_router_forward_scaled(x, ldx, gate_w, ldw, nullptr, T, H, E, k, scoring, logits, ldl, weights, indices, counts, dtype,
+                                         status, stream);
 }

@@ -137,8 +137,8 @@ bool umma_w_gemm_supported(const WGemm& g, int dtype);
 int umma_row_gemm(const RowGemm& g, int dtype, int32_t* status, cudaStream_t stream);
 int umma_w_gemm(const WGemm& g, int dtype, int32_t* status, cudaStream_t stream);
 int umma_router(const void* x, int64_t ldx, const void* gate_w, int64_t ldw, int64_t T, int H, int E, int k, int scoring,
-                void* logits, int64_t ldl, void* weights, int64_t* indices, int32_t* counts, int dtype, int32_t* status,
-                cudaStream_t stream);
+                const float* row_scale, void* logits, int64_t ldl, void* weights, int64_t* indices, int32_t* counts, int dtype,
+                int32_t* status, cudaStream_t stream);
 
 // row-wise kernels used by the API layer
 int launch_swiglu_forward(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t rows, int h, int dtype,

@@ -87,7 +87,10 @@ __global__ void __launch_bounds__(kEpWarps * 32) ep_pull_combine_kernel(PeerTabl
             my_row = (const T*)peers.ptr[d] + ((int64_t)base[d] + (n - start[d])) * (int64_t)width;
             if (gates) my_gate = Elem<T>::to_f(gates[t * k + lane]);
         }
-        for (int col = lane * V; col < width; col += 32 * V) {
+        // every lane runs every sweep (the shuffles need the whole warp); a lane past the row's end only skips its accesses
+        for (int col0 = 0; col0 < width; col0 += 32 * V) {
+            const int col = col0 + lane * V;
+            const bool in = col < width;
             float acc[V];
 #pragma unroll
             for (int i = 0; i < V; ++i) acc[i] = 0.f;
@@ -95,15 +98,18 @@ __global__ void __launch_bounds__(kEpWarps * 32) ep_pull_combine_kernel(PeerTabl
             for (int j = 0; j < k; ++j) {
                 const T* row = (const T*)__shfl_sync(0xffffffffu, (unsigned long long)my_row, j);
                 const float g = __shfl_sync(0xffffffffu, my_gate, j);
+                if (!in) continue;
                 Pack<T, V> p = *reinterpret_cast<const Pack<T, V>*>(row + col);
 #pragma unroll
                 for (int i = 0; i < V; ++i) acc[i] += g * Elem<T>::to_f(p.v[i]);
                 if (expanded) *reinterpret_cast<Pack<T, V>*>(expanded + (t * k + j) * (int64_t)width + col) = p;
             }
-            Pack<T, V> o;
+            if (in) {
+                Pack<T, V> o;
 #pragma unroll
-            for (int i = 0; i < V; ++i) o.v[i] = Elem<T>::from_f(acc[i]);
-            *reinterpret_cast<Pack<T, V>*>(out + t * ldo + col) = o;
+                for (int i = 0; i < V; ++i) o.v[i] = Elem<T>::from_f(acc[i]);
+                *reinterpret_cast<Pack<T, V>*>(out + t * ldo + col) = o;
+            }
         }
     }
 }

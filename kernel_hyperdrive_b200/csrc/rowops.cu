@@ -108,7 +108,7 @@ __global__ void combine_kernel(const T* __restrict__ in, int64_t ldi, const T* _
 // out[t, :] = sum_j gates[t, j] * in[pos[t*k + j], :]: the combine pass reading rows of the padded grouped order.
 // One warp per token; lane j < k looks up row j and its gate, the k rows are then read side by side.  k <= 32.
 template <typename T, int V>
-__global__ void __launch_bounds__(kRowWarps * 32) combine_rows_kernel(const T* __restrict__ in, int64_t ldi, const int32_t* __restrict__ pos,
+__global__ void __launch_bounds__(kRowWarps * 32) combine_rows_kernel(const T* __restrict__ in_rows, int64_t ldi, const int32_t* __restrict__ pos,
                                                                      const T* __restrict__ gates, T* __restrict__ out, int64_t ldo, int64_t Tn,
                                                                      int k, int H) {
     const int lane = threadIdx.x & 31;
@@ -119,7 +119,10 @@ __global__ void __launch_bounds__(kRowWarps * 32) combine_rows_kernel(const T* _
             my_row = pos[t * k + lane];
             my_gate = gates ? Elem<T>::to_f(gates[t * k + lane]) : 1.f;
         }
-        for (int col = lane * V; col < H; col += 32 * V) {
+        // every lane runs every sweep (the shuffles need the whole warp); a lane past the row's end only skips its accesses
+        for (int col0 = 0; col0 < H; col0 += 32 * V) {
+            const int col = col0 + lane * V;
+            const bool in = col < H;
             float acc[V];
 #pragma unroll
             for (int i = 0; i < V; ++i) acc[i] = 0.f;
@@ -127,15 +130,17 @@ __global__ void __launch_bounds__(kRowWarps * 32) combine_rows_kernel(const T* _
             for (int j = 0; j < k; ++j) {
                 const int row = __shfl_sync(0xffffffffu, my_row, j);
                 const float g = __shfl_sync(0xffffffffu, my_gate, j);
-                if (row < 0) continue;
-                Pack<T, V> p = *reinterpret_cast<const Pack<T, V>*>(in + (int64_t)row * ldi + col);
+                if (row < 0 || !in) continue;
+                Pack<T, V> p = *reinterpret_cast<const Pack<T, V>*>(in_rows + (int64_t)row * ldi + col);
 #pragma unroll
                 for (int i = 0; i < V; ++i) acc[i] += g * Elem<T>::to_f(p.v[i]);
             }
-            Pack<T, V> o;
+            if (in) {
+                Pack<T, V> o;
 #pragma unroll
-            for (int i = 0; i < V; ++i) o.v[i] = Elem<T>::from_f(acc[i]);
-            *reinterpret_cast<Pack<T, V>*>(out + t * ldo + col) = o;
+                for (int i = 0; i < V; ++i) o.v[i] = Elem<T>::from_f(acc[i]);
+                *reinterpret_cast<Pack<T, V>*>(out + t * ldo + col) = o;
+            }
         }
     }
 }

@@ -56,6 +56,7 @@ struct UmmaParams {
     // router (EPI_ROUTER, one-CTA kernel): one group of `rows_fixed` rows (offsets == nullptr), N = number of experts
     int64_t rows_fixed;
     int r_k, r_scoring, r_vec;  // experts per token; 0 softmax / 1 normalised sigmoid; logits rows allow 16-byte stores
+    const float* r_rowscale;    // optional fp32 factor per row applied to the logits before rounding (RMSNorm's 1 / rms)
     int64_t* r_indices;         // (rows, k) selected experts
     int32_t* r_counts;          // (N) rows per expert, accumulated with atomics
 };
@@ -404,6 +405,7 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
                 tix[j] = 0;
             }
             uint8_t* lrow = (uint8_t*)p.out + row * p.ldo * 2;
+            const float rs = (p.r_rowscale != nullptr && row_ok) ? p.r_rowscale[row] : 1.f;
 #pragma unroll 1
             for (int c = 0; c < E; c += 32) {
                 uint32_t v[32];
@@ -411,7 +413,7 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
                 tc_wait_ld();
                 float f[32];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) f[i] = round_elem(__uint_as_float(v[i]), is_f16);
+                for (int i = 0; i < 32; ++i) f[i] = round_elem(__uint_as_float(v[i]) * rs, is_f16);
                 if (row_ok) {
                     if (p.r_vec) {
 #pragma unroll

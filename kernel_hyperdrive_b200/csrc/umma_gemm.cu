@@ -664,8 +664,8 @@ int umma_row_gemm(const RowGemm& g, int dtype, int32_t* status, cudaStream_t str
 // Fused router: logits = x @ gate_wT on the tensor cores (one group of T rows, the experts are the tile's columns),
 // top-k, scores and the per-expert counts in the epilogue.
 int umma_router(const void* x, int64_t ldx, const void* gate_w, int64_t ldw, int64_t T, int H, int E, int k, int scoring,
-                void* logits, int64_t ldl, void* weights, int64_t* indices, int32_t* counts, int dtype, int32_t* status,
-                cudaStream_t stream) {
+                const float* row_scale, void* logits, int64_t ldl, void* weights, int64_t* indices, int32_t* counts, int dtype,
+                int32_t* status, cudaStream_t stream) {
     UmmaParams p{};
     p.wfam = 0;
     p.E = 1;
@@ -686,6 +686,7 @@ int umma_router(const void* x, int64_t ldx, const void* gate_w, int64_t ldw, int
     p.out2 = weights;
     p.r_indices = indices;
     p.r_counts = counts;
+    p.r_rowscale = row_scale;
     p.r_k = k;
     p.r_scoring = scoring;
     p.r_vec = E % 8 == 0 && ldl % 8 == 0 && aligned16(logits);

@@ -546,7 +546,7 @@ class MoE_B200(MoE_Torch):
     fused_router = False
 
     def _compute_routing_weights(self, hidden_states: torch.Tensor):
-        if self.fused_router and self.gate.weight.dtype == hidden_states.dtype and fused_router_supported(hidden_states, self.num_experts, self.top_k):
+        if self.fused_router and fused_router_supported(hidden_states, self.num_experts, self.top_k, self.gate.weight):
             logits, weights, selected_experts, _ = fused_router(hidden_states, self.gate.weight, self.top_k, self.router_scoring)
             return logits, weights, selected_experts
         return super()._compute_routing_weights(hidden_states)

@@ -156,3 +156,67 @@ def test_layer_with_fused_router():
     y.float().pow(2).sum().backward()
     assert moe.gate.weight.grad is not None and moe.gate.weight.grad.abs().sum().item() > 0
     assert xg.grad is not None and torch.isfinite(xg.grad).all()
+
+
+def test_router_backward_with_few_experts_runs_on_the_grouped_gemm_operators():
+    """Eight experts: the logit gradient is an (T, 8) operand, a reduction extent far below one k step of the tensor-core
+    kernels (the rest of the step reads as zeros)."""
+    T, H, E, k = 1111, 4096, 8, 2
+    x, w = make(T, H, E, torch.bfloat16, seed=33, std=0.05)
+    x.requires_grad_(True)
+    w.requires_grad_(True)
+    gb = (torch.randn(T, E, device="cuda") * 0.1).to(torch.bfloat16)
+    before = _lib.lib().b200moe_launch_count()
+    logits, _, _, _ = fused_router(x, w, k, "softmax")
+    (logits * gb).sum().backward()
+    assert _lib.lib().b200moe_launch_count() - before >= 3  # router, input-gradient GEMM, weight-gradient GEMM (+ index kernels)
+    _lib.check_status(x.device)
+    assert rel_l2(x.grad, gb.float() @ w.detach().float()) <= 1e-2
+    assert rel_l2(w.grad, gb.float().t() @ x.detach().float()) <= 1e-2
+
+
+def test_unsupported_layouts_take_the_eager_router():
+    from kernel_hyperdrive_b200.router import fused_router_supported
+
+    x, w = make(64, 512, 8, torch.bfloat16, seed=2)
+    assert fused_router_supported(x, 8, 2, w)
+    wide = torch.zeros(64, 520, device="cuda", dtype=torch.bfloat16)
+    assert not fused_router_supported(wide[:, 4:516], 8, 2, w)  # rows start 8 bytes off a 16-byte boundary
+    assert not fused_router_supported(x, 8, 2, w.float())
+    assert not fused_router_supported(x.t().contiguous().t(), 8, 2, w)  # inner stride is not 1
+    moe = kh.MoE_B200(8, 2, 512, 256, kh.swiglu_unchunked_torch, True, False, 0.05).cuda().to(torch.bfloat16)
+    moe.fused_router = True
+    y, _ = moe(wide[:, 4:516].unsqueeze(0).contiguous())  # contiguous copy: supported again
+    assert torch.isfinite(y).all()
+
+
+@pytest.mark.parametrize("T,H,E,k", [(900, 2048, 64, 6), (257, 4096, 8, 2)])
+def test_rmsnorm_fused_with_the_gate_projection(T, H, E, k):
+    """RMSNorm feeding the layer with its normalisation folded into the router GEMM (per-row factor in the epilogue,
+    norm weight folded into the gate weight): against the eager sequence rms_norm -> linear -> top-k -> softmax."""
+    from kernel_hyperdrive_b200.router import fused_rmsnorm_router
+
+    dt, eps = torch.bfloat16, 1e-5
+    x, w = make(T, H, E, dt, seed=T, std=0.05)
+    x = (x * 3).requires_grad_(True)
+    w.requires_grad_(True)
+    nw = (1 + 0.1 * torch.randn(H, device="cuda")).to(dt).requires_grad_(True)
+    gy = torch.randn(T, H, device="cuda").to(dt)
+    gl = (torch.randn(T, E, device="cuda") * 0.1).to(dt)
+    before = _lib.lib().b200moe_launch_count()
+    y, logits, weights, idx, counts = fused_rmsnorm_router(x, nw, w, eps, k)
+    assert _lib.lib().b200moe_launch_count() - before == 2  # the norm kernel and the router kernel
+    ((y * gy).sum() + (logits * gl).sum()).backward()
+    _lib.check_status(x.device)
+    got = (y.detach(), logits.detach(), x.grad.clone(), w.grad.clone(), nw.grad.clone())
+    # eager, fp32
+    xf, wf, nf = (t.detach().float().requires_grad_(True) for t in (x, w, nw))
+    yf = torch.nn.functional.rms_norm(xf, (H,), nf, eps)
+    lf = yf @ wf.t()
+    ((yf * gy.float()).sum() + (lf * gl.float()).sum()).backward()
+    for name, a, b in zip(("y", "logits", "dx", "d_gate", "d_norm"), got, (yf, lf, xf.grad, wf.grad, nf.grad)):
+        assert rel_l2(a, b) <= 1e-2, (name, rel_l2(a, b))
+    # selection: stable top-k of the stored logits, histogram of the selection, weights from the selected logits
+    assert torch.equal(torch.sort(logits.float(), dim=-1, descending=True, stable=True).indices[:, :k], idx)
+    assert torch.equal(counts.long(), torch.bincount(idx.flatten(), minlength=E))
+    assert rel_l2(weights, eager_scores(logits.gather(1, idx), "softmax", dt)) <= 1e-2
