@@ -240,6 +240,11 @@ int b200moe_gather_rows(const void* src, int64_t lds, const int32_t* row_map, vo
  * the activation of the reference's MoE test, tests/test_commons.py:86-87). */
 #define B200MOE_ACT_SWIGLU 0
 #define B200MOE_ACT_GLU 1
+/* Un-gated activation of a non-GLU expert layer: a = gelu_tanh(h), h = x @ w_fc^T with w_fc (E, I, H) (torch.nn.GELU(
+ * approximate="tanh"), the activation of the reference's non-GLU MoE test, tests/test_commons.py:86-87).  With this code
+ * every "2I" below reads "I": h and dh are (Mcap, I), and b200moe_up_dgrad is called with I / 2 in place of I so that
+ * its reduction extent 2 * (I / 2) is the layer's I. */
+#define B200MOE_ACT_GELU_TANH 2
 
 /* Up projection with the token gather on the input rows and the gated activation in the epilogue:
  * h[p, :] = x[row_token[p], :] @ w_fc[e(p)]^T  (Mcap, 2I), a[p, :] = h[p, :I] * m(h[p, I:])  (Mcap, I).

@@ -1,7 +1,7 @@
 """B200-native (sm_100a) implementation of the scattermoe MoE layer path."""
 
 from .custom_op import set_cute_tracing
-from .ops import combine, contiguous_count_cute, group, group_bwd_W, rmsnorm_cute, rmsnorm_torch, scatter2scatter, swiglu_unchunked_cute, swiglu_unchunked_torch
+from .ops import combine, contiguous_count_cute, gate_grad, group, group_bwd_W, rmsnorm_cute, rmsnorm_torch, scatter2scatter, swiglu_unchunked_cute, swiglu_unchunked_torch
 from .scattermoe import (
     Experts_B200,
     Experts_Torch,
@@ -14,4 +14,4 @@ from .scattermoe import (
     scattered_experts,
 )
 from .inject import GraphInjector, adopt_moe, replace_swiglu_unchunked, swap_moe_modules
-from .router import fused_router, router_forward
+from .router import fused_rmsnorm_router, fused_router, router_forward

@@ -275,28 +275,31 @@ extern "C" int b200moe_up_forward(const void* x, int64_t ldx, const void* w_fc, 
                                   int64_t m_cap, int activation, int dtype, int32_t* status, b200moe_stream_t stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     REQUIRE_COMMON("up_forward");
-    B200MOE_REQUIRE(activation == B200MOE_ACT_SWIGLU || activation == B200MOE_ACT_GLU, B200MOE_ERR_ARG, "up_forward: activation %d", activation);
+    B200MOE_REQUIRE(activation == B200MOE_ACT_SWIGLU || activation == B200MOE_ACT_GLU || activation == B200MOE_ACT_GELU_TANH, B200MOE_ERR_ARG,
+                    "up_forward: activation %d", activation);
     if (m_cap == 0) return B200MOE_OK;
     B200MOE_REQUIRE(x && w_fc && expert_offsets && h && a && T >= 0, B200MOE_ERR_ARG, "up_forward: NULL pointer");
+    const bool gated = activation != B200MOE_ACT_GELU_TANH;
+    const int F = gated ? 2 * I : I;  // output features of the up projection
     RowGemm g{};
     g.A = x;
     g.lda = ldx;
     g.a_map = row_token;
     g.a_rows = row_token ? T : m_cap;
-    g.W = w_fc;  // (E, 2I, H): element (e, kk, n) at e*2I*H + n*H + kk
-    g.w_se = (int64_t)2 * I * H;
+    g.W = w_fc;  // (E, F, H): element (e, kk, n) at e*F*H + n*H + kk
+    g.w_se = (int64_t)F * H;
     g.w_sk = 1;
     g.w_sn = H;
     g.out = h;
-    g.ldo = 2 * (int64_t)I;
+    g.ldo = F;
     g.o_map = nullptr;
     g.offsets = expert_offsets;
     g.padded = 1;
     g.rows_cap = m_cap;
     g.K = H;
-    g.N = 2 * I;
+    g.N = F;
     g.E = E;
-    g.epi = EPI_SWIGLU;
+    g.epi = gated ? EPI_SWIGLU : EPI_UNARY;
     g.act = activation;
     g.out2 = a;
     int eng = pick_engine(g, dtype, umma_row_gemm_supported, "up_forward");
@@ -305,6 +308,7 @@ extern "C" int b200moe_up_forward(const void* x, int64_t ldx, const void* w_fc, 
     g.epi = EPI_STORE;
     int rc = simt_row_gemm(g, dtype, stream);
     if (rc) return rc;
+    if (!gated) return launch_unary_forward(h, I, a, I, m_cap, I, dtype, stream);
     return launch_swiglu_forward(h, 2 * (int64_t)I, a, I, m_cap, I, dtype, stream, activation);
 }
 
@@ -345,9 +349,11 @@ extern "C" int b200moe_down_dgrad(const void* grad_rows, int64_t ldg, const void
                                   int64_t m_cap, int activation, int dtype, int32_t* status, b200moe_stream_t stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     REQUIRE_COMMON("down_dgrad");
-    B200MOE_REQUIRE(activation == B200MOE_ACT_SWIGLU || activation == B200MOE_ACT_GLU, B200MOE_ERR_ARG, "down_dgrad: activation %d", activation);
+    B200MOE_REQUIRE(activation == B200MOE_ACT_SWIGLU || activation == B200MOE_ACT_GLU || activation == B200MOE_ACT_GELU_TANH, B200MOE_ERR_ARG,
+                    "down_dgrad: activation %d", activation);
     if (m_cap == 0) return B200MOE_OK;
     B200MOE_REQUIRE(grad_rows && w_proj && expert_offsets && h && dh && T >= 0, B200MOE_ERR_ARG, "down_dgrad: NULL pointer");
+    const bool gated = activation != B200MOE_ACT_GELU_TANH;
     RowGemm g{};
     g.A = grad_rows;
     g.lda = ldg;
@@ -358,7 +364,7 @@ extern "C" int b200moe_down_dgrad(const void* grad_rows, int64_t ldg, const void
     g.w_sk = I;
     g.w_sn = 1;
     g.out = dh;
-    g.ldo = 2 * (int64_t)I;
+    g.ldo = gated ? 2 * (int64_t)I : I;
     g.o_map = nullptr;
     g.offsets = expert_offsets;
     g.padded = 1;
@@ -366,16 +372,17 @@ extern "C" int b200moe_down_dgrad(const void* grad_rows, int64_t ldg, const void
     g.K = H;
     g.N = I;
     g.E = E;
-    g.epi = EPI_DGRAD_DOWN;
+    g.epi = gated ? EPI_DGRAD_DOWN : EPI_DGRAD_UNARY;
     g.act = activation;
     g.h = h;
     int eng = pick_engine(g, dtype, umma_row_gemm_supported, "down_dgrad");
     if (eng < 0) return eng;
     if (eng) return umma_row_gemm(g, dtype, status, stream);
-    // CUDA-core engine: d into the first half of every dh row, then the element-wise tail in place
+    // CUDA-core engine: d into (the first half of) every dh row, then the element-wise tail in place
     g.epi = EPI_STORE;
     int rc = simt_row_gemm(g, dtype, stream);
     if (rc) return rc;
+    if (!gated) return launch_unary_backward(h, I, dh, I, m_cap, I, dtype, stream);
     return launch_dgrad_down_post(h, dh, m_cap, I, dtype, stream, activation);
 }
 

@@ -99,7 +99,7 @@ struct RowGemm {
     int64_t rows_cap;  // upper bound of layout rows (grid sizing)
     int K, N, E;
     // fused epilogues (tcgen05 engine only)
-    int epi;               // 0 store, 1 SwiGLU forward, 2 down-projection dgrad
+    int epi;               // EPI_STORE, EPI_SWIGLU (gated forward), EPI_DGRAD_DOWN (gated dgrad), EPI_UNARY, EPI_DGRAD_UNARY
     int act;               // gated activation of epilogues 1 and 2 (ACT_SILU, ACT_SIGMOID)
     void* out2;            // SwiGLU: activation output a (rows_cap, N/2)
     const void* h;         // dgrad: pre-activation (rows_cap, 2N) as the SwiGLU epilogue of the same engine stored it
@@ -122,9 +122,20 @@ struct WGemm {
     int Mout, Nout, E;
 };
 
+// Un-gated activation of a plain (non-GLU) expert: a = f(h).  UNARY_GELU_TANH: the tanh form of GELU
+// (torch.nn.GELU(approximate="tanh"), the activation of the reference's non-GLU layer test).  `th` is
+// tanh(sqrt(2/pi) * (x + 0.044715 x^3)), supplied by the caller (hardware approximation for 16-bit tensors, tanhf for fp32).
+enum { UNARY_GELU_TANH = 2 };
+__device__ __forceinline__ float gelu_tanh_arg(float x) { return 0.7978845608028654f * (x + 0.044715f * x * x * x); }
+__device__ __forceinline__ float gelu_tanh_value(float x, float th) { return 0.5f * x * (1.f + th); }
+__device__ __forceinline__ float gelu_tanh_slope(float x, float th) {
+    return 0.5f * (1.f + th) + 0.5f * x * (1.f - th * th) * 0.7978845608028654f * (1.f + 0.134145f * x * x);
+}
+
 // Epilogues of the tensor-core kernels (template arguments).  The two gated-activation epilogues exist once per gate
 // function so that the choice costs nothing at run time; RowGemm names them as (EPI_SWIGLU or EPI_DGRAD_DOWN, act).
-enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_DGRAD_DOWN = 2, EPI_ROUTER = 3, EPI_GLU = 4, EPI_DGRAD_DOWN_GLU = 5 };
+// EPI_UNARY / EPI_DGRAD_UNARY are the forward / input-gradient epilogues of a non-GLU expert (a = gelu_tanh(h)).
+enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_DGRAD_DOWN = 2, EPI_ROUTER = 3, EPI_GLU = 4, EPI_DGRAD_DOWN_GLU = 5, EPI_UNARY = 6, EPI_DGRAD_UNARY = 7 };
 __host__ __device__ constexpr bool epi_gated_forward(int epi) { return epi == EPI_SWIGLU || epi == EPI_GLU; }
 __host__ __device__ constexpr bool epi_gated_dgrad(int epi) { return epi == EPI_DGRAD_DOWN || epi == EPI_DGRAD_DOWN_GLU; }
 __host__ __device__ constexpr int epi_act(int epi) { return (epi == EPI_GLU || epi == EPI_DGRAD_DOWN_GLU) ? 1 : 0; }
@@ -146,6 +157,9 @@ int launch_swiglu_forward(const void* x, int64_t ldx, void* y, int64_t ldy, int6
 int launch_swiglu_backward(const void* x, int64_t ldx, const void* dy, int64_t lddy, void* dx, int64_t lddx,
                            int64_t rows, int h, int dtype, cudaStream_t stream);
 int launch_dgrad_down_post(const void* h, void* dh, int64_t rows, int I, int dtype, cudaStream_t stream, int act = ACT_SILU);
+// a = gelu_tanh(h) on (rows, width) tensors, and dh = d * gelu_tanh'(h) in place on dh (which holds d on entry)
+int launch_unary_forward(const void* h, int64_t ldh, void* a, int64_t lda, int64_t rows, int width, int dtype, cudaStream_t stream);
+int launch_unary_backward(const void* h, int64_t ldh, void* dh, int64_t ldd, int64_t rows, int width, int dtype, cudaStream_t stream);
 
 int current_engine();
 int option_value(int option);

@@ -273,6 +273,41 @@ __global__ void __launch_bounds__(kRowWarps * 32) gather_grad_rows_kernel(const 
     }
 }
 
+// ---- un-gated activation (CUDA-core engine of a non-GLU expert) -------------------------------------
+template <typename T>
+__device__ __forceinline__ float tanh_for(float x) {
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x));
+    return t;
+}
+template <>
+__device__ __forceinline__ float tanh_for<float>(float x) {
+    return tanhf(x);
+}
+
+template <typename T>
+__global__ void unary_fwd_kernel(const T* __restrict__ h, int64_t ldh, T* __restrict__ a, int64_t lda, int64_t rows, int width) {
+    const int64_t total = rows * width;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / width;
+        const int c = (int)(i - r * width);
+        const float x = Elem<T>::to_f(h[r * ldh + c]);
+        a[r * lda + c] = Elem<T>::from_f(gelu_tanh_value(x, tanh_for<T>(gelu_tanh_arg(x))));
+    }
+}
+
+template <typename T>
+__global__ void unary_bwd_kernel(const T* __restrict__ h, int64_t ldh, T* __restrict__ dh, int64_t ldd, int64_t rows, int width) {
+    const int64_t total = rows * width;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / width;
+        const int c = (int)(i - r * width);
+        const float x = Elem<T>::to_f(h[r * ldh + c]);
+        const float d = Elem<T>::to_f(dh[r * ldd + c]);
+        dh[r * ldd + c] = Elem<T>::from_f(d * gelu_tanh_slope(x, tanh_for<T>(gelu_tanh_arg(x))));
+    }
+}
+
 template <typename F>
 int dispatch_dtype(int dtype, F&& f) {
     switch (dtype) {
@@ -339,6 +374,28 @@ int launch_dgrad_down_post(const void* h, void* dh, int64_t rows, int I, int dty
         dgrad_down_post_kernel<T><<<(unsigned)rows, 256, 0, stream>>>((const T*)h, (T*)dh, rows, I, act);
         count_launch();
         return check_launch("dgrad_down_post");
+    });
+}
+
+int launch_unary_forward(const void* h, int64_t ldh, void* a, int64_t lda, int64_t rows, int width, int dtype, cudaStream_t stream) {
+    if (rows == 0 || width == 0) return B200MOE_OK;
+    return dispatch_dtype(dtype, [&](auto tag) {
+        using T = decltype(tag);
+        int64_t blocks = (rows * width + 255) / 256;
+        unary_fwd_kernel<T><<<(unsigned)(blocks < 148 * 32 ? blocks : 148 * 32), 256, 0, stream>>>((const T*)h, ldh, (T*)a, lda, rows, width);
+        count_launch();
+        return check_launch("unary_forward");
+    });
+}
+
+int launch_unary_backward(const void* h, int64_t ldh, void* dh, int64_t ldd, int64_t rows, int width, int dtype, cudaStream_t stream) {
+    if (rows == 0 || width == 0) return B200MOE_OK;
+    return dispatch_dtype(dtype, [&](auto tag) {
+        using T = decltype(tag);
+        int64_t blocks = (rows * width + 255) / 256;
+        unary_bwd_kernel<T><<<(unsigned)(blocks < 148 * 32 ? blocks : 148 * 32), 256, 0, stream>>>((const T*)h, ldh, (T*)dh, ldd, rows, width);
+        count_launch();
+        return check_launch("unary_backward");
     });
 }
 

@@ -39,7 +39,7 @@ constexpr int B_HALF_BYTES = (BN / 2) * BK * 2;  // 16 KB
 // epilogues (latency-bound work: about a quarter of an instruction per cycle and scheduler with eight warps; exposed when
 // the reduction loop of a tile is short), eight (two per lane quarter, 128 columns each) for the SwiGLU forward epilogue,
 // whose register count does not fit twelve.
-__host__ __device__ constexpr int epi_warps_of(int epi) { return (epi_gated_dgrad(epi) || epi == EPI_STORE) ? 12 : 8; }
+__host__ __device__ constexpr int epi_warps_of(int epi) { return epi_gated_forward(epi) ? 8 : 12; }
 __host__ __device__ constexpr int threads_of(int epi) { return (2 + epi_warps_of(epi)) * 32; }  // + TMA warp, MMA warp
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -679,6 +679,10 @@ int launch_2cta(int epi, const UmmaParams& p, const CUtensorMap& ma, const CUten
             return launch2<EPI_GLU>(p, ma, mb, mo, mo2, mo3, tiles_bound, stream);
         case EPI_DGRAD_DOWN_GLU:
             return launch2<EPI_DGRAD_DOWN_GLU>(p, ma, mb, mo, mo2, mo3, tiles_bound, stream);
+        case EPI_UNARY:
+            return launch2<EPI_UNARY>(p, ma, mb, mo, mo2, mo3, tiles_bound, stream);
+        case EPI_DGRAD_UNARY:
+            return launch2<EPI_DGRAD_UNARY>(p, ma, mb, mo, mo2, mo3, tiles_bound, stream);
         default:
             set_error_detail("unknown epilogue %d", epi);
             return B200MOE_ERR_ARG;

@@ -157,6 +157,12 @@ __device__ __forceinline__ float sigmoid_tanh(float x) {
     return fmaf(0.5f, t, 0.5f);
 }
 
+__device__ __forceinline__ float tanh_fast(float x) {
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x));
+    return t;
+}
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
@@ -481,6 +487,54 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
                     if (key >= 0 && lane == (__ffs(same) - 1)) atomicAdd(p.r_counts + key, __popc(same));
                 }
             }
+        }
+    } else if (EPI == EPI_UNARY) {
+        // Non-GLU expert, forward: the tile holds 256 columns of h = x @ w_fc^T.  h is rounded to the tensor type (the
+        // reference materialises it) and stored for the backward pass, a = gelu_tanh(h) is stored for the down projection.
+        const int n0 = ti.nb * BN;
+        const int row_c = ti.row0 + q * 32;
+#pragma unroll 1
+        for (int c = c_begin; c < c_end; c += 32) {
+            if (n0 + c >= p.N) break;
+            uint32_t v[32], hv[16], av[16];
+            tc_ld32(taddr + c, v);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                hv[i] = pack2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]), is_f16);
+                const float2 f = unpack2(hv[i], is_f16);
+                av[i] = pack2(gelu_tanh_value(f.x, tanh_fast(gelu_tanh_arg(f.x))), gelu_tanh_value(f.y, tanh_fast(gelu_tanh_arg(f.y))), is_f16);
+            }
+            stage_store(mo, n0 + c, row_c, 0, hv);
+            stage_store(mo2, n0 + c, row_c, 0, av);
+        }
+    } else if (EPI == EPI_DGRAD_UNARY) {
+        // Non-GLU expert, input gradient of the down projection: dh = d * gelu_tanh'(h), d = the accumulator rounded to
+        // the tensor type, h (rows, N) as the forward stored it.
+        const int n0 = ti.nb * BN;
+        const int row_c = ti.row0 + q * 32;
+        const uint8_t* hrow = (const uint8_t*)p.h + ((int64_t)(ti.row0 + r) * p.N + n0) * 2;
+#pragma unroll 1
+        for (int c = c_begin; c < c_end; c += 32) {
+            if (n0 + c >= p.N) break;
+            uint4 h4[4];
+#pragma unroll
+            for (int qd = 0; qd < 4; ++qd)
+                h4[qd] = (n0 + c + qd * 8 < p.N) ? *reinterpret_cast<const uint4*>(hrow + (c + qd * 8) * 2) : make_uint4(0, 0, 0, 0);
+            uint32_t u[32], dv[16];
+            tc_ld32(taddr + c, u);
+            tc_wait_ld();
+#pragma unroll
+            for (int qd = 0; qd < 4; ++qd) {
+                const uint32_t ha[4] = {h4[qd].x, h4[qd].y, h4[qd].z, h4[qd].w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 hh = unpack2(ha[i], is_f16);
+                    const float2 d = unpack2(pack2(__uint_as_float(u[qd * 8 + 2 * i]), __uint_as_float(u[qd * 8 + 2 * i + 1]), is_f16), is_f16);
+                    dv[qd * 4 + i] = pack2(d.x * gelu_tanh_slope(hh.x, tanh_fast(gelu_tanh_arg(hh.x))), d.y * gelu_tanh_slope(hh.y, tanh_fast(gelu_tanh_arg(hh.y))), is_f16);
+                }
+            }
+            stage_store(mo, n0 + c, row_c, 0, dv);
         }
     } else {  // EPI_DGRAD_DOWN, EPI_DGRAD_DOWN_GLU
         // The accumulator holds d[p, :] = (gate-scaled upstream gradient rows) @ w_proj[e]: the gradient with respect to

@@ -122,7 +122,9 @@ bool use_pair_kernels(const UmmaParams& p, int epi, int64_t rows_cap) {
     if (forced == B200MOE_TILE_PAIR_256x256) return true;
     if (forced == B200MOE_TILE_CTA_128x256) return false;
     const int64_t rows_per_expert = p.E > 0 ? rows_cap / p.E : rows_cap;
-    const int op = p.wfam ? B200MOE_OP_WGRAD : (epi_gated_forward(epi) ? B200MOE_OP_UP_FORWARD : (epi_gated_dgrad(epi) ? B200MOE_OP_DOWN_DGRAD : B200MOE_OP_ROW_STORE));
+    const int op = p.wfam ? B200MOE_OP_WGRAD
+                          : ((epi_gated_forward(epi) || epi == EPI_UNARY) ? B200MOE_OP_UP_FORWARD
+                                                                          : ((epi_gated_dgrad(epi) || epi == EPI_DGRAD_UNARY) ? B200MOE_OP_DOWN_DGRAD : B200MOE_OP_ROW_STORE));
     return tile_table_lookup(op, p.wfam ? p.Mout : p.K, p.N, rows_per_expert) == B200MOE_TILE_PAIR_256x256;
 }
 
@@ -559,6 +561,8 @@ bool umma_row_gemm_supported(const RowGemm& g, int dtype) {
     }
     if (g.epi == EPI_SWIGLU && (g.w_sk != 1 || (g.N / 2) % 8 || !aligned16(g.out2))) return false;
     if (g.epi == EPI_DGRAD_DOWN && !aligned16(g.h)) return false;
+    if (g.epi == EPI_UNARY && !aligned16(g.out2)) return false;
+    if (g.epi == EPI_DGRAD_UNARY && !aligned16(g.h)) return false;
     return true;
 }
 
@@ -645,6 +649,17 @@ int umma_row_gemm(const RowGemm& g, int dtype, int32_t* status, cudaStream_t str
     }
     p.N = g.N;
     p.nb_count = (g.N + BN - 1) / BN;
+    if (g.epi == EPI_UNARY || g.epi == EPI_DGRAD_UNARY) {
+        B200MOE_REQUIRE(g.padded && g.o_map == nullptr, B200MOE_ERR_ARG, "activation epilogue needs the padded grouped order");
+        rc = make_store_map(&mo, g.out, 0, g.rows_cap, g.N, g.ldo, 0, p.is_f16);
+        if (rc) return rc;
+        if (g.epi == EPI_UNARY) {
+            rc = make_store_map(&mo2, g.out2, 0, g.rows_cap, g.N, g.N, 0, p.is_f16);
+            if (rc) return rc;
+            return launch_any<EPI_UNARY>(p, ma, mb, mo, mo2, mo3, g.rows_cap, stream);
+        }
+        return launch_any<EPI_DGRAD_UNARY>(p, ma, mb, mo, mo2, mo3, g.rows_cap, stream);
+    }
     if (g.epi == EPI_DGRAD_DOWN) {
         B200MOE_REQUIRE(g.padded && g.o_map == nullptr, B200MOE_ERR_ARG, "dgrad epilogue needs the padded grouped order");
         rc = make_store_map(&mo, g.out, 0, g.rows_cap, g.N, 2 * (int64_t)g.N, 0, p.is_f16);

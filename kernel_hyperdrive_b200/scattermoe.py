@@ -7,7 +7,8 @@ kernels; the former name is kept as an alias), `Experts_Torch`, `Experts_Triton`
 cute_kernels/kernels/scattermoe/triton_implementation/__init__.py:11-101, ops.py:133-301).
 
 Two execution paths exist in `MoE_B200._compute_experts`:
-  * fused: taken when the layer is a GLU layer whose activation is SwiGLU on the fused tensor or `nn.GLU()`.  One
+  * fused: taken when the layer is a GLU layer whose activation is SwiGLU on the fused tensor or `nn.GLU()`, or a plain
+    layer whose activation is `nn.GELU(approximate="tanh")` (the two activations of the reference's layer test).  One
     routing call, then up-projection + SwiGLU, down-projection + gate scaling, slot sum; the backward
     runs five kernels.  Intermediates live in the padded grouped order.
   * generic: any other activation callable.  The same sequence of operators as the reference
@@ -213,9 +214,10 @@ def _gather_rows(src: torch.Tensor, row_map: torch.Tensor, out: torch.Tensor) ->
 
 @b200_op("up_forward", mutates_args={"h", "a"})
 def _up_forward(x: torch.Tensor, w_fc: torch.Tensor, expert_offsets: torch.Tensor, row_token: torch.Tensor | None, h: torch.Tensor, a: torch.Tensor, activation: int = 0) -> None:
-    E, I2, H = w_fc.shape
+    E, F_, H = w_fc.shape
+    I = F_ if activation == ACTIVATIONS["gelu_tanh"] else F_ // 2
     check(
-        lib().b200moe_up_forward(ptr(x), x.stride(0), ptr(w_fc), ptr(expert_offsets), ptr(row_token), ptr(h), ptr(a), x.size(0), H, I2 // 2, E, h.size(0), activation, dtype_code(x), ptr(status_word(x.device)), stream_ptr(x.device)),
+        lib().b200moe_up_forward(ptr(x), x.stride(0), ptr(w_fc), ptr(expert_offsets), ptr(row_token), ptr(h), ptr(a), x.size(0), H, I, E, h.size(0), activation, dtype_code(x), ptr(status_word(x.device)), stream_ptr(x.device)),
         "up_forward",
     )
 
@@ -299,8 +301,8 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
         # does not see them as inputs.
         y_out, dx_out = out_bufs if out_bufs is not None else (None, None)
         T, H = x.shape
-        E, I2, _ = w_fc.shape
-        I = I2 // 2
+        E, I2, _ = w_fc.shape  # I2: output features of the up projection (2I for a gated layer, I otherwise)
+        I = I2 if activation == ACTIVATIONS["gelu_tanh"] else I2 // 2
         k = selected_experts.size(1)
         M = T * k
         assert w_fc.is_contiguous() and w_proj.is_contiguous(), "expert weights must be stored contiguously as (E, out, in)"
@@ -395,11 +397,14 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
         return d_x, d_w_fc, d_w_proj, d_rw, None, None, None
 
 
-ACTIVATIONS = {"swiglu": 0, "glu": 1}  # a = h[:, :I] * silu(h[:, I:]) / h[:, :I] * sigmoid(h[:, I:])
+# a = h[:, :I] * silu(h[:, I:]) / h[:, :I] * sigmoid(h[:, I:]) for gated layers (w_fc (E, 2I, H)); a = gelu_tanh(h) for a plain
+# layer (w_fc (E, I, H))
+ACTIVATIONS = {"swiglu": 0, "glu": 1, "gelu_tanh": 2}
 
 
 def fused_swiglu_experts(x, w_fc, w_proj, router_weights, selected_experts, y_out=None, dx_out=None, activation: str = "swiglu"):
-    """Routed GLU experts on the fused kernels; `activation` selects the gate function (`ACTIVATIONS`)."""
+    """Routed experts on the fused kernels; `activation` (`ACTIVATIONS`) selects the gate function of a GLU layer or the
+    un-gated tanh-GELU of a plain one."""
     if x.size(0) == 0:
         # no tokens: nothing to launch; the zero-weighted sums keep every input in the graph with a zero gradient
         return x.new_zeros(0, x.size(1)) + 0 * (x.sum() + w_fc.sum() + w_proj.sum() + router_weights.sum())
@@ -525,8 +530,11 @@ def is_swiglu_callable(fn) -> bool:
     return getattr(fn, "__name__", "") in ("swiglu_unchunked_torch", "swiglu_unchunked_cute")
 
 
-def fused_activation(fn) -> str | None:
-    """Name of the fused gate function an activation callable maps to, or None (the layer then runs it un-fused)."""
+def fused_activation(fn, is_glu: bool = True) -> str | None:
+    """Name of the fused activation an activation callable maps to, or None (the layer then runs it un-fused).  GLU
+    layers: SwiGLU on the fused tensor, `nn.GLU()`.  Plain layers: `nn.GELU(approximate="tanh")`."""
+    if not is_glu:
+        return "gelu_tanh" if isinstance(fn, nn.GELU) and fn.approximate == "tanh" else None
     if is_swiglu_callable(fn):
         return "swiglu"
     if isinstance(fn, nn.GLU) and fn.dim in (-1, 1):  # the layer applies it to 2-D (rows, 2I) tensors
@@ -552,7 +560,9 @@ class MoE_B200(MoE_Torch):
         return super()._compute_routing_weights(hidden_states)
 
     def _compute_experts(self, hidden_states: torch.Tensor, router_weights: torch.Tensor, selected_experts: torch.Tensor) -> torch.Tensor:
-        fused = fused_activation(self.act) if self.is_glu else None
+        fused = fused_activation(self.act, self.is_glu)
+        if fused == "gelu_tanh" and self.intermediate_size % 2:
+            fused = None
         if fused is not None:
             return fused_swiglu_experts(hidden_states, self.c_fc.weight, self.c_proj.weight, router_weights, selected_experts, activation=fused)
         with torch.no_grad():

@@ -153,6 +153,49 @@ def test_generic_path_matches_eager_module(dtype, act_name, is_glu):
         assert rel_l2(a, b) < (tol if what != "d_gate" else 20 * tol), (what, rel_l2(a, b))
 
 
+@pytest.mark.parametrize("name", ["tiny", "c2_small", "c4_small", "odd"])
+@pytest.mark.parametrize("engine,dtype", [("simt", torch.float32), ("umma", torch.bfloat16), ("umma", torch.float16), ("umma1", torch.bfloat16)])
+def test_fused_gelu_experts_match_oracle(name, engine, dtype):
+    """Plain (non-GLU) expert layer with the tanh form of GELU, the other activation of the reference's layer test
+    (tests/test_commons.py:86-87): fused forward and input-gradient epilogues against the oracle's expert computation
+    with the same activation.  The up projection has I output features here (the first I rows of the case's weights)."""
+    w = SMALL[name]
+    case = make_case(w, seed=2, dtype=dtype)
+    case["w_fc"] = case["w_fc"][:, : w.intermediate].contiguous()
+    gelu = lambda t: torch.nn.functional.gelu(t, approximate="tanh")
+    ref = orc.experts_with_grads(case["x"], case["w_fc"], case["w_proj"], case["rw"], case["sel"], case["g"], act=gelu)
+    _lib.set_engine({"simt": _lib.ENGINE_SIMT, "umma": _lib.ENGINE_UMMA, "umma1": _lib.ENGINE_UMMA_1CTA}[engine])
+    got = run_fused(to_dev(case, dtype), activation="gelu_tanh")
+    check(got, ref, tolerance(dtype), (name, engine, dtype, "gelu_tanh"))
+
+
+def test_gelu_module_takes_the_fused_path():
+    from kernel_hyperdrive_b200 import scattermoe
+
+    assert scattermoe.fused_activation(torch.nn.GELU(approximate="tanh"), is_glu=False) == "gelu_tanh"
+    assert scattermoe.fused_activation(torch.nn.GELU(), is_glu=False) is None  # the erf form stays un-fused
+    ref_m = kh.MoE_Torch(8, 2, 256, 384, torch.nn.GELU(approximate="tanh"), False, False, 0.02).cuda().bfloat16()
+    m = kh.MoE_Triton(8, 2, 256, 384, torch.nn.GELU(approximate="tanh"), False, False, 0.02).cuda().bfloat16()
+    m.load_state_dict(ref_m.state_dict())
+    x = torch.randn(300, 256, device="cuda", dtype=torch.bfloat16)
+    g = torch.randn_like(x)
+    names = []
+    scattermoe.set_timing_sink(names)
+    outs = []
+    try:
+        for layer in (m, ref_m):
+            xr = x.clone().requires_grad_(True)
+            y, _ = layer(xr)
+            y.backward(g)
+            outs.append((y.detach(), xr.grad, layer.c_fc.weight.grad, layer.c_proj.weight.grad))
+    finally:
+        scattermoe.set_timing_sink(None)
+    gemms = ("up_forward", "down_forward", "down_dgrad", "down_wgrad", "up_wgrad", "up_dgrad")
+    assert [n[0] for n in names if n[0] in gemms] == list(gemms)  # the eager module launches none of them
+    for a, b, what in zip(outs[0], outs[1], ("y", "dx", "d_w_fc", "d_w_proj")):
+        assert rel_l2(a, b) < 1.5e-2, (what, rel_l2(a, b))
+
+
 def test_drop_in_shapes_and_state_dict():
     m = kh.MoE_Triton(8, 2, 256, 512, kh.swiglu_unchunked_torch, True, False, 0.02).cuda().bfloat16()
     x = torch.randn(2, 3, 5, 256, device="cuda", dtype=torch.bfloat16)
