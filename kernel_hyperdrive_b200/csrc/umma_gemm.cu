@@ -21,7 +21,9 @@
 // Every wait on an mbarrier is bounded: after about two seconds the waiting thread raises a CTA-wide
 // abort flag, writes a code to the status word and every role leaves its loop; TMEM is freed on the way
 // out.  Nothing here uses cluster multicast.
+#include <cstring>
 #include <mutex>
+#include <unordered_map>
 
 #include "umma_common.cuh"
 
@@ -49,38 +51,89 @@ EncodeTiledFn encode_fn() {
 
 }  // namespace
 
+// Encoded tensor maps are a pure function of (base address, extents, strides, box, element type, swizzle): they are
+// kept in a small cache so that a layer that calls with the same buffers and shapes step after step (weights always,
+// activations whenever the allocator hands back the same blocks) does not pay the driver's encode call on every launch.
+struct MapKey {
+    const void* base;
+    uint64_t dims[3], strides[2];
+    uint32_t box[3];
+    int rank, dtype, swizzle, promo;
+    bool operator==(const MapKey& o) const { return memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        const uint64_t* w = reinterpret_cast<const uint64_t*>(&k);
+        uint64_t h = 1469598103934665603ull;
+        for (size_t i = 0; i < sizeof(MapKey) / 8; ++i) h = (h ^ w[i]) * 1099511628211ull;
+        return (size_t)h;
+    }
+};
+static_assert(sizeof(MapKey) % 8 == 0, "MapKey is hashed in 8-byte words");
+
+int encode_cached(CUtensorMap* map, const MapKey& key_in) {
+    static std::mutex mtx;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    MapKey key;
+    memset(&key, 0, sizeof(key));  // padding bytes take part in the comparison
+    key.base = key_in.base;
+    for (int i = 0; i < 3; ++i) key.dims[i] = key_in.dims[i], key.box[i] = key_in.box[i];
+    for (int i = 0; i < 2; ++i) key.strides[i] = key_in.strides[i];
+    key.rank = key_in.rank, key.dtype = key_in.dtype, key.swizzle = key_in.swizzle, key.promo = key_in.promo;
+    {
+        std::lock_guard<std::mutex> lock(mtx);
+        auto it = cache.find(key);
+        if (it != cache.end()) {
+            *map = it->second;
+            return B200MOE_OK;
+        }
+    }
+    EncodeTiledFn fn = encode_fn();
+    B200MOE_REQUIRE(fn != nullptr, B200MOE_ERR_DRIVER, "cuTensorMapEncodeTiled not available from the driver");
+    cuuint64_t dims[3] = {key.dims[0], key.dims[1], key.dims[2]};
+    cuuint64_t strides[2] = {key.strides[0], key.strides[1]};
+    cuuint32_t box[3] = {key.box[0], key.box[1], key.box[2]};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult rc = fn(map, key.dtype ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)key.rank, (void*)key.base, dims,
+                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, (CUtensorMapSwizzle)key.swizzle, (CUtensorMapL2promotion)key.promo,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    B200MOE_REQUIRE(rc == CUDA_SUCCESS, B200MOE_ERR_DRIVER, "cuTensorMapEncodeTiled failed with %d (rank=%d dims=%llu x %llu x %llu ld=%llu)", (int)rc,
+                    key.rank, (unsigned long long)key.dims[0], (unsigned long long)key.dims[1], (unsigned long long)key.dims[2],
+                    (unsigned long long)key.strides[0]);
+    std::lock_guard<std::mutex> lock(mtx);
+    if (cache.size() >= 4096) cache.clear();
+    cache.emplace(key, *map);
+    return B200MOE_OK;
+}
+
 // Output box of the epilogue: 32 columns x 32 rows (x 1 expert), 64-byte swizzle.  rank 2: [rows][cols] with row
 // stride ld; rank 3: [experts][rows][cols] with expert stride se, so that a tile never spills into the next expert.
 int make_store_map(CUtensorMap* map, const void* base, int64_t experts, int64_t rows, int64_t cols, int64_t ld, int64_t se,
                    int is_f16) {
-    EncodeTiledFn fn = encode_fn();
-    B200MOE_REQUIRE(fn != nullptr, B200MOE_ERR_DRIVER, "cuTensorMapEncodeTiled not available from the driver");
-    int rank = experts > 0 ? 3 : 2;
-    cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)(experts > 0 ? experts : 1)};
-    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)se * 2};
-    cuuint32_t box[3] = {32u, 32u, 1u};
-    cuuint32_t estr[3] = {1u, 1u, 1u};
-    CUresult rc = fn(map, is_f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, (void*)base, dims,
-                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
-                     CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    B200MOE_REQUIRE(rc == CUDA_SUCCESS, B200MOE_ERR_DRIVER, "cuTensorMapEncodeTiled (store map) failed with %d", (int)rc);
-    return B200MOE_OK;
+    MapKey k{};
+    k.base = base;
+    k.rank = experts > 0 ? 3 : 2;
+    k.dims[0] = (uint64_t)cols, k.dims[1] = (uint64_t)rows, k.dims[2] = (uint64_t)(experts > 0 ? experts : 1);
+    k.strides[0] = (uint64_t)ld * 2, k.strides[1] = (uint64_t)se * 2;
+    k.box[0] = 32u, k.box[1] = 32u, k.box[2] = 1u;
+    k.dtype = is_f16 ? 1 : 0;
+    k.swizzle = (int)CU_TENSOR_MAP_SWIZZLE_64B;
+    k.promo = (int)CU_TENSOR_MAP_L2_PROMOTION_NONE;
+    return encode_cached(map, k);
 }
 
 // 2-D row-major matrix [rows][cols] with row stride ld (elements), box of 64 columns x box_rows rows.
 int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows, int is_f16) {
-    EncodeTiledFn fn = encode_fn();
-    B200MOE_REQUIRE(fn != nullptr, B200MOE_ERR_DRIVER, "cuTensorMapEncodeTiled not available from the driver");
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1u, 1u};
-    CUresult rc = fn(map, is_f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims,
-                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    B200MOE_REQUIRE(rc == CUDA_SUCCESS, B200MOE_ERR_DRIVER, "cuTensorMapEncodeTiled failed with %d (rows=%lld cols=%lld ld=%lld)",
-                    (int)rc, (long long)rows, (long long)cols, (long long)ld);
-    return B200MOE_OK;
+    MapKey k{};
+    k.base = base;
+    k.rank = 2;
+    k.dims[0] = (uint64_t)cols, k.dims[1] = (uint64_t)rows, k.dims[2] = 1;
+    k.strides[0] = (uint64_t)ld * 2, k.strides[1] = 0;
+    k.box[0] = 64u, k.box[1] = (uint32_t)box_rows, k.box[2] = 1u;
+    k.dtype = is_f16 ? 1 : 0;
+    k.swizzle = (int)CU_TENSOR_MAP_SWIZZLE_128B;
+    k.promo = (int)CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+    return encode_cached(map, k);
 }
 
 // Row-gather map: [rows][cols] with row stride ld, box of 64 columns x 1 row (tile::gather4 fetches four such rows).

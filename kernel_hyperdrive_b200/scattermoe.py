@@ -17,6 +17,7 @@ Two execution paths exist in `MoE_B200._compute_experts`:
 
 from __future__ import annotations
 
+import os
 from typing import Callable
 
 import torch
@@ -65,6 +66,10 @@ def route(expert_ids: torch.Tensor, num_experts: int, k: int, want_sorted: bool,
     M, dev = expert_ids.numel(), expert_ids.device
     outs = _route_fake(expert_ids, num_experts, k, want_sorted, want_row_maps)
     se, ss, offsets, counts, row_token, row_slot = outs
+    if want_sorted:
+        # an id outside [0, E) is skipped by the sort (status 101): the tail of the two lists then stays unwritten
+        se.zero_()
+        ss.zero_()
     nbytes = lib().b200moe_route_workspace_bytes(M, num_experts)
     ws = _workspace(dev, nbytes)
     check(
@@ -151,6 +156,18 @@ def scattered_experts(inputs, expert_weights, k, sorted_expert_idxs, sorted_scat
 # --------------------------------------------------------------------------------------------------
 # fused path
 # --------------------------------------------------------------------------------------------------
+
+# Device-side failures (a bounded wait that expired, an expert id outside [0, E), an exchange buffer overrun) are
+# written to a per-device status word that the host reads with `_lib.check_status(device)`.  Reading it synchronises the
+# stream, so the layers do not do it on their own; with this switch on (or B200MOE_CHECK_STATUS=1 in the environment)
+# the fused path checks at the end of every forward and backward pass and raises on a recorded failure.
+CHECK_STATUS = os.environ.get("B200MOE_CHECK_STATUS", "0") == "1"
+
+
+def _maybe_check_status(device: torch.device) -> None:
+    if CHECK_STATUS and not torch.compiler.is_compiling():
+        _lib.check_status(device)
+
 
 # When a list is installed here, every grouped-GEMM launch of the fused path is bracketed by two CUDA
 # events on the current stream and (name, start, end) is appended; the benchmark reads kernel durations
@@ -345,6 +362,7 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
         ctx.activation = activation
         ctx.rw_dtype = router_weights.dtype
         ctx.dx_out = dx_out if k == 1 else None
+        _maybe_check_status(x.device)
         return y
 
     @staticmethod
@@ -394,6 +412,7 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
                 _launch("combine_dx", _combine_rows, dx_rows, slot_row, None, d_x, k)
         if d_gates is not None:
             d_rw = d_gates.view(T, k).to(ctx.rw_dtype)
+        _maybe_check_status(x.device)
         return d_x, d_w_fc, d_w_proj, d_rw, None, None, None
 
 
