@@ -259,7 +259,7 @@ SHARE = {"up_forward": 4, "down_forward": 2, "down_dgrad": 2, "down_wgrad": 2, "
 class Job:
     """One workload on this rank: the layer, its resident inputs and the forward closure."""
 
-    def __init__(self, w, world, rank, dev, exchange, placement=None, micro_batches=1):
+    def __init__(self, w, world, rank, dev, exchange, placement=None, micro_batches=1, sync_free=False):
         import torch.distributed as dist
 
         import kernel_hyperdrive_b200 as kh
@@ -283,7 +283,7 @@ class Job:
                 rows = int(1.25 * T * k)  # iid logits: the per-rank receive counts stay within a few percent of T * k
             self.layer = MoE_B200_EP(E, k, H, I, kh.swiglu_unchunked_torch, True, False, w.weight_std, group=dist.group.WORLD, device=dev, dtype=dtype, seed=0,
                                      exchange=exchange, exchange_rows=(rows + 127) // 128 * 128, placement=placement, expected_load=expected,
-                                     micro_batches=micro_batches, **extra)
+                                     micro_batches=micro_batches, sync_free=sync_free, **extra)
         else:
             torch.manual_seed(0)
             torch.set_default_dtype(dtype)  # build the (large) expert tensors directly in the workload's type
@@ -386,9 +386,7 @@ class Job:
         if self.world > 1:
             import torch.distributed as dist
 
-            from kernel_hyperdrive_b200 import expert_parallel
-
-            rows = float(expert_parallel.last_received_rows or 0)
+            rows = float(self.layer.received_rows())
             exch = sum(v for n, v in phases.items() if n.startswith("ep_push") or n.startswith("ep_pull"))
             barr = phases.get("ep_barrier", 0.0)
             mine = torch.tensor([rows, gemm_total, exch, barr], device=self.dev, dtype=torch.float64)
@@ -424,7 +422,7 @@ def run_ep_configs(args, world, rank, dev, peaks):
             continue
         w = synthetic.scaled(base, tokens=base.tokens // world)
         try:
-            job = Job(w, world, rank, dev, args.ep_exchange, micro_batches=args.ep_micro_batches)
+            job = Job(w, world, rank, dev, args.ep_exchange, micro_batches=args.ep_micro_batches, sync_free=args.ep_sync_free)
             m = job.measure_resident(args.ep_config_steps, 3)
             entry = {
                 "tokens_global": base.tokens, "tokens_per_gpu": w.tokens, "experts_per_gpu": base.num_experts // world, "ms_per_step": round(m["ms_per_step"], 4),
@@ -509,7 +507,7 @@ def run_gpu_arm(args, w):
             dist.destroy_process_group()
             sys.exit(3)
 
-    job = Job(w, world, rank, dev, args.ep_exchange, placement=args.ep_placement, micro_batches=args.ep_micro_batches)
+    job = Job(w, world, rank, dev, args.ep_exchange, placement=args.ep_placement, micro_batches=args.ep_micro_batches, sync_free=args.ep_sync_free)
     dtype, T, H = job.dtype, w.tokens, w.hidden
     x_host, g_host, params, forward = job.x_host, job.g_host, job.params, job.forward
     y_host = torch.empty(T, H, dtype=dtype).pin_memory()
@@ -716,6 +714,7 @@ def main():
     ap.add_argument("--tile-scheduler", type=int, default=None, choices=[0, 1, 2, 3], help="two-CTA kernels: 0 = fixed stride, 1 = weight-gradient launches draw tiles from a counter, 2 = those and long-reduction row launches (library default), 3 = every launch")
     ap.add_argument("--ep-placement", default=None, choices=["contiguous", "strided", "balanced"], help="N > 1: expert -> rank placement (default: contiguous; the Zipf workload defaults to balanced by expected load)")
     ap.add_argument("--ep-micro-batches", type=int, default=1, help="N > 1, peer-memory exchange: slices of a rank's tokens whose transfers overlap the expert GEMMs of the other slices")
+    ap.add_argument("--ep-sync-free", action="store_true", help="N > 1, peer-memory exchange: no host read per pass (local tensors sized by the buffer capacity)")
     ap.add_argument("--skip-ep-parity", action="store_true", help="N > 1: skip the parity check of the expert-parallel exchange that precedes the timing")
     ap.add_argument("--no-ep-configs", action="store_true", help="skip the short runs of the other benchmark configurations appended as `ep_configs`")
     ap.add_argument("--ep-config-steps", type=int, default=5)

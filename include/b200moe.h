@@ -121,7 +121,9 @@ int64_t b200moe_route_workspace_bytes(int64_t M, int E);
  * grouped order.  Replaces `selected_experts.flatten().sort()` and
  * `contiguous_count_cute(...).cumsum(-1)` (SMT/__init__.py:79-81).  The order inside one expert's segment
  * is ascending flat index (what torch.sort(stable=True) gives).
- *   expert_ids             device int64 (M), values in [0, E)
+ *   expert_ids             device int64 (M), values in [0, E); a NEGATIVE value marks a slot that goes to no expert
+ *                          (a padding token, a slot dropped by a capacity limit): it is counted nowhere and appears
+ *                          in none of the outputs; a value >= E sets status word 101 and is left out as well
  *   sorted_expert_idxs     device int64 (M)      or NULL
  *   sorted_scattered_idxs  device int64 (M)      or NULL
  *   expert_offsets         device int64 (E), inclusive prefix sum of the counts

@@ -57,8 +57,8 @@ __global__ void __launch_bounds__(kSortThreads) route_block_hist(const int64_t* 
             int64_t e = ids[i];
             if (e >= 0 && e < E) {
                 atomicAdd(&hist[e], 1);
-            } else if (status) {
-                atomicExch(status, 101);  // expert id out of range
+            } else if (e >= E && status) {
+                atomicExch(status, 101);  // expert id out of range (a negative id is a slot without an expert: left out)
             }
         }
     }

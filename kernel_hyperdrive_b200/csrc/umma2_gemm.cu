@@ -194,7 +194,8 @@ struct Ctl2 {
     int sched_tile[SCHED_SLOTS];
     uint32_t tmem_slot;
     int abort_flag;
-    int pad[2];
+    int use_counter;  // tiles come from the global counter (else: fixed stride)
+    int pad[1];
     Tables tb;
 };
 
@@ -221,7 +222,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(EPI), 1)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const int cluster_id = blockIdx.x >> 1, nclusters = gridDim.x >> 1;
-    const bool dyn = p.tile_counter != nullptr;
 
     for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
         int64_t prev = e ? p.offsets[e - 1] : 0;
@@ -247,7 +247,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(EPI), 1)
     __syncthreads();
     if (p.wfam) fill_expert_order(tb, p.E);
     if (threadIdx.x == 0) {
-        int start = 0, tiles = 0;
+        int start = 0, tiles = 0, maxc = 0;
+        long long sum = 0;
         for (int e = 0; e < p.E; ++e) {
             int cnt = tb.seg_cnt[e];
             int cover = p.padded ? (cnt + kPadRows - 1) / kPadRows * kPadRows : cnt;
@@ -255,8 +256,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(EPI), 1)
             tb.tile_prefix[e] = tiles;
             start += cover;
             tiles += ((cover + BM - 1) / BM + 1) / 2;
+            sum += cnt;
+            maxc = cnt > maxc ? cnt : maxc;
         }
         tb.tile_prefix[p.E] = tiles;
+        // Weight-gradient tiles are drawn from the counter only when the experts' row counts are uneven (the largest above
+        // twice the mean): with even counts the fixed stride balances as well and needs no hand-over of indices.  Both
+        // CTAs of every cluster see the same counts and so take the same decision.
+        ctl.use_counter = p.tile_counter != nullptr && (!p.wfam || (long long)maxc * p.E > 2 * sum);
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl.tmem_slot)), "r"(512)
@@ -268,6 +275,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(EPI), 1)
     tc_fence_after();
     const uint32_t tmem_base = *(volatile uint32_t*)&ctl.tmem_slot;
     const int ntiles = total_tiles2(p, tb);
+    const bool dyn = *(volatile int*)&ctl.use_counter != 0;
 
     // ---- tile feed ----
     // Readers (every role except the leader's producer): the next tile index of this cluster, or a value >= ntiles when
@@ -497,11 +505,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(EPI), 1)
             const uint32_t empty0_peer = map_to_cta(empty0, 1);
             const uint32_t idesc = p.idesc;
             uint32_t ready = 0;  // the look-ahead result for (stage, phase)
-            for (int t = next_tile(false, 218); t < ntiles && ok; t = next_tile(false, 218)) {
+            // The index of the following tile is fetched right after the first k step of the current one has been issued:
+            // it was published a whole tile earlier, and the fetch then overlaps MMAs already queued.
+            int t = next_tile(false, 218);
+            while (t < ntiles && ok) {
                 decode_tile2(p, tb, t, 0, ti);
                 if (!mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1, abort_flag, p.status, 212)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
+                int t_next = 0x7fffffff;
+                bool have_next = false;
                 for (int ks = 0; ks < ti.ksteps; ++ks) {
                     if (!ready && !mbar_wait(full0 + stage * 8, phase, abort_flag, p.status, 213)) {
                         ok = false;
@@ -522,6 +535,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(EPI), 1)
                     // the stage is free in both CTAs once these MMAs have read it
                     tc_commit_pair(empty0 + s_cur * 8);
                     tc_commit_pair(empty0_peer + s_cur * 8);
+                    if (ks == 0) {
+                        t_next = next_tile(false, 218);
+                        have_next = true;
+                    }
                 }
                 if (!ok) break;
                 const uint32_t fb = smem_u32(&tmem_full_bar[acc]);
@@ -531,6 +548,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(EPI), 1)
                     acc = 0;
                     acc_phase ^= 1;
                 }
+                t = have_next ? t_next : next_tile(false, 218);
             }
         }
     } else {
@@ -563,9 +581,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(EPI), 1)
         int acc = 0;
         uint32_t acc_phase = 0;
         Tile ti;
-        for (int t = next_tile(true, 219); t < ntiles; t = next_tile(true, 219)) {
+        for (int t = next_tile(true, 219), t_next; t < ntiles; t = t_next) {
             decode_tile2(p, tb, t, rank, ti);
             if (!mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status, 215, 200)) break;
+            t_next = next_tile(true, 219);  // published a tile ago: no wait, and off the path between two accumulators
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
             // a CTA whose half of the cluster tile does not exist (odd number of row blocks) has nothing to write

@@ -133,6 +133,15 @@ def exchange_counts(counts: torch.Tensor, world: int, group) -> torch.Tensor:
 
 
 last_received_rows = None  # rows this rank's experts received in the most recent exchange pass (load report)
+_last_plan = None          # plan of the most recent peer-memory pass (its received-row count may not have been read yet)
+
+
+def received_rows_of_last_pass() -> int:
+    """Rows this rank's experts received in the most recent pass; reads the count from the plan where the pass itself
+    ran without a host read."""
+    if last_received_rows is not None:
+        return int(last_received_rows)
+    return _last_plan.received_rows() if _last_plan is not None else 0
 
 
 def ep_experts(x, router_weights, selected_experts, num_experts: int, local_experts_fn: Callable, group, ops=CudaRowOps):
@@ -207,6 +216,7 @@ class PeerExchange:
         torch.cuda.synchronize(device)
         dist.barrier(group)  # every rank's flags are zero before anyone publishes an epoch
         self.backward_reads_pending = False
+        self.sync_free = False  # True: no host read per pass (see _PeerDispatch.forward)
         self.host_rows = torch.empty(2, dtype=torch.int64).pin_memory()  # landing place of the per-pass host read
 
     def barrier(self) -> None:
@@ -241,6 +251,21 @@ class _Plan:
     """Where this rank's sorted rows go: computed once per pass from the all-gathered expert counts."""
 
     __slots__ = ("ss", "inv", "start", "base", "m_recv", "max_recv", "local_ids", "k", "_recv_counts", "_host", "_event", "_e_local", "_world")
+
+    def local_ids_for_capacity(self, cap_rows: int) -> torch.Tensor:
+        """Local expert of every row of a receive buffer of `cap_rows` rows, -1 for the rows past the received ones,
+        computed on the device without knowing the received count on the host."""
+        dev = self._recv_counts.device
+        cum = self._recv_counts.reshape(-1).long().cumsum(0)
+        seg = torch.searchsorted(cum, torch.arange(cap_rows, device=dev), right=True)
+        ids = torch.cat([torch.arange(self._e_local, device=dev).repeat(self._world), torch.full((1,), -1, device=dev, dtype=torch.long)])
+        return ids[seg.clamp(max=self._world * self._e_local)]
+
+    def received_rows(self) -> int:
+        """Rows this rank received in the pass of this plan (waits for the small host copy queued with the plan)."""
+        if self._event is not None:
+            self._event.synchronize()
+        return int(self._host[0].item())
 
     def resolve(self) -> None:
         """Finish the plan with the one host read of the pass: the number of rows this rank receives (it sizes the local
@@ -320,6 +345,12 @@ class _PeerDispatch(torch.autograd.Function):
         xc.backward_reads_pending = torch.is_grad_enabled()
         xc.push("x", x.contiguous(), plan.ss, plan.k, None, plan)
         xc.barrier()  # all rows have landed
+        if getattr(xc, "sync_free", False):
+            # No host read: the local tensors are sized by the buffer capacity and the rows past the received ones carry
+            # no expert.  A buffer that is too small shows up as status word 301 (rows skipped), not as an exception.
+            plan.m_recv = xc.cap_rows
+            plan.local_ids = plan.local_ids_for_capacity(xc.cap_rows)
+            return xc.bufs["x"]
         plan.resolve()
         # The decision is the same on every rank (the largest receive count of the group), so either all ranks go on to
         # the next barrier or none does.  Rows that did not fit were skipped by the push kernel (status 301).
@@ -379,6 +410,10 @@ def ep_experts_p2p(x, router_weights, selected_experts, num_experts: int, local_
     world, rank = xc.world, dist.get_rank(xc.group)
     with torch.no_grad(), _phase("ep_plan"):
         plan = _make_plan(selected_experts, num_experts, world, rank, xc.group, ops, getattr(xc, "host_rows", None))
+    global _last_plan, last_received_rows
+    _last_plan = plan
+    if getattr(xc, "sync_free", False):
+        last_received_rows = None
     recv = _PeerDispatch.apply(x, xc, plan)
     out_rows = local_experts_fn(recv, plan.local_ids)
     return _PeerCombine.apply(out_rows, router_weights.to(x.dtype), xc, plan, ops)
@@ -433,7 +468,7 @@ class MoE_B200_EP(nn.Module):
     def __init__(self, num_experts, num_experts_per_tok, hidden_size, intermediate_size, activation_function, is_glu, add_bias, std,
                  group=None, device=None, dtype=torch.float32, seed: int = 0, ops=CudaRowOps, local_experts_fn=None,
                  num_shared_experts: int = 0, shared_intermediate_size: int | None = None, router_scoring: str = "softmax",
-                 exchange: str = "nccl", exchange_rows: int | None = None, placement=None, expected_load=None, micro_batches: int = 1):
+                 exchange: str = "nccl", exchange_rows: int | None = None, placement=None, expected_load=None, micro_batches: int = 1, sync_free: bool = False):
         super().__init__()
         assert is_glu, "the expert-parallel layer implements GLU experts"
         assert router_scoring in ("softmax", "sigmoid")
@@ -458,11 +493,15 @@ class MoE_B200_EP(nn.Module):
         self.exchange = PeerExchange(self.group, exchange_rows, hidden_size, dtype, torch.device(device)) if exchange == "p2p" else None
         # Pipelining (peer-memory exchange only): the rank's tokens are split into `micro_batches` parts, each with its own
         # exchange buffers and stream, so that the row transfers of one part run while the expert GEMMs of another do.
+        if self.exchange is not None:
+            self.exchange.sync_free = sync_free
         self.micro_batches = micro_batches if exchange == "p2p" else 1
         self._pipe = None
         if self.micro_batches > 1:
             rows = ((exchange_rows + self.micro_batches - 1) // self.micro_batches + 127) // 128 * 128
             self._pipe = [(PeerExchange(self.group, rows, hidden_size, dtype, torch.device(device)), torch.cuda.Stream(device)) for _ in range(self.micro_batches)]
+            for xc_, _ in self._pipe:
+                xc_.sync_free = sync_free
         # every rank draws with the same per-expert seeds on the same kind of device, so shards agree across ranks
         gen_dev = torch.device(device) if device is not None and torch.device(device).type == "cuda" else torch.device("cpu")
 
@@ -545,6 +584,8 @@ class MoE_B200_EP(nn.Module):
         T = hidden_states.size(0)
         bounds = [T * i // self.micro_batches for i in range(self.micro_batches + 1)]
         outs, received = [], 0
+        sync_free_mode = self._pipe[0][0].sync_free
+        plans = []
         global last_received_rows
         for i, (xc, stream) in enumerate(self._pipe):
             lo, hi = bounds[i], bounds[i + 1]
@@ -554,11 +595,20 @@ class MoE_B200_EP(nn.Module):
                                      lambda rows, ids, xc=xc: self.local_experts(rows, ids, xc), xc, self.ops)
             y_i.record_stream(main)
             outs.append(y_i)
-            received += last_received_rows or 0
+            plans.append(_last_plan)
+            received += received_rows_of_last_pass() if not sync_free_mode else 0
         for _, stream in self._pipe:
             main.wait_stream(stream)
-        last_received_rows = received
+        last_received_rows = received if not sync_free_mode else None
+        self._plans_of_last_pass = plans
         return torch.cat(outs)
+
+    def received_rows(self) -> int:
+        """Rows this rank's experts received in the most recent pass (load report; may wait for a small host copy)."""
+        plans = getattr(self, "_plans_of_last_pass", None)
+        if self._pipe is not None and plans:
+            return sum(p.received_rows() for p in plans)
+        return received_rows_of_last_pass()
 
     def allreduce_replicated_grads(self) -> None:
         """Sums the gradient of the replicated gate over the ranks (tokens are data-parallel)."""
@@ -614,7 +664,8 @@ def parity_selfcheck(group, device, cases=None) -> dict:
     if cases is None:
         cases = [("fp32_E16_k4_H256_I384", torch.float32, 16, 4, 256, 384, 800, None, 1), ("bf16_E64_k6_H512_I768", torch.bfloat16, 64, 6, 512, 768, 800, None, 1),
                  ("bf16_E64_k6_H512_I768_strided", torch.bfloat16, 64, 6, 512, 768, 800, "strided", 1),
-                 ("bf16_E64_k6_H512_I768_pipelined3", torch.bfloat16, 64, 6, 512, 768, 800, None, 3)]
+                 ("bf16_E64_k6_H512_I768_pipelined3", torch.bfloat16, 64, 6, 512, 768, 800, None, 3),
+                 ("bf16_E64_k6_H512_I768_no_host_read", torch.bfloat16, 64, 6, 512, 768, 800, None, -1)]
     report, ok = {}, True
     for name, dtype, E, k, H, I, T, placement, micro in cases:
         if E % world:
@@ -629,7 +680,7 @@ def parity_selfcheck(group, device, cases=None) -> dict:
         for exchange in ("p2p", "nccl") if micro == 1 else ("p2p",):
             cap = (sum(counts) * k + 127) // 128 * 128
             layer = MoE_B200_EP(E, k, H, I, swiglu_unchunked_torch, True, False, 0.05, group=group, device=device, dtype=dtype, seed=5,
-                                exchange=exchange, exchange_rows=cap, placement=placement, micro_batches=micro)
+                                exchange=exchange, exchange_rows=cap, placement=placement, micro_batches=max(micro, 1), sync_free=micro < 0)
             ref = MoE_B200(E, k, H, I, swiglu_unchunked_torch, True, False, 0.05).to(device).to(dtype)
             ref.load_state_dict(layer.full_state_dict())
             x = x_all[lo : lo + counts[rank]].clone().requires_grad_(True)

@@ -351,7 +351,7 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
             # reference's bmm over its `output_expanded`.  The backward forms the gate gradient from the kept rows.
             y_rows = torch.empty(cap, H, device=x.device, dtype=x.dtype)
             _launch("down_forward", _down_forward, a, w_proj, offsets, None, None, y_rows)
-            slot_row = torch.empty(M, device=x.device, dtype=torch.int32)
+            slot_row = torch.full((M,), -1, device=x.device, dtype=torch.int32)  # -1: a slot without an expert contributes nothing
             _invert_row_map(row_slot, slot_row)
             y = y_out[:T] if (k == 1 and y_out is not None) else torch.empty(T, H, device=x.device, dtype=x.dtype)
             _launch("combine_y", _combine_rows, y_rows, slot_row, gates, y, k)
@@ -378,7 +378,7 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
         # upstream gradient rows in the padded grouped order, scaled by their gates (the reference's
         # `group(grad_out, coeff=gates)`), and the gate gradient <unweighted expert output, upstream gradient>
         g_rows = torch.empty(cap, H, device=x.device, dtype=x.dtype)
-        d_gates = torch.empty(M, device=x.device, dtype=torch.float32) if (need_g and y_rows is not None) else None
+        d_gates = torch.zeros(M, device=x.device, dtype=torch.float32) if (need_g and y_rows is not None) else None  # slots without an expert keep 0
         _launch("gather_grad", _gather_grad_rows, grad_y, row_token, row_slot, gates, y_rows if d_gates is not None else None, g_rows, d_gates, True)
         del y_rows
 
@@ -406,7 +406,7 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
                 dx_rows = torch.empty(cap, H, device=x.device, dtype=x.dtype)
                 _launch("up_dgrad", _up_dgrad, dh, w_fc, offsets, None, dx_rows)
                 if slot_row is None:
-                    slot_row = torch.empty(M, device=x.device, dtype=torch.int32)
+                    slot_row = torch.full((M,), -1, device=x.device, dtype=torch.int32)
                     _invert_row_map(row_slot, slot_row)
                 d_x = torch.empty(T, H, device=x.device, dtype=x.dtype)
                 _launch("combine_dx", _combine_rows, dx_rows, slot_row, None, d_x, k)
@@ -423,7 +423,8 @@ ACTIVATIONS = {"swiglu": 0, "glu": 1, "gelu_tanh": 2}
 
 def fused_swiglu_experts(x, w_fc, w_proj, router_weights, selected_experts, y_out=None, dx_out=None, activation: str = "swiglu"):
     """Routed experts on the fused kernels; `activation` (`ACTIVATIONS`) selects the gate function of a GLU layer or the
-    un-gated tanh-GELU of a plain one."""
+    un-gated tanh-GELU of a plain one.  A negative entry of `selected_experts` is a slot without an expert (padding, a
+    dropped token): it contributes nothing to the output and receives a zero router-weight gradient."""
     if x.size(0) == 0:
         # no tokens: nothing to launch; the zero-weighted sums keep every input in the graph with a zero gradient
         return x.new_zeros(0, x.size(1)) + 0 * (x.sum() + w_fc.sum() + w_proj.sum() + router_weights.sum())

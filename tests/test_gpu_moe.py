@@ -196,6 +196,29 @@ def test_gelu_module_takes_the_fused_path():
         assert rel_l2(a, b) < 1.5e-2, (what, rel_l2(a, b))
 
 
+@pytest.mark.parametrize("dtype,engine", [(torch.float32, "simt"), (torch.bfloat16, "umma")])
+def test_slots_without_an_expert_are_left_out(dtype, engine):
+    """Negative expert ids (padding tokens, slots dropped by a capacity limit) take no part: same output and gradients as
+    the oracle run in which those slots carry a zero gate, and a zero router-weight gradient for them."""
+    w = synthetic.MoEWorkload("drop", 8, 3, 128, 256, 300, routing="normal_logits")
+    case = make_case(w, seed=4, dtype=dtype)
+    drop = torch.rand(case["sel"].shape, generator=torch.Generator().manual_seed(9)) < 0.3
+    drop[7] = True  # a token that keeps no expert at all
+    ref_case = dict(case)
+    ref_case["rw"] = torch.where(drop, torch.zeros_like(case["rw"]), case["rw"])
+    ref = oracle_experts(ref_case)
+    case["sel"] = torch.where(drop, torch.full_like(case["sel"], -1), case["sel"])
+    _lib.set_engine({"simt": _lib.ENGINE_SIMT, "umma": _lib.ENGINE_UMMA}[engine])
+    got = run_fused(to_dev(case, dtype))
+    keep = ~drop
+    tol = tolerance(dtype)
+    for key in ("y", "dx", "d_w_fc", "d_w_proj"):
+        assert rel_l2(got[key], ref[key]) < tol, (key, rel_l2(got[key], ref[key]))
+    assert float(got["y"][7].abs().max()) == 0.0
+    assert rel_l2(got["d_router_weights"].cpu()[keep], ref["d_router_weights"][keep]) < tol
+    assert float(got["d_router_weights"].cpu()[drop].abs().max()) == 0.0
+
+
 def test_drop_in_shapes_and_state_dict():
     m = kh.MoE_Triton(8, 2, 256, 512, kh.swiglu_unchunked_torch, True, False, 0.02).cuda().bfloat16()
     x = torch.randn(2, 3, 5, 256, device="cuda", dtype=torch.bfloat16)
