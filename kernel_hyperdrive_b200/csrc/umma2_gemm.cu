@@ -170,8 +170,14 @@ __device__ __forceinline__ void decode_tile2(const UmmaParams& p, const Tables& 
         ti.e = lo;
         int pairs_e = tb.tile_prefix[lo + 1] - tb.tile_prefix[lo];
         int local = t - tb.tile_prefix[lo] * p.nb_count;
-        ti.nb = local / pairs_e;
-        int pair = local - ti.nb * pairs_e;
+        int pair;
+        if (p.nb_inner) {
+            pair = local / p.nb_count;
+            ti.nb = local - pair * p.nb_count;
+        } else {
+            ti.nb = local / pairs_e;
+            pair = local - ti.nb * pairs_e;
+        }
         int blk = 2 * pair + rank;
         ti.mb = blk;
         ti.row0 = tb.seg_start[lo] + blk * BM;

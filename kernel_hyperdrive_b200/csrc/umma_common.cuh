@@ -24,6 +24,7 @@ struct UmmaParams {
     int N;          // columns of the output (R: N, W: Nout)
     int Mout;       // W: rows of the output
     int nb_count;   // column blocks
+    int nb_inner;   // R: 1 = walk the column blocks of a row tile first (the expert's weight matrix fits L2), 0 = the row tiles of a column block first
     int mb_count;   // W: row blocks
     int swiglu_half;  // EPI_SWIGLU: I (columns of one half); tiles cover 128 columns of each half
     // operand A (R: activations; W: P)
@@ -281,8 +282,14 @@ __device__ __forceinline__ void decode_tile(const UmmaParams& p, const Tables& t
         ti.e = lo;
         int mt_e = tb.tile_prefix[lo + 1] - tb.tile_prefix[lo];
         int local = t - tb.tile_prefix[lo] * p.nb_count;
-        ti.nb = local / mt_e;  // all row tiles of one column block first: the weight panel is shared
-        int mt = local - ti.nb * mt_e;
+        int mt;
+        if (p.nb_inner) {  // all column blocks of one row tile first: the rows are streamed once, the weights come from L2
+            mt = local / p.nb_count;
+            ti.nb = local - mt * p.nb_count;
+        } else {  // all row tiles of one column block first: the weight panel is shared by the tiles in flight
+            ti.nb = local / mt_e;
+            mt = local - ti.nb * mt_e;
+        }
         ti.mb = mt;
         ti.row0 = tb.seg_start[lo] + mt * BM;
         int cover = p.padded ? (tb.seg_cnt[lo] + kPadRows - 1) / kPadRows * kPadRows : tb.seg_cnt[lo];

@@ -660,6 +660,15 @@ int umma_row_gemm(const RowGemm& g, int dtype, int32_t* status, cudaStream_t str
     p.status = status;
     p.idesc = make_idesc(0, p.b_mn, p.is_f16, BM);
     p.full_count = 1 + (p.a_tma ? 0 : GATHER_THREADS);
+    // Tile order inside an expert.  The tiles in flight at one time are consecutive in the list; what they share comes from
+    // L2, what they do not share is streamed from HBM once per visit.  When one expert's weight matrix is small enough to stay
+    // in L2 beside the activations in flight (K * N * 2 bytes up to 32 MB), the column blocks of a row tile are walked first, so
+    // that every activation row is read from HBM once; with larger weight matrices (the Mixtral-shaped layer: 117 / 235 MB per
+    // expert) the row tiles of a column block are walked first, so that the tiles in flight share the weight panel.
+    {
+        const int forced = option_value(B200MOE_OPT_TILE_ORDER);
+        p.nb_inner = forced >= 0 ? forced : ((int64_t)g.K * g.N * 2 <= ((int64_t)32 << 20) ? 1 : 0);
+    }
 
     CUtensorMap ma{}, mb{};
     int rc;
