@@ -252,7 +252,7 @@ int b200moe_gather_rows(const void* src, int64_t lds, const int32_t* row_map, vo
 
 /* Up projection with the token gather on the input rows and the gated activation in the epilogue:
  * h[p, :] = x[row_token[p], :] @ w_fc[e(p)]^T  (Mcap, 2I), a[p, :] = h[p, :I] * m(h[p, I:])  (Mcap, I).
- * h is kept for b200moe_down_dgrad only and its column order is the engine's own (see there).
+ * h is kept for b200moe_down_dgrad only; what it holds and in which column order is the engine's own business (see there).
  * row_token == NULL: x already holds the padded grouped rows (m_cap rows, see b200moe_gather_rows).
  * Replaces scatter2scatter for c_fc plus the activation call (SMT/__init__.py:83-91). */
 int b200moe_up_forward(const void* x, int64_t ldx, const void* w_fc, const int64_t* expert_offsets,
@@ -288,8 +288,10 @@ int b200moe_gather_grad_rows(const void* grad_out, int64_t ldg, const int32_t* r
  * rows, from b200moe_gather_grad_rows); with row_token given it holds T token rows instead and the kernel gathers
  * them (no gate scaling then).  With d[p, :] = grad_rows[p, :] @ w_proj[e(p)] rounded to the tensor type (Mcap, I):
  *   dh[p, :] = activation backward of h[p, :] for upstream d[p, :]   (Mcap, 2I), plain (up | gate) column order
- * h is the buffer b200moe_up_forward wrote IN THE SAME ENGINE: the tensor-core engine stores it interleaved per
- * 32-column chunk (up part, gate part), the CUDA-core engine as (up | gate); treat it as opaque between the two calls.
+ * h is the buffer b200moe_up_forward wrote IN THE SAME ENGINE; treat it as opaque between the two calls.  The CUDA-core
+ * engine keeps the pre-activation (up | gate) there; the tensor-core engine keeps, interleaved per 32-column chunk, the
+ * two factors of the activation's derivative (m(gate) and up * m'(gate), resp. gelu_tanh'(h)), computed in its forward
+ * epilogue from h rounded to the tensor type, so that this kernel's epilogue is two multiplications per element.
  * Replaces scatter2scatter of the c_proj backward (SMT/ops.py:247-256) and the activation backward between the two
  * projections (cute_kernels/kernels/swiglu_unchunked/triton_implementation/kernels_backward.py:13-48). */
 int b200moe_down_dgrad(const void* grad_rows, int64_t ldg, const void* w_proj, const int64_t* expert_offsets,

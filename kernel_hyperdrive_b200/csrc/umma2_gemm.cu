@@ -702,8 +702,6 @@ int launch_2cta(int epi, const UmmaParams& p, const CUtensorMap& ma, const CUten
             return launch2<EPI_DGRAD_DOWN>(p, ma, mb, mo, mo2, mo3, tiles_bound, stream);
         case EPI_GLU:
             return launch2<EPI_GLU>(p, ma, mb, mo, mo2, mo3, tiles_bound, stream);
-        case EPI_DGRAD_DOWN_GLU:
-            return launch2<EPI_DGRAD_DOWN_GLU>(p, ma, mb, mo, mo2, mo3, tiles_bound, stream);
         case EPI_UNARY:
             return launch2<EPI_UNARY>(p, ma, mb, mo, mo2, mo3, tiles_bound, stream);
         case EPI_DGRAD_UNARY:

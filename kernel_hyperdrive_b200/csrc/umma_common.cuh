@@ -385,20 +385,28 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
             tc_ld32(taddr + c, u);
             tc_ld32(taddr + 128 + c, gt);
             tc_wait_ld();
+            // What is kept for the backward pass are the two factors of the activation's derivative, not h itself: with
+            // d the gradient of the activation output, d(up) = d * m(gate) and d(gate) = d * up * m'(gate).  All the
+            // transcendental work thus happens here, where the epilogue has slack, and the down-dgrad epilogue is left with
+            // two multiplications per element.  The factors are formed in fp32 from h rounded to the tensor type (what the
+            // reference materialises) and rounded once more when stored.
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-                hu[i] = pack2(__uint_as_float(u[2 * i]), __uint_as_float(u[2 * i + 1]), is_f16);
-                hg[i] = pack2(__uint_as_float(gt[2 * i]), __uint_as_float(gt[2 * i + 1]), is_f16);
-                // the activation sees the values as stored (rounded to the tensor type)
-                float2 fu = unpack2(hu[i], is_f16), fg = unpack2(hg[i], is_f16);
-                av[i] = pack2(fu.x * gate_value(ACT, fg.x, sigmoid_tanh(fg.x)), fu.y * gate_value(ACT, fg.y, sigmoid_tanh(fg.y)), is_f16);
+                const uint32_t ru = pack2(__uint_as_float(u[2 * i]), __uint_as_float(u[2 * i + 1]), is_f16);
+                const uint32_t rg = pack2(__uint_as_float(gt[2 * i]), __uint_as_float(gt[2 * i + 1]), is_f16);
+                const float2 fu = unpack2(ru, is_f16), fg = unpack2(rg, is_f16);
+                const float s0 = sigmoid_tanh(fg.x), s1 = sigmoid_tanh(fg.y);
+                const float m0 = gate_value(ACT, fg.x, s0), m1 = gate_value(ACT, fg.y, s1);
+                av[i] = pack2(fu.x * m0, fu.y * m1, is_f16);
+                hu[i] = pack2(m0, m1, is_f16);
+                hg[i] = pack2(fu.x * gate_slope(ACT, fg.x, s0), fu.y * gate_slope(ACT, fg.y, s1), is_f16);
             }
-            // h is stored interleaved per 32-column chunk: chunk j of a row holds up[32j .. 32j+w) then gate[32j .. 32j+w)
-            // (w = 32 except in a ragged last chunk), so that the down-dgrad epilogue finds both halves of a chunk in one
-            // 128-byte line.  The up box has its own map, clipped where the last chunk's gate part begins.
+            // stored interleaved per 32-column chunk: chunk j of a row holds the 32 (w in a ragged last chunk) first factors,
+            // then the second factors of the same columns, so that the down-dgrad epilogue finds both in one 128-byte line.
+            // The first box has its own map, clipped where the last chunk's second part begins.
             const int wch = min(32, I - (n0 + c));
-            stage_store(mo, 2 * (n0 + c), row_c, 0, hu);         // up part of the chunk
-            stage_store(mo3, 2 * (n0 + c) + wch, row_c, 0, hg);  // gate part of the chunk
+            stage_store(mo, 2 * (n0 + c), row_c, 0, hu);
+            stage_store(mo3, 2 * (n0 + c) + wch, row_c, 0, hg);
             stage_store(mo2, n0 + c, row_c, 0, av);   // activation
         }
     } else if (EPI == EPI_ROUTER) {
@@ -497,7 +505,7 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
         }
     } else if (EPI == EPI_UNARY) {
         // Non-GLU expert, forward: the tile holds 256 columns of h = x @ w_fc^T.  h is rounded to the tensor type (the
-        // reference materialises it) and stored for the backward pass, a = gelu_tanh(h) is stored for the down projection.
+        // reference materialises it); a = gelu_tanh(h) is stored for the down projection and gelu_tanh'(h) for the backward pass.
         const int n0 = ti.nb * BN;
         const int row_c = ti.row0 + q * 32;
 #pragma unroll 1
@@ -508,16 +516,17 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
             tc_wait_ld();
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-                hv[i] = pack2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]), is_f16);
-                const float2 f = unpack2(hv[i], is_f16);
-                av[i] = pack2(gelu_tanh_value(f.x, tanh_fast(gelu_tanh_arg(f.x))), gelu_tanh_value(f.y, tanh_fast(gelu_tanh_arg(f.y))), is_f16);
+                const float2 f = unpack2(pack2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]), is_f16), is_f16);  // h as the reference stores it
+                const float t0 = tanh_fast(gelu_tanh_arg(f.x)), t1 = tanh_fast(gelu_tanh_arg(f.y));
+                av[i] = pack2(gelu_tanh_value(f.x, t0), gelu_tanh_value(f.y, t1), is_f16);
+                hv[i] = pack2(gelu_tanh_slope(f.x, t0), gelu_tanh_slope(f.y, t1), is_f16);  // kept for the backward pass: the derivative
             }
             stage_store(mo, n0 + c, row_c, 0, hv);
             stage_store(mo2, n0 + c, row_c, 0, av);
         }
     } else if (EPI == EPI_DGRAD_UNARY) {
         // Non-GLU expert, input gradient of the down projection: dh = d * gelu_tanh'(h), d = the accumulator rounded to
-        // the tensor type, h (rows, N) as the forward stored it.
+        // the tensor type; p.h (rows, N) holds gelu_tanh'(h) as the forward epilogue stored it.
         const int n0 = ti.nb * BN;
         const int row_c = ti.row0 + q * 32;
         const uint8_t* hrow = (const uint8_t*)p.h + ((int64_t)(ti.row0 + r) * p.N + n0) * 2;
@@ -536,18 +545,18 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
                 const uint32_t ha[4] = {h4[qd].x, h4[qd].y, h4[qd].z, h4[qd].w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const float2 hh = unpack2(ha[i], is_f16);
+                    const float2 sl = unpack2(ha[i], is_f16);  // gelu_tanh'(h), stored by the forward epilogue
                     const float2 d = unpack2(pack2(__uint_as_float(u[qd * 8 + 2 * i]), __uint_as_float(u[qd * 8 + 2 * i + 1]), is_f16), is_f16);
-                    dv[qd * 4 + i] = pack2(d.x * gelu_tanh_slope(hh.x, tanh_fast(gelu_tanh_arg(hh.x))), d.y * gelu_tanh_slope(hh.y, tanh_fast(gelu_tanh_arg(hh.y))), is_f16);
+                    dv[qd * 4 + i] = pack2(d.x * sl.x, d.y * sl.y, is_f16);
                 }
             }
             stage_store(mo, n0 + c, row_c, 0, dv);
         }
     } else {  // EPI_DGRAD_DOWN, EPI_DGRAD_DOWN_GLU
         // The accumulator holds d[p, :] = (gate-scaled upstream gradient rows) @ w_proj[e]: the gradient with respect to
-        // the activation output.  It is rounded to the tensor type (the reference materialises it) and pushed through the
-        // backward of the gated activation with the pre-activation values of the row, read from the interleaved h.
-        constexpr int ACT = epi_act(EPI);
+        // the activation output.  It is rounded to the tensor type (the reference materialises it) and multiplied by the two
+        // derivative factors the forward epilogue stored (interleaved per 32-column chunk in p.h): d(up) = d * m(gate),
+        // d(gate) = d * up * m'(gate).  The same code serves both gate functions.
         const int I = p.N;
         const int64_t prow = ti.row0 + r;
         const int n0 = ti.nb * BN;
@@ -559,7 +568,7 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
             if (col >= I) break;
             const int wch = min(32, I - col);
             const uint8_t* hp = hrow + (int64_t)col * 4;  // chunk base: element 2 * col
-            // the pre-activation values of this row: requested before the accumulator is read
+            // the stored factors of this row: requested before the accumulator is read
             uint4 hu4[4], hg4[4];
 #pragma unroll
             for (int qd = 0; qd < 4; ++qd) {
@@ -576,11 +585,10 @@ __device__ __forceinline__ void epilogue_tile(const UmmaParams& p, const Tile& t
                 const uint32_t hga[4] = {hg4[qd].x, hg4[qd].y, hg4[qd].z, hg4[qd].w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const float2 up = unpack2(hua[i], is_f16), gt = unpack2(hga[i], is_f16);
+                    const float2 f1 = unpack2(hua[i], is_f16), f2 = unpack2(hga[i], is_f16);  // m(gate) and up * m'(gate)
                     const float2 d = unpack2(pack2(__uint_as_float(u[qd * 8 + 2 * i]), __uint_as_float(u[qd * 8 + 2 * i + 1]), is_f16), is_f16);
-                    const float s0 = sigmoid_fast(gt.x), s1 = sigmoid_fast(gt.y);
-                    du[qd * 4 + i] = pack2(d.x * gate_value(ACT, gt.x, s0), d.y * gate_value(ACT, gt.y, s1), is_f16);
-                    dg[qd * 4 + i] = pack2(d.x * up.x * gate_slope(ACT, gt.x, s0), d.y * up.y * gate_slope(ACT, gt.y, s1), is_f16);
+                    du[qd * 4 + i] = pack2(d.x * f1.x, d.y * f1.y, is_f16);
+                    dg[qd * 4 + i] = pack2(d.x * f2.x, d.y * f2.y, is_f16);
                 }
             }
             stage_store(mo, col, row_c, 0, du);    // up half of dh

@@ -728,8 +728,8 @@ int umma_row_gemm(const RowGemm& g, int dtype, int32_t* status, cudaStream_t str
         if (rc) return rc;
         rc = make_store_map(&mo3, (const uint8_t*)g.out + (int64_t)g.N * 2, 0, g.rows_cap, g.N, 2 * (int64_t)g.N, 0, p.is_f16);
         if (rc) return rc;
-        return g.act == ACT_SIGMOID ? launch_any<EPI_DGRAD_DOWN_GLU>(p, ma, mb, mo, mo2, mo3, g.rows_cap, stream)
-                                    : launch_any<EPI_DGRAD_DOWN>(p, ma, mb, mo, mo2, mo3, g.rows_cap, stream);
+        // one epilogue for both gate functions: the forward epilogue stored the derivative factors, not h
+        return launch_any<EPI_DGRAD_DOWN>(p, ma, mb, mo, mo2, mo3, g.rows_cap, stream);
     }
     if (g.o_map == nullptr && g.scale == nullptr) {
         rc = make_store_map(&mo, g.out, 0, g.rows_cap, g.N, g.ldo, 0, p.is_f16);
