@@ -29,13 +29,17 @@ __device__ __forceinline__ int find_dest(const int32_t* __restrict__ start, int 
     return d;
 }
 
-// Both exchange kernels give a row (push) or a token (pull) to one warp, eight per block, blocks striding over the rows:
-// a lane keeps four 16-byte accesses in flight, which is what a transfer over NVLink needs to approach the link rate.
-constexpr int kEpWarps = 8;
-constexpr int kEpUnroll = 4;
+// Both exchange kernels give a row (push) or a token (pull) to one warp, six per block, blocks striding over the rows:
+// a lane keeps several 16-byte accesses in flight, which is what a transfer over NVLink needs to approach the link rate.
+// They are held to 40 registers per thread in blocks of 192 threads and use no shared memory, so that a block fits on an
+// SM BESIDE a CTA of the persistent GEMM kernels (448 threads x 128 registers leave 8192 registers free; 192 x 40 = 7680):
+// with the layer's tokens split into
+// slices, the transfers of one slice then run while the expert GEMMs of another occupy every SM.
+constexpr int kEpWarps = 6;
+constexpr int kEpUnroll = 2;
 
 template <typename T, int V>
-__global__ void __launch_bounds__(kEpWarps * 32) ep_push_kernel(const T* __restrict__ src, int64_t lds, const int64_t* __restrict__ idx, int fan_out,
+__global__ void __launch_bounds__(kEpWarps * 32, 8) ep_push_kernel(const T* __restrict__ src, int64_t lds, const int64_t* __restrict__ idx, int fan_out,
                                                                const T* __restrict__ coeff, PeerTable peers, const int32_t* __restrict__ start,
                                                                const int32_t* __restrict__ base, int R, int64_t M, int width, int64_t cap_rows,
                                                                int32_t* status) {
@@ -72,7 +76,7 @@ __global__ void __launch_bounds__(kEpWarps * 32) ep_push_kernel(const T* __restr
 }
 
 template <typename T, int V>
-__global__ void __launch_bounds__(kEpWarps * 32) ep_pull_combine_kernel(PeerTable peers, const int64_t* __restrict__ inv, const int32_t* __restrict__ start,
+__global__ void __launch_bounds__(kEpWarps * 32, 8) ep_pull_combine_kernel(PeerTable peers, const int64_t* __restrict__ inv, const int32_t* __restrict__ start,
                                                                        const int32_t* __restrict__ base, int R, const T* __restrict__ gates,
                                                                        T* __restrict__ out, int64_t ldo, T* __restrict__ expanded, int64_t Tn, int k,
                                                                        int width) {

@@ -404,12 +404,14 @@ class _PeerCombine(torch.autograd.Function):
         return xc.bufs["dy"][: plan.m_recv], d_gates, None, None, None
 
 
-def ep_experts_p2p(x, router_weights, selected_experts, num_experts: int, local_experts_fn: Callable, xc, ops=CudaRowOps):
+def ep_experts_p2p(x, router_weights, selected_experts, num_experts: int, local_experts_fn: Callable, xc, ops=CudaRowOps, plan=None):
     """Routed experts over an expert-parallel group with the row exchange done by this package's kernels on peer
-    memory (see PeerExchange).  Same contract as `ep_experts`.  `x.requires_grad` must agree across the ranks."""
+    memory (see PeerExchange).  Same contract as `ep_experts`.  `x.requires_grad` must agree across the ranks.
+    `plan`: a placement plan made beforehand with `_make_plan` for exactly these `selected_experts`."""
     world, rank = xc.world, dist.get_rank(xc.group)
-    with torch.no_grad(), _phase("ep_plan"):
-        plan = _make_plan(selected_experts, num_experts, world, rank, xc.group, ops, getattr(xc, "host_rows", None))
+    if plan is None:
+        with torch.no_grad(), _phase("ep_plan"):
+            plan = _make_plan(selected_experts, num_experts, world, rank, xc.group, ops, getattr(xc, "host_rows", None))
     global _last_plan, last_received_rows
     _last_plan = plan
     if getattr(xc, "sync_free", False):
@@ -585,17 +587,21 @@ class MoE_B200_EP(nn.Module):
         bounds = [T * i // self.micro_batches for i in range(self.micro_batches + 1)]
         outs, received = [], 0
         sync_free_mode = self._pipe[0][0].sync_free
-        plans = []
         global last_received_rows
+        # The placement plans of all slices come first, on the calling stream: their small kernels (sort, count all-gather)
+        # do not fit on an SM beside a GEMM CTA and would otherwise wait behind the previous slice's expert kernels.
+        plans = []
+        with torch.no_grad(), _phase("ep_plan"):
+            for i, (xc, _) in enumerate(self._pipe):
+                plans.append(_make_plan(selected_experts[bounds[i] : bounds[i + 1]], self.num_experts, self.world, self.rank, xc.group, self.ops, xc.host_rows))
         for i, (xc, stream) in enumerate(self._pipe):
             lo, hi = bounds[i], bounds[i + 1]
             stream.wait_stream(main)
             with torch.cuda.stream(stream):
                 y_i = ep_experts_p2p(hidden_states[lo:hi], router_weights[lo:hi], selected_experts[lo:hi], self.num_experts,
-                                     lambda rows, ids, xc=xc: self.local_experts(rows, ids, xc), xc, self.ops)
+                                     lambda rows, ids, xc=xc: self.local_experts(rows, ids, xc), xc, self.ops, plan=plans[i])
             y_i.record_stream(main)
             outs.append(y_i)
-            plans.append(_last_plan)
             received += received_rows_of_last_pass() if not sync_free_mode else 0
         for _, stream in self._pipe:
             main.wait_stream(stream)
