@@ -712,6 +712,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(synthetic.WORKLOADS))
     ap.add_argument("--tokens", type=int, default=None, help="override tokens per GPU (profiling on a small case)")
+    ap.add_argument("--experts", type=int, default=None, help="override the number of experts (e.g. the per-GPU expert count of a larger job on fewer GPUs)")
     ap.add_argument("--cpu-sample-tokens", type=int, default=1024, help="tokens of the workload the CPU arm times (1/16 of the Mixtral-shaped batch by default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ep-exchange", default="p2p", choices=["p2p", "nccl"], help="N > 1: row exchange by this package's kernels over peer memory, or NCCL all-to-all")
@@ -729,6 +730,8 @@ def main():
     ap.add_argument("--profile", action="store_true", help="profiling run under ncu: exactly --warmup warm-up steps, no end-to-end and CPU legs; its numbers are not benchmark values")
     args = ap.parse_args()
     w = synthetic.WORKLOADS[args.workload]
+    if args.experts:
+        w = synthetic.scaled(w, num_experts=args.experts)
     if args.tokens:
         w = synthetic.scaled(w, tokens=args.tokens)
     elif w.name == "c5":

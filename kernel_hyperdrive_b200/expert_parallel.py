@@ -247,10 +247,30 @@ class PeerExchange:
             )
 
 
+class _Chain:
+    """Orders the dispatches of the slices of one pipelined pass: a slice starts sending only when the slice before it has
+    finished its own dispatch (and so has begun its expert GEMMs), so that every transfer but the first runs beside GEMMs
+    instead of beside the other slices' transfers."""
+
+    def __init__(self):
+        self.fwd_event = None
+        self.bwd_event = None
+
+    def wait(self, which: str) -> None:
+        ev = getattr(self, which)
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+
+    def mark(self, which: str) -> None:
+        ev = torch.cuda.Event()
+        ev.record()
+        setattr(self, which, ev)
+
+
 class _Plan:
     """Where this rank's sorted rows go: computed once per pass from the all-gathered expert counts."""
 
-    __slots__ = ("ss", "inv", "start", "base", "m_recv", "max_recv", "local_ids", "k", "_recv_counts", "_host", "_event", "_e_local", "_world")
+    __slots__ = ("ss", "inv", "start", "base", "m_recv", "max_recv", "local_ids", "k", "_recv_counts", "_host", "_event", "_e_local", "_world", "chain")
 
     def local_ids_for_capacity(self, cap_rows: int) -> torch.Tensor:
         """Local expert of every row of a receive buffer of `cap_rows` rows, -1 for the rows past the received ones,
@@ -290,6 +310,7 @@ def _make_plan(selected_experts, num_experts: int, world: int, rank: int, group,
     T, k = selected_experts.shape
     e_local = num_experts // world
     plan = _Plan()
+    plan.chain = None
     plan.k = k
     ss, counts = ops.route(selected_experts.reshape(-1), num_experts, k)
     plan.ss = ss
@@ -343,8 +364,12 @@ class _PeerDispatch(torch.autograd.Function):
         if xc.backward_reads_pending:
             xc.barrier()
         xc.backward_reads_pending = torch.is_grad_enabled()
+        if plan.chain is not None:
+            plan.chain.wait("fwd_event")
         xc.push("x", x.contiguous(), plan.ss, plan.k, None, plan)
         xc.barrier()  # all rows have landed
+        if plan.chain is not None:
+            plan.chain.mark("fwd_event")
         if getattr(xc, "sync_free", False):
             # No host read: the local tensors are sized by the buffer capacity and the rows past the received ones carry
             # no expert.  A buffer that is too small shows up as status word 301 (rows skipped), not as an exception.
@@ -399,8 +424,12 @@ class _PeerCombine(torch.autograd.Function):
         grad_y = grad_y.contiguous()
         with _phase("ep_gate_grad"):
             d_gates = _gate_grad_via(ctx.ops, expanded, grad_y, k).to(gates.dtype)
+        if plan.chain is not None:
+            plan.chain.wait("bwd_event")
         xc.push("dy", grad_y, plan.ss, k, gates.reshape(-1), plan)
         xc.barrier()  # all gradient rows have landed
+        if plan.chain is not None:
+            plan.chain.mark("bwd_event")
         return xc.bufs["dy"][: plan.m_recv], d_gates, None, None, None
 
 
@@ -590,10 +619,11 @@ class MoE_B200_EP(nn.Module):
         global last_received_rows
         # The placement plans of all slices come first, on the calling stream: their small kernels (sort, count all-gather)
         # do not fit on an SM beside a GEMM CTA and would otherwise wait behind the previous slice's expert kernels.
-        plans = []
+        plans, chain = [], _Chain()
         with torch.no_grad(), _phase("ep_plan"):
             for i, (xc, _) in enumerate(self._pipe):
                 plans.append(_make_plan(selected_experts[bounds[i] : bounds[i + 1]], self.num_experts, self.world, self.rank, xc.group, self.ops, xc.host_rows))
+                plans[-1].chain = chain
         for i, (xc, stream) in enumerate(self._pipe):
             lo, hi = bounds[i], bounds[i + 1]
             stream.wait_stream(main)
