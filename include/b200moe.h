@@ -337,6 +337,28 @@ int b200moe_ep_pull_combine(const void* const* peer_ptrs, const int64_t* inv, co
                             const int32_t* base, int R, const void* gates, void* out, int64_t ldo, void* expanded,
                             int64_t T, int k, int width, int dtype, b200moe_stream_t stream);
 
+/* The same two transfers with the destination row of every routed row given explicitly: dest_pos (device int32, M
+ * entries, indexed like start's rows) is the row of the owning rank's buffer.  With dest_pos = the row's position in the
+ * RECEIVER's padded grouped order (every rank can compute it from the all-gathered expert counts), dispatched rows land
+ * where the receiver's expert GEMMs read them and results are fetched from where its GEMM epilogues stored them: the
+ * receiver runs no sort and no gather pass of its own.  base may be NULL when dest_pos is given.  cap_rows (> 0): rows of a
+ * peer buffer; a row whose place lies beyond it was never stored by the dispatch (status 301) and is read as zeros.
+ * max_blocks (> 0) caps the grid of the transfer: at one block per SM (the kernels use 192 threads x 40 registers and no
+ * shared memory) a transfer launched beside persistent GEMM kernels leaves room for their CTAs on every SM. */
+int b200moe_ep_push_rows_at(const void* src, int64_t lds, const int64_t* idx, int fan_out, const void* coeff,
+                            const void* const* peer_ptrs, const int32_t* start, const int32_t* base, const int32_t* dest_pos,
+                            int R, int64_t M, int width, int64_t cap_rows, int max_blocks, int dtype, int32_t* status,
+                            b200moe_stream_t stream);
+int b200moe_ep_pull_combine_at(const void* const* peer_ptrs, const int64_t* inv, const int32_t* start, const int32_t* base,
+                               const int32_t* dest_pos, int R, int64_t cap_rows, int max_blocks, const void* gates, void* out,
+                               int64_t ldo, void* expanded, int64_t T, int k, int width, int dtype, b200moe_stream_t stream);
+
+/* Clears the rows of a padded grouped buffer that belong to no routed row (between the end of an expert's rows and the
+ * next multiple of 128): needed where the rows were written by other ranks, which only send real rows.
+ * expert_offsets: device int64 (E), inclusive. */
+int b200moe_zero_filler_rows(void* buf, int64_t ld, const int64_t* expert_offsets, int E, int width, int64_t cap_rows, int dtype,
+                             b200moe_stream_t stream);
+
 /* Rank barrier on the stream, over a symmetric flag array: flag_ptrs is a HOST array of R device pointers, entry d being
  * rank d's array of R int32 words (zero before the first barrier), mapped into this process.  `epoch` is the number of
  * this barrier (1, 2, 3, ... the same on every rank).  The kernel publishes the epoch to every peer and waits, for at most

@@ -41,13 +41,15 @@ constexpr int kEpUnroll = 2;
 template <typename T, int V>
 __global__ void __launch_bounds__(kEpWarps * 32, 8) ep_push_kernel(const T* __restrict__ src, int64_t lds, const int64_t* __restrict__ idx, int fan_out,
                                                                const T* __restrict__ coeff, PeerTable peers, const int32_t* __restrict__ start,
-                                                               const int32_t* __restrict__ base, int R, int64_t M, int width, int64_t cap_rows,
-                                                               int32_t* status) {
+                                                               const int32_t* __restrict__ base, const int32_t* __restrict__ dest_pos, int R,
+                                                               int64_t M, int width, int64_t cap_rows, int32_t* status) {
     const int lane = threadIdx.x & 31;
     const int step = 32 * V;
     for (int64_t n = (int64_t)blockIdx.x * kEpWarps + (threadIdx.x >> 5); n < M; n += (int64_t)gridDim.x * kEpWarps) {
         const int d = find_dest(start, R, (int)n);
-        const int64_t pos = (int64_t)base[d] + (n - start[d]);
+        // the row of the destination buffer: given explicitly (rows land in the receiver's padded grouped order), or the
+        // rows of source rank r follow those of ranks 0..r-1 in the order they are sent
+        const int64_t pos = dest_pos ? (int64_t)dest_pos[n] : (int64_t)base[d] + (n - start[d]);
         if (pos < 0 || pos >= cap_rows) {  // would overrun the peer's buffer: record and skip
             if (lane == 0 && status) atomicCAS(status, 0, 301);
             continue;
@@ -77,7 +79,8 @@ __global__ void __launch_bounds__(kEpWarps * 32, 8) ep_push_kernel(const T* __re
 
 template <typename T, int V>
 __global__ void __launch_bounds__(kEpWarps * 32, 8) ep_pull_combine_kernel(PeerTable peers, const int64_t* __restrict__ inv, const int32_t* __restrict__ start,
-                                                                       const int32_t* __restrict__ base, int R, const T* __restrict__ gates,
+                                                                       const int32_t* __restrict__ base, const int32_t* __restrict__ dest_pos, int R,
+                                                                       int64_t cap_rows, const T* __restrict__ gates,
                                                                        T* __restrict__ out, int64_t ldo, T* __restrict__ expanded, int64_t Tn, int k,
                                                                        int width) {
     const int lane = threadIdx.x & 31;
@@ -88,7 +91,9 @@ __global__ void __launch_bounds__(kEpWarps * 32, 8) ep_pull_combine_kernel(PeerT
         if (lane < k) {
             const int64_t n = inv[t * k + lane];
             const int d = find_dest(start, R, (int)n);
-            my_row = (const T*)peers.ptr[d] + ((int64_t)base[d] + (n - start[d])) * (int64_t)width;
+            const int64_t pos = dest_pos ? (int64_t)dest_pos[n] : (int64_t)base[d] + (n - start[d]);
+            // a row that did not fit into the owner's buffer was never stored (the dispatch recorded status 301): it reads as zeros
+            if (pos >= 0 && (cap_rows <= 0 || pos < cap_rows)) my_row = (const T*)peers.ptr[d] + pos * (int64_t)width;
             if (gates) my_gate = Elem<T>::to_f(gates[t * k + lane]);
         }
         // every lane runs every sweep (the shuffles need the whole warp); a lane past the row's end only skips its accesses
@@ -103,7 +108,13 @@ __global__ void __launch_bounds__(kEpWarps * 32, 8) ep_pull_combine_kernel(PeerT
                 const T* row = (const T*)__shfl_sync(0xffffffffu, (unsigned long long)my_row, j);
                 const float g = __shfl_sync(0xffffffffu, my_gate, j);
                 if (!in) continue;
-                Pack<T, V> p = *reinterpret_cast<const Pack<T, V>*>(row + col);
+                Pack<T, V> p;
+                if (row != nullptr) {
+                    p = *reinterpret_cast<const Pack<T, V>*>(row + col);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < V; ++i) p.v[i] = Elem<T>::from_f(0.f);
+                }
 #pragma unroll
                 for (int i = 0; i < V; ++i) acc[i] += g * Elem<T>::to_f(p.v[i]);
                 if (expanded) *reinterpret_cast<Pack<T, V>*>(expanded + (t * k + j) * (int64_t)width + col) = p;
@@ -173,6 +184,30 @@ __global__ void ep_barrier_kernel(PeerTable flags, int rank, int R, int epoch, l
     }
 }
 
+// Rows of a padded grouped buffer that belong to no routed row: expert e owns rows [seg(e), seg(e) + count(e)) with
+// seg(e) = 128 * sum_{e' < e} ceil(count(e') / 128); the rows from seg(e) + count(e) up to the next multiple of 128 are
+// cleared (the weight-gradient GEMMs reduce over whole 64-row steps and must read zeros there).  One block per expert.
+template <typename T, int V>
+__global__ void zero_filler_rows_kernel(T* __restrict__ buf, int64_t ld, const int64_t* __restrict__ offsets, int E, int width, int64_t cap_rows) {
+    const int e = blockIdx.x;
+    if (e >= E) return;
+    int64_t seg = 0;
+    for (int i = 0; i < e; ++i) {
+        const int64_t c = offsets[i] - (i ? offsets[i - 1] : 0);
+        seg += (c + kPadRows - 1) / kPadRows * kPadRows;
+    }
+    const int64_t cnt = offsets[e] - (e ? offsets[e - 1] : 0);
+    const int64_t first = seg + cnt, last = seg + (cnt + kPadRows - 1) / kPadRows * kPadRows;
+    Pack<T, V> z;
+#pragma unroll
+    for (int i = 0; i < V; ++i) z.v[i] = Elem<T>::from_f(0.f);
+    const int per_row = width / V;
+    for (int64_t i = threadIdx.x; i < (last - first) * per_row; i += blockDim.x) {
+        const int64_t r = first + i / per_row;
+        if (r < cap_rows) *reinterpret_cast<Pack<T, V>*>(buf + r * ld + (i % per_row) * V) = z;
+    }
+}
+
 int fill_peers(PeerTable& tab, const void* const* peer_ptrs, int R, const char* what) {
     B200MOE_REQUIRE(R >= 1 && R <= kMaxRanks && peer_ptrs, B200MOE_ERR_ARG, "%s: bad rank count or NULL peer table", what);
     for (int i = 0; i < R; ++i) {
@@ -183,9 +218,12 @@ int fill_peers(PeerTable& tab, const void* const* peer_ptrs, int R, const char* 
     return B200MOE_OK;
 }
 
-unsigned ep_grid(int64_t rows) {
+// `max_blocks` > 0 caps the grid: with one block per SM at most, a transfer that runs beside the persistent GEMM kernels of
+// another slice never takes the registers a GEMM CTA needs to become resident (blocks stride over the rows, so a block
+// that got an SM keeps it until the whole transfer is done).
+unsigned ep_grid(int64_t rows, int max_blocks = 0) {
     int64_t blocks = (rows + kEpWarps - 1) / kEpWarps;
-    const int64_t cap = 148 * 16;
+    const int64_t cap = max_blocks > 0 ? max_blocks : 148 * 16;
     return (unsigned)(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
 }
 
@@ -203,10 +241,17 @@ extern "C" int b200moe_ep_push_rows(const void* src, int64_t lds, const int64_t*
                                     const void* const* peer_ptrs, const int32_t* start, const int32_t* base, int R,
                                     int64_t M, int width, int64_t cap_rows, int dtype, int32_t* status,
                                     b200moe_stream_t stream_) {
+    return b200moe_ep_push_rows_at(src, lds, idx, fan_out, coeff, peer_ptrs, start, base, nullptr, R, M, width, cap_rows, 0, dtype, status, stream_);
+}
+
+extern "C" int b200moe_ep_push_rows_at(const void* src, int64_t lds, const int64_t* idx, int fan_out, const void* coeff,
+                                       const void* const* peer_ptrs, const int32_t* start, const int32_t* base,
+                                       const int32_t* dest_pos, int R, int64_t M, int width, int64_t cap_rows, int max_blocks,
+                                       int dtype, int32_t* status, b200moe_stream_t stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     B200MOE_REQUIRE(M >= 0 && width > 0 && fan_out > 0 && cap_rows >= 0, B200MOE_ERR_ARG, "ep_push_rows: bad sizes");
     if (M == 0) return B200MOE_OK;
-    B200MOE_REQUIRE(src && start && base, B200MOE_ERR_ARG, "ep_push_rows: NULL pointer");
+    B200MOE_REQUIRE(src && start && (base || dest_pos), B200MOE_ERR_ARG, "ep_push_rows: NULL pointer");
     PeerTable tab{};
     int rc = fill_peers(tab, peer_ptrs, R, "ep_push_rows");
     if (rc) return rc;
@@ -215,15 +260,15 @@ extern "C" int b200moe_ep_push_rows(const void* src, int64_t lds, const int64_t*
     B200MOE_REQUIRE(width % V == 0 && lds % V == 0 && ((uintptr_t)src & 15) == 0, B200MOE_ERR_LAYOUT,
                     "ep_push_rows: rows must be 16-byte aligned and a multiple of 16 bytes wide");
     if (dtype == B200MOE_F32) {
-        ep_push_kernel<float, 4><<<ep_grid(M), kEpWarps * 32, 0, stream>>>((const float*)src, lds, idx, fan_out, (const float*)coeff, tab,
-                                                                   start, base, R, M, width, cap_rows, status);
+        ep_push_kernel<float, 4><<<ep_grid(M, max_blocks), kEpWarps * 32, 0, stream>>>((const float*)src, lds, idx, fan_out, (const float*)coeff, tab,
+                                                                   start, base, dest_pos, R, M, width, cap_rows, status);
     } else if (dtype == B200MOE_BF16) {
-        ep_push_kernel<__nv_bfloat16, 8><<<ep_grid(M), kEpWarps * 32, 0, stream>>>((const __nv_bfloat16*)src, lds, idx, fan_out,
-                                                                           (const __nv_bfloat16*)coeff, tab, start, base, R, M,
+        ep_push_kernel<__nv_bfloat16, 8><<<ep_grid(M, max_blocks), kEpWarps * 32, 0, stream>>>((const __nv_bfloat16*)src, lds, idx, fan_out,
+                                                                           (const __nv_bfloat16*)coeff, tab, start, base, dest_pos, R, M,
                                                                            width, cap_rows, status);
     } else {
-        ep_push_kernel<__half, 8><<<ep_grid(M), kEpWarps * 32, 0, stream>>>((const __half*)src, lds, idx, fan_out, (const __half*)coeff,
-                                                                    tab, start, base, R, M, width, cap_rows, status);
+        ep_push_kernel<__half, 8><<<ep_grid(M, max_blocks), kEpWarps * 32, 0, stream>>>((const __half*)src, lds, idx, fan_out, (const __half*)coeff,
+                                                                    tab, start, base, dest_pos, R, M, width, cap_rows, status);
     }
     count_launch();
     return check_launch("ep_push_rows");
@@ -233,10 +278,17 @@ extern "C" int b200moe_ep_pull_combine(const void* const* peer_ptrs, const int64
                                        const int32_t* base, int R, const void* gates, void* out, int64_t ldo,
                                        void* expanded, int64_t T_, int k, int width, int dtype,
                                        b200moe_stream_t stream_) {
+    return b200moe_ep_pull_combine_at(peer_ptrs, inv, start, base, nullptr, R, 0, 0, gates, out, ldo, expanded, T_, k, width, dtype, stream_);
+}
+
+extern "C" int b200moe_ep_pull_combine_at(const void* const* peer_ptrs, const int64_t* inv, const int32_t* start,
+                                          const int32_t* base, const int32_t* dest_pos, int R, int64_t cap_rows, int max_blocks,
+                                          const void* gates, void* out, int64_t ldo, void* expanded, int64_t T_, int k, int width,
+                                          int dtype, b200moe_stream_t stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     B200MOE_REQUIRE(T_ >= 0 && width > 0 && k > 0 && k <= 32, B200MOE_ERR_ARG, "ep_pull_combine: bad sizes (k <= 32)");
     if (T_ == 0) return B200MOE_OK;
-    B200MOE_REQUIRE(inv && start && base && out, B200MOE_ERR_ARG, "ep_pull_combine: NULL pointer");
+    B200MOE_REQUIRE(inv && start && (base || dest_pos) && out, B200MOE_ERR_ARG, "ep_pull_combine: NULL pointer");
     PeerTable tab{};
     int rc = fill_peers(tab, peer_ptrs, R, "ep_pull_combine");
     if (rc) return rc;
@@ -245,13 +297,13 @@ extern "C" int b200moe_ep_pull_combine(const void* const* peer_ptrs, const int64
     B200MOE_REQUIRE(width % V == 0 && ldo % V == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)expanded & 15) == 0,
                     B200MOE_ERR_LAYOUT, "ep_pull_combine: rows must be 16-byte aligned and a multiple of 16 bytes wide");
     if (dtype == B200MOE_F32) {
-        ep_pull_combine_kernel<float, 4><<<ep_grid(T_), kEpWarps * 32, 0, stream>>>(tab, inv, start, base, R, (const float*)gates, (float*)out,
+        ep_pull_combine_kernel<float, 4><<<ep_grid(T_, max_blocks), kEpWarps * 32, 0, stream>>>(tab, inv, start, base, dest_pos, R, cap_rows, (const float*)gates, (float*)out,
                                                                             ldo, (float*)expanded, T_, k, width);
     } else if (dtype == B200MOE_BF16) {
-        ep_pull_combine_kernel<__nv_bfloat16, 8><<<ep_grid(T_), kEpWarps * 32, 0, stream>>>(
-            tab, inv, start, base, R, (const __nv_bfloat16*)gates, (__nv_bfloat16*)out, ldo, (__nv_bfloat16*)expanded, T_, k, width);
+        ep_pull_combine_kernel<__nv_bfloat16, 8><<<ep_grid(T_, max_blocks), kEpWarps * 32, 0, stream>>>(
+            tab, inv, start, base, dest_pos, R, cap_rows, (const __nv_bfloat16*)gates, (__nv_bfloat16*)out, ldo, (__nv_bfloat16*)expanded, T_, k, width);
     } else {
-        ep_pull_combine_kernel<__half, 8><<<ep_grid(T_), kEpWarps * 32, 0, stream>>>(tab, inv, start, base, R, (const __half*)gates,
+        ep_pull_combine_kernel<__half, 8><<<ep_grid(T_, max_blocks), kEpWarps * 32, 0, stream>>>(tab, inv, start, base, dest_pos, R, cap_rows, (const __half*)gates,
                                                                              (__half*)out, ldo, (__half*)expanded, T_, k, width);
     }
     count_launch();
@@ -291,4 +343,24 @@ extern "C" int b200moe_ep_barrier(const void* const* flag_ptrs, int rank, int R,
     ep_barrier_kernel<<<1, 64, 0, stream>>>(tab, rank, R, epoch, (long long)limit_cycles, status);
     count_launch();
     return check_launch("ep_barrier");
+}
+
+extern "C" int b200moe_zero_filler_rows(void* buf, int64_t ld, const int64_t* expert_offsets, int E, int width, int64_t cap_rows, int dtype,
+                                        b200moe_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    B200MOE_REQUIRE(E > 0 && E <= kMaxExperts && width > 0 && cap_rows >= 0, B200MOE_ERR_ARG, "zero_filler_rows: bad sizes");
+    B200MOE_REQUIRE(buf && expert_offsets, B200MOE_ERR_ARG, "zero_filler_rows: NULL pointer");
+    B200MOE_REQUIRE(dtype == B200MOE_BF16 || dtype == B200MOE_F16 || dtype == B200MOE_F32, B200MOE_ERR_DTYPE, "zero_filler_rows: dtype");
+    int esz = dtype == B200MOE_F32 ? 4 : 2, V = 16 / esz;
+    B200MOE_REQUIRE(width % V == 0 && ld % V == 0 && ((uintptr_t)buf & 15) == 0, B200MOE_ERR_LAYOUT,
+                    "zero_filler_rows: rows must be 16-byte aligned and a multiple of 16 bytes wide");
+    if (dtype == B200MOE_F32) {
+        zero_filler_rows_kernel<float, 4><<<E, 256, 0, stream>>>((float*)buf, ld, expert_offsets, E, width, cap_rows);
+    } else if (dtype == B200MOE_BF16) {
+        zero_filler_rows_kernel<__nv_bfloat16, 8><<<E, 256, 0, stream>>>((__nv_bfloat16*)buf, ld, expert_offsets, E, width, cap_rows);
+    } else {
+        zero_filler_rows_kernel<__half, 8><<<E, 256, 0, stream>>>((__half*)buf, ld, expert_offsets, E, width, cap_rows);
+    }
+    count_launch();
+    return check_launch("zero_filler_rows");
 }

@@ -217,6 +217,8 @@ class PeerExchange:
         dist.barrier(group)  # every rank's flags are zero before anyone publishes an epoch
         self.backward_reads_pending = False
         self.sync_free = False  # True: no host read per pass (see _PeerDispatch.forward)
+        self.direct = False     # True: rows are exchanged in the receiver's padded grouped order (see ep_experts_p2p)
+        self.max_blocks = 0     # > 0: cap on the grid of the transfer kernels (one block per SM when they run beside GEMMs)
         self.host_rows = torch.empty(2, dtype=torch.int64).pin_memory()  # landing place of the per-pass host read
 
     def barrier(self) -> None:
@@ -231,18 +233,27 @@ class PeerExchange:
 
         with _phase("ep_push_" + name):
             check(
-                lib().b200moe_ep_push_rows(ptr(src), src.stride(0), ptr(idx), fan_out, ptr(coeff), self.peer_ptrs[name], ptr(plan.start), ptr(plan.base),
-                                           self.world, plan.ss.numel(), src.size(1), self.cap_rows, dtype_code(src), ptr(status_word(src.device)), stream_ptr(src.device)),
+                lib().b200moe_ep_push_rows_at(ptr(src), src.stride(0), ptr(idx), fan_out, ptr(coeff), self.peer_ptrs[name], ptr(plan.start), ptr(plan.base),
+                                              ptr(plan.dest_pos), self.world, plan.ss.numel(), src.size(1), self.cap_rows, self.max_blocks, dtype_code(src),
+                                              ptr(status_word(src.device)), stream_ptr(src.device)),
                 "ep_push_rows",
             )
+
+    def zero_fillers(self, name: str, plan: "_Plan") -> None:
+        """Clears the filler rows of this rank's own buffer (peers only store real rows)."""
+        from ._lib import check, dtype_code, lib, ptr, stream_ptr
+
+        buf = self.bufs[name]
+        check(lib().b200moe_zero_filler_rows(ptr(buf), buf.stride(0), ptr(plan.local_offsets), plan.local_offsets.numel(), buf.size(1), buf.size(0), dtype_code(buf),
+                                             stream_ptr(buf.device)), "zero_filler_rows")
 
     def pull(self, name: str, gates, out, expanded, plan: "_Plan") -> None:
         from ._lib import check, dtype_code, lib, ptr, stream_ptr
 
         with _phase("ep_pull_" + name):
             check(
-                lib().b200moe_ep_pull_combine(self.peer_ptrs[name], ptr(plan.inv), ptr(plan.start), ptr(plan.base), self.world, ptr(gates), ptr(out), out.stride(0),
-                                              ptr(expanded), out.size(0), plan.k, out.size(1), dtype_code(out), stream_ptr(out.device)),
+                lib().b200moe_ep_pull_combine_at(self.peer_ptrs[name], ptr(plan.inv), ptr(plan.start), ptr(plan.base), ptr(plan.dest_pos), self.world, self.cap_rows, self.max_blocks, ptr(gates),
+                                                 ptr(out), out.stride(0), ptr(expanded), out.size(0), plan.k, out.size(1), dtype_code(out), stream_ptr(out.device)),
                 "ep_pull_combine",
             )
 
@@ -270,7 +281,7 @@ class _Chain:
 class _Plan:
     """Where this rank's sorted rows go: computed once per pass from the all-gathered expert counts."""
 
-    __slots__ = ("ss", "inv", "start", "base", "m_recv", "max_recv", "local_ids", "k", "_recv_counts", "_host", "_event", "_e_local", "_world", "chain")
+    __slots__ = ("ss", "inv", "start", "base", "m_recv", "max_recv", "local_ids", "k", "_recv_counts", "_host", "_event", "_e_local", "_world", "chain", "dest_pos", "local_offsets")
 
     def local_ids_for_capacity(self, cap_rows: int) -> torch.Tensor:
         """Local expert of every row of a receive buffer of `cap_rows` rows, -1 for the rows past the received ones,
@@ -306,11 +317,15 @@ class _Plan:
         )
 
 
-def _make_plan(selected_experts, num_experts: int, world: int, rank: int, group, ops, host_rows=None) -> "_Plan":
+def _make_plan(selected_experts, num_experts: int, world: int, rank: int, group, ops, host_rows=None, direct: bool = False) -> "_Plan":
+    """`direct`: also compute, for every sorted row, its row in the RECEIVER's padded grouped order (`dest_pos`) and this
+    rank's own inclusive expert offsets over everything it receives (`local_offsets`), so that rows can be stored where
+    the receiver's expert GEMMs read them."""
     T, k = selected_experts.shape
     e_local = num_experts // world
     plan = _Plan()
     plan.chain = None
+    plan.dest_pos = plan.local_offsets = None
     plan.k = k
     ss, counts = ops.route(selected_experts.reshape(-1), num_experts, k)
     plan.ss = ss
@@ -327,7 +342,21 @@ def _make_plan(selected_experts, num_experts: int, world: int, rank: int, group,
     plan._recv_counts, plan._e_local, plan._world = recv_counts, e_local, world
     plan.m_recv, plan.max_recv, plan.local_ids = None, None, None
     received = to_rank.sum(0).to(torch.int64)  # rows every rank receives: identical on all ranks
-    summary = torch.stack([received[rank], received.max()])
+    if direct:
+        ca = counts_all.long()
+        total = ca.sum(0)                                              # rows of every expert over all sources
+        padded = (total + 127) // 128 * 128                            # its segment in the owner's padded grouped order
+        pv = padded.view(world, e_local)
+        pad_start = (pv.cumsum(1) - pv).reshape(-1)                    # first row of the segment in the owner's buffers
+        before = (ca.cumsum(0) - ca)[rank]                             # rows of lower-ranked sources inside the segment
+        own = counts.long()
+        excl = own.cumsum(0) - own                                     # first sorted row of every expert on this rank
+        se = torch.repeat_interleave(torch.arange(num_experts, device=ss.device), own, output_size=ss.numel())
+        plan.dest_pos = (pad_start[se] + before[se] + (torch.arange(ss.numel(), device=ss.device) - excl[se])).to(torch.int32)
+        plan.local_offsets = total[rank * e_local : (rank + 1) * e_local].cumsum(0)
+        summary = torch.stack([received[rank], pv.sum(1).max()])       # real rows here; most padded rows any rank's buffers must hold
+    else:
+        summary = torch.stack([received[rank], received.max()])
     if ss.is_cuda:
         plan._host = host_rows if host_rows is not None else torch.empty(2, dtype=torch.int64).pin_memory()
         plan._host.copy_(summary, non_blocking=True)
@@ -370,6 +399,11 @@ class _PeerDispatch(torch.autograd.Function):
         xc.barrier()  # all rows have landed
         if plan.chain is not None:
             plan.chain.mark("fwd_event")
+        if plan.dest_pos is not None:
+            # rows sit in this rank's padded grouped order already; only the filler rows need clearing
+            xc.zero_fillers("x", plan)
+            plan.m_recv = xc.cap_rows
+            return xc.bufs["x"]
         if getattr(xc, "sync_free", False):
             # No host read: the local tensors are sized by the buffer capacity and the rows past the received ones carry
             # no expert.  A buffer that is too small shows up as status word 301 (rows skipped), not as an exception.
@@ -430,6 +464,8 @@ class _PeerCombine(torch.autograd.Function):
         xc.barrier()  # all gradient rows have landed
         if plan.chain is not None:
             plan.chain.mark("bwd_event")
+        if plan.dest_pos is not None:
+            xc.zero_fillers("dy", plan)
         return xc.bufs["dy"][: plan.m_recv], d_gates, None, None, None
 
 
@@ -438,14 +474,27 @@ def ep_experts_p2p(x, router_weights, selected_experts, num_experts: int, local_
     memory (see PeerExchange).  Same contract as `ep_experts`.  `x.requires_grad` must agree across the ranks.
     `plan`: a placement plan made beforehand with `_make_plan` for exactly these `selected_experts`."""
     world, rank = xc.world, dist.get_rank(xc.group)
+    direct = getattr(xc, "direct", False)
     if plan is None:
         with torch.no_grad(), _phase("ep_plan"):
-            plan = _make_plan(selected_experts, num_experts, world, rank, xc.group, ops, getattr(xc, "host_rows", None))
+            plan = _make_plan(selected_experts, num_experts, world, rank, xc.group, ops, getattr(xc, "host_rows", None), direct)
     global _last_plan, last_received_rows
     _last_plan = plan
-    if getattr(xc, "sync_free", False):
+    if getattr(xc, "sync_free", False) or direct:
         last_received_rows = None
     recv = _PeerDispatch.apply(x, xc, plan)
+    if direct:
+        # Rows were stored straight into this rank's padded grouped order: the local layer needs only the expert offsets.
+        # The one host read of the pass (largest padded row count of the group, for the collective overflow refusal) comes
+        # after everything is queued: its copy was queued with the plan, so it has long finished.
+        out_rows = local_experts_fn(recv, plan.local_offsets)
+        y = _PeerCombine.apply(out_rows, router_weights.to(x.dtype), xc, plan, ops)
+        if plan._event is not None:
+            plan._event.synchronize()
+        plan.max_recv = int(plan._host[1].item())
+        if plan.max_recv > xc.cap_rows:
+            raise RuntimeError(f"expert-parallel exchange buffer too small: a rank needs {plan.max_recv} padded rows, capacity {xc.cap_rows}")
+        return y
     out_rows = local_experts_fn(recv, plan.local_ids)
     return _PeerCombine.apply(out_rows, router_weights.to(x.dtype), xc, plan, ops)
 
@@ -499,7 +548,7 @@ class MoE_B200_EP(nn.Module):
     def __init__(self, num_experts, num_experts_per_tok, hidden_size, intermediate_size, activation_function, is_glu, add_bias, std,
                  group=None, device=None, dtype=torch.float32, seed: int = 0, ops=CudaRowOps, local_experts_fn=None,
                  num_shared_experts: int = 0, shared_intermediate_size: int | None = None, router_scoring: str = "softmax",
-                 exchange: str = "nccl", exchange_rows: int | None = None, placement=None, expected_load=None, micro_batches: int = 1, sync_free: bool = False):
+                 exchange: str = "nccl", exchange_rows: int | None = None, placement=None, expected_load=None, micro_batches: int = 1, sync_free: bool = False, direct: bool = True):
         super().__init__()
         assert is_glu, "the expert-parallel layer implements GLU experts"
         assert router_scoring in ("softmax", "sigmoid")
@@ -521,18 +570,28 @@ class MoE_B200_EP(nn.Module):
         self.num_shared_experts = num_shared_experts
         assert exchange in ("nccl", "p2p")
         # "p2p": rows move by this package's kernels over peer memory; exchange_rows = capacity of each buffer in rows
-        self.exchange = PeerExchange(self.group, exchange_rows, hidden_size, dtype, torch.device(device)) if exchange == "p2p" else None
+        def buffer_rows(rows: int) -> int:
+            # the padded grouped order needs up to 127 filler rows per local expert on top of the rows themselves
+            return (rows + (128 * self.e_local if direct else 0) + 127) // 128 * 128
+
+        self.exchange = PeerExchange(self.group, buffer_rows(exchange_rows), hidden_size, dtype, torch.device(device)) if exchange == "p2p" else None
         # Pipelining (peer-memory exchange only): the rank's tokens are split into `micro_batches` parts, each with its own
         # exchange buffers and stream, so that the row transfers of one part run while the expert GEMMs of another do.
+        # `direct` (peer-memory exchange): dispatched rows are stored in the receiver's padded grouped order and results are
+        # fetched from there, so the receiving rank runs no sort, no gather pass and needs no host read
         if self.exchange is not None:
             self.exchange.sync_free = sync_free
+            self.exchange.direct = direct
         self.micro_batches = micro_batches if exchange == "p2p" else 1
         self._pipe = None
         if self.micro_batches > 1:
-            rows = ((exchange_rows + self.micro_batches - 1) // self.micro_batches + 127) // 128 * 128
+            rows = buffer_rows((exchange_rows + self.micro_batches - 1) // self.micro_batches)
             self._pipe = [(PeerExchange(self.group, rows, hidden_size, dtype, torch.device(device)), torch.cuda.Stream(device)) for _ in range(self.micro_batches)]
+            sms = torch.cuda.get_device_properties(device).multi_processor_count
             for xc_, _ in self._pipe:
                 xc_.sync_free = sync_free
+                xc_.direct = direct
+                xc_.max_blocks = sms  # the transfers of a slice run beside the other slices' GEMM CTAs: one block per SM
         # every rank draws with the same per-expert seeds on the same kind of device, so shards agree across ranks
         gen_dev = torch.device(device) if device is not None and torch.device(device).type == "cuda" else torch.device("cpu")
 
@@ -556,13 +615,17 @@ class MoE_B200_EP(nn.Module):
             self.shared_c_proj_weight = nn.Parameter(torch.stack([draw((hidden_size, i_s), seed * 100003 + 8 + 2 * s_, std) for s_ in range(num_shared_experts)]).to(device))
 
     def local_experts(self, rows: torch.Tensor, local_ids: torch.Tensor, exchange=None) -> torch.Tensor:
+        """This rank's experts on the rows it received.  `local_ids`: the local expert of every row; with an exchange that
+        places rows directly in the padded grouped order (`exchange.direct`) it is the inclusive expert offsets instead."""
         if self._local_experts_fn is not None:
             return self._local_experts_fn(rows, local_ids, self.c_fc_weight, self.c_proj_weight)
-        from .scattermoe import fused_swiglu_experts
+        from .scattermoe import fused_swiglu_experts, grouped_experts
 
+        exchange = exchange if exchange is not None else self.exchange
+        if exchange is not None and getattr(exchange, "direct", False):
+            return grouped_experts(rows, self.c_fc_weight, self.c_proj_weight, local_ids, exchange.bufs["y"], exchange.bufs["dx"])
         ones = torch.ones(rows.size(0), 1, dtype=rows.dtype, device=rows.device)
         y_out = dx_out = None
-        exchange = exchange if exchange is not None else self.exchange
         if exchange is not None and hasattr(exchange, "peer_ptrs"):  # the kernels write straight into the buffers the other ranks read
             y_out, dx_out = exchange.bufs["y"], exchange.bufs["dx"]
         return fused_swiglu_experts(rows, self.c_fc_weight, self.c_proj_weight, ones, local_ids.view(-1, 1), y_out, dx_out)
@@ -622,7 +685,7 @@ class MoE_B200_EP(nn.Module):
         plans, chain = [], _Chain()
         with torch.no_grad(), _phase("ep_plan"):
             for i, (xc, _) in enumerate(self._pipe):
-                plans.append(_make_plan(selected_experts[bounds[i] : bounds[i + 1]], self.num_experts, self.world, self.rank, xc.group, self.ops, xc.host_rows))
+                plans.append(_make_plan(selected_experts[bounds[i] : bounds[i + 1]], self.num_experts, self.world, self.rank, xc.group, self.ops, xc.host_rows, xc.direct))
                 plans[-1].chain = chain
         for i, (xc, stream) in enumerate(self._pipe):
             lo, hi = bounds[i], bounds[i + 1]
@@ -698,12 +761,14 @@ def parity_selfcheck(group, device, cases=None) -> dict:
 
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     if cases is None:
-        cases = [("fp32_E16_k4_H256_I384", torch.float32, 16, 4, 256, 384, 800, None, 1), ("bf16_E64_k6_H512_I768", torch.bfloat16, 64, 6, 512, 768, 800, None, 1),
-                 ("bf16_E64_k6_H512_I768_strided", torch.bfloat16, 64, 6, 512, 768, 800, "strided", 1),
-                 ("bf16_E64_k6_H512_I768_pipelined3", torch.bfloat16, 64, 6, 512, 768, 800, None, 3),
-                 ("bf16_E64_k6_H512_I768_no_host_read", torch.bfloat16, 64, 6, 512, 768, 800, None, -1)]
+        bf = ("bf16_E64_k6_H512_I768", torch.bfloat16, 64, 6, 512, 768, 800)
+        cases = [("fp32_E16_k4_H256_I384", torch.float32, 16, 4, 256, 384, 800, {}), bf + ({},),
+                 (bf[0] + "_strided",) + bf[1:] + ({"placement": "strided"},),
+                 (bf[0] + "_pipelined3",) + bf[1:] + ({"micro_batches": 3},),
+                 (bf[0] + "_received_order",) + bf[1:] + ({"direct": False},),
+                 (bf[0] + "_received_order_no_host_read",) + bf[1:] + ({"direct": False, "sync_free": True},)]
     report, ok = {}, True
-    for name, dtype, E, k, H, I, T, placement, micro in cases:
+    for name, dtype, E, k, H, I, T, extra in cases:
         if E % world:
             continue
         tol = 1e-5 if dtype == torch.float32 else 1e-2
@@ -713,10 +778,11 @@ def parity_selfcheck(group, device, cases=None) -> dict:
         gs = [torch.randn(c, H, generator=gen) for c in counts]
         x_all, g_all = torch.cat(xs).to(device, dtype), torch.cat(gs).to(device, dtype)
         lo = sum(counts[:rank])
-        for exchange in ("p2p", "nccl") if micro == 1 else ("p2p",):
+        p2p_only = any(key in extra for key in ("micro_batches", "direct", "sync_free"))
+        for exchange in ("p2p",) if p2p_only else ("p2p", "nccl"):
             cap = (sum(counts) * k + 127) // 128 * 128
             layer = MoE_B200_EP(E, k, H, I, swiglu_unchunked_torch, True, False, 0.05, group=group, device=device, dtype=dtype, seed=5,
-                                exchange=exchange, exchange_rows=cap, placement=placement, micro_batches=max(micro, 1), sync_free=micro < 0)
+                                exchange=exchange, exchange_rows=cap, **extra)
             ref = MoE_B200(E, k, H, I, swiglu_unchunked_torch, True, False, 0.05).to(device).to(dtype)
             ref.load_state_dict(layer.full_state_dict())
             x = x_all[lo : lo + counts[rank]].clone().requires_grad_(True)

@@ -416,6 +416,60 @@ class _FusedSwiGLUExperts(torch.autograd.Function):
         return d_x, d_w_fc, d_w_proj, d_rw, None, None, None
 
 
+class _GroupedExperts(torch.autograd.Function):
+    """Experts on rows that already sit in the padded grouped order (every expert's segment starts at a multiple of 128
+    rows, filler rows are zero): no sort, no gather, no un-sort.  `x_rows (cap, H)` and `expert_offsets` (inclusive row
+    counts) describe the input; the output rows `y_rows (cap, H)` have the same order.  `bufs = (y_buf, dx_buf)` may name
+    caller-owned buffers that receive the output and the input gradient (exchange buffers other ranks read from).  This is
+    the local layer of the expert-parallel pass whose dispatch kernel places rows directly in this order."""
+
+    @staticmethod
+    def forward(ctx, x_rows, w_fc, w_proj, expert_offsets, bufs=None, activation=0):
+        y_buf, dx_buf = bufs if bufs is not None else (None, None)
+        cap, H = x_rows.shape
+        E, I2, _ = w_fc.shape
+        I = I2 if activation == ACTIVATIONS["gelu_tanh"] else I2 // 2
+        assert cap % 128 == 0 and w_fc.is_contiguous() and w_proj.is_contiguous() and w_proj.shape == (E, H, I)
+        h = torch.empty(cap, I2, device=x_rows.device, dtype=x_rows.dtype)
+        a = torch.empty(cap, I, device=x_rows.device, dtype=x_rows.dtype)
+        _launch("up_forward", _up_forward, x_rows, w_fc, expert_offsets, None, h, a, activation)
+        y_rows = y_buf if y_buf is not None else torch.empty(cap, H, device=x_rows.device, dtype=x_rows.dtype)
+        _launch("down_forward", _down_forward, a, w_proj, expert_offsets, None, None, y_rows)
+        ctx.save_for_backward(x_rows, w_fc, w_proj, expert_offsets, h, a)
+        ctx.activation, ctx.dx_buf = activation, dx_buf
+        _maybe_check_status(x_rows.device)
+        return y_rows
+
+    @staticmethod
+    def backward(ctx, g_rows):
+        x_rows, w_fc, w_proj, offsets, h, a = ctx.saved_tensors
+        cap, H = x_rows.shape
+        need_x, need_w1, need_w2 = ctx.needs_input_grad[:3]
+        if g_rows.stride(1) != 1 or g_rows.stride(0) != H:
+            g_rows = g_rows.contiguous()
+        d_w_proj = d_w_fc = d_x = dh = None
+        if need_w1 or need_x:
+            dh = torch.empty_like(h)
+            _launch("down_dgrad", _down_dgrad, g_rows, w_proj, offsets, None, h, dh, ctx.activation)
+        if need_w2:
+            d_w_proj = torch.empty_like(w_proj)
+            _launch("down_wgrad", _wgrad, g_rows, None, a, None, offsets, d_w_proj, cap)
+        if need_w1:
+            d_w_fc = torch.empty_like(w_fc)
+            _launch("up_wgrad", _wgrad, dh, None, x_rows, None, offsets, d_w_fc, cap)
+        if need_x:
+            d_x = ctx.dx_buf if ctx.dx_buf is not None else torch.empty(cap, H, device=x_rows.device, dtype=x_rows.dtype)
+            _launch("up_dgrad", _up_dgrad, dh, w_fc, offsets, None, d_x)
+        _maybe_check_status(x_rows.device)
+        return d_x, d_w_fc, d_w_proj, None, None, None
+
+
+def grouped_experts(x_rows, w_fc, w_proj, expert_offsets, y_buf=None, dx_buf=None, activation: str = "swiglu"):
+    """Experts on rows already in the padded grouped order; see `_GroupedExperts`."""
+    bufs = (y_buf, dx_buf) if (y_buf is not None or dx_buf is not None) else None
+    return _GroupedExperts.apply(x_rows, w_fc, w_proj, expert_offsets, bufs, ACTIVATIONS[activation])
+
+
 # a = h[:, :I] * silu(h[:, I:]) / h[:, :I] * sigmoid(h[:, I:]) for gated layers (w_fc (E, 2I, H)); a = gelu_tanh(h) for a plain
 # layer (w_fc (E, I, H))
 ACTIVATIONS = {"swiglu": 0, "glu": 1, "gelu_tanh": 2}

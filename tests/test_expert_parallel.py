@@ -45,6 +45,7 @@ class TorchPeerExchange:
         self.shared, self.cap_rows = shared, cap_rows
         self.bufs = {name: shared[name][self.rank] for name in shared}
         self.backward_reads_pending = False
+        self.direct = False
         self.barriers = 0
         self.skipped = 0
 
@@ -54,7 +55,17 @@ class TorchPeerExchange:
 
     def _dest(self, plan, n):
         d = torch.searchsorted(plan.start[1 : self.world].long().contiguous(), n, right=True)
+        if plan.dest_pos is not None:  # rows go to their place in the receiver's padded grouped order
+            return d, plan.dest_pos.long()[n]
         return d, plan.base.long()[d] + n - plan.start.long()[d]
+
+    def zero_fillers(self, name, plan):
+        counts = torch.diff(plan.local_offsets, prepend=plan.local_offsets.new_zeros(1))
+        seg = 0
+        for c in counts.tolist():
+            pad = (c + 127) // 128 * 128
+            self.bufs[name][seg + c : seg + pad] = 0
+            seg += pad
 
     def push(self, name, src, idx, fan_out, coeff, plan):
         n = torch.arange(plan.ss.numel())
@@ -71,11 +82,25 @@ class TorchPeerExchange:
     def pull(self, name, gates, out, expanded, plan):
         T, k = out.size(0), plan.k
         d, pos = self._dest(plan, plan.inv)
-        rows = torch.stack([self.shared[name][int(di)][int(pi)] for di, pi in zip(d.tolist(), pos.tolist())]) if d.numel() else out.new_zeros(0, out.size(1))
+        zero = out.new_zeros(out.size(1))  # a row that did not fit into the owner's buffer was never stored
+        rows = torch.stack([self.shared[name][int(di)][int(pi)] if pi < self.cap_rows else zero for di, pi in zip(d.tolist(), pos.tolist())]) if d.numel() else out.new_zeros(0, out.size(1))
         if expanded is not None:
             expanded.copy_(rows)
         r3 = rows.view(T, k, -1)
         out.copy_(r3.sum(1) if gates is None else (r3 * gates.view(T, k, 1)).sum(1))
+
+
+def eager_grouped_experts(x_rows, offsets, w_fc, w_proj):
+    """Local experts on rows in the padded grouped order (segments start at multiples of 128 rows)."""
+    counts = torch.diff(offsets, prepend=offsets.new_zeros(1)).tolist()
+    out = torch.zeros(x_rows.size(0), w_proj.size(1), dtype=x_rows.dtype)
+    seg = 0
+    for e, c in enumerate(counts):
+        sel = torch.arange(min(seg, x_rows.size(0)), min(seg + c, x_rows.size(0)))  # clipped where the buffer ends (an overflowing pass is refused later)
+        if sel.numel():
+            out = out.index_add(0, sel, F.linear(kh.swiglu_unchunked_torch(F.linear(x_rows[sel], w_fc[e])), w_proj[e]))
+        seg += (c + 127) // 128 * 128
+    return out
 
 
 def eager_local_experts(rows, local_ids, w_fc, w_proj):
@@ -93,16 +118,17 @@ def free_port():
         return s.getsockname()[1]
 
 
-def worker(rank, world, port, E, k, H, I, T, result_queue, shared=None, cap_rows=0, placement=None):
+def worker(rank, world, port, E, k, H, I, T, result_queue, shared=None, cap_rows=0, placement=None, direct=False):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         torch.manual_seed(0)
         load = [1.0 / (e + 1) for e in range(E)] if placement == "balanced" else None
-        layer = ep.MoE_B200_EP(E, k, H, I, kh.swiglu_unchunked_torch, True, False, 0.05, ops=TorchRowOps, local_experts_fn=eager_local_experts, seed=3,
-                               placement=placement, expected_load=load)
+        layer = ep.MoE_B200_EP(E, k, H, I, kh.swiglu_unchunked_torch, True, False, 0.05, ops=TorchRowOps, seed=3,
+                               local_experts_fn=eager_grouped_experts if direct else eager_local_experts, placement=placement, expected_load=load)
         if shared is not None:
             layer.exchange = TorchPeerExchange(dist.group.WORLD, shared, cap_rows)
+            layer.exchange.direct = direct
         full = kh.MoE_Torch(E, k, H, I, kh.swiglu_unchunked_torch, True, False, 0.05)
         full.load_state_dict(layer.full_state_dict())
         # every rank draws all ranks' tokens so that it can evaluate the single-process layer on the union
@@ -144,16 +170,16 @@ def shared_exchange_buffers(world, cap_rows, H):
     return {name: [torch.zeros(cap_rows, H).share_memory_() for _ in range(world)] for name in ("x", "y", "dy", "dx")}
 
 
-@pytest.mark.parametrize("exchange", ["all_to_all", "peer"])
+@pytest.mark.parametrize("exchange", ["all_to_all", "peer", "peer_direct"])
 @pytest.mark.parametrize("world,E,k,placement", [(2, 8, 2, None), (4, 8, 3, None), (2, 6, 1, None), (4, 8, 2, "strided"), (2, 8, 3, "balanced")])
 def test_expert_parallel_matches_single_process_layer(world, E, k, placement, exchange):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = free_port()
     T, H = 40, 32
-    cap_rows = (T + 3 * world) * k * world  # every row of every rank could land on one rank
-    shared = shared_exchange_buffers(world, cap_rows, H) if exchange == "peer" else None
-    procs = [ctx.Process(target=worker, args=(r, world, port, E, k, H, 48, T, q, shared, cap_rows, placement)) for r in range(world)]
+    cap_rows = (T + 3 * world) * k * world + 128 * (E // world)  # every row of every rank could land on one rank, plus filler rows
+    shared = shared_exchange_buffers(world, cap_rows, H) if exchange != "all_to_all" else None
+    procs = [ctx.Process(target=worker, args=(r, world, port, E, k, H, 48, T, q, shared, cap_rows, placement, exchange == "peer_direct")) for r in range(world)]
     for p in procs:
         p.start()
     results = [q.get(timeout=180) for _ in range(world)]
@@ -165,7 +191,7 @@ def test_expert_parallel_matches_single_process_layer(world, E, k, placement, ex
             assert v < 2e-5, (rank, name, v)
 
 
-def overflow_worker(rank, world, port, q, shared, cap_rows):
+def overflow_worker(rank, world, port, q, shared, cap_rows, direct=False):
     """Exchange buffers too small for the busiest rank: every rank must refuse the pass (no rank may go on to a
     barrier the others never reach), and the rows that did not fit must have been skipped, not written."""
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
@@ -174,8 +200,10 @@ def overflow_worker(rank, world, port, q, shared, cap_rows):
     dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=30))
     try:
         E, k, H, I, T = 4, 2, 16, 24, 24
-        layer = ep.MoE_B200_EP(E, k, H, I, kh.swiglu_unchunked_torch, True, False, 0.05, ops=TorchRowOps, local_experts_fn=eager_local_experts, seed=1)
+        layer = ep.MoE_B200_EP(E, k, H, I, kh.swiglu_unchunked_torch, True, False, 0.05, ops=TorchRowOps, seed=1,
+                               local_experts_fn=eager_grouped_experts if direct else eager_local_experts)
         layer.exchange = TorchPeerExchange(dist.group.WORLD, shared, cap_rows)
+        layer.exchange.direct = direct
         x = torch.randn(T, H, generator=torch.Generator().manual_seed(rank))
         # every token of every rank picks experts 0 and 1: rank 0 receives all 2 * T * world rows
         sel = torch.tensor([[0, 1]]).expand(T, 2).contiguous()
@@ -189,13 +217,14 @@ def overflow_worker(rank, world, port, q, shared, cap_rows):
         dist.destroy_process_group()
 
 
-def test_exchange_overflow_is_refused_by_every_rank_together():
+@pytest.mark.parametrize("direct", [False, True])
+def test_exchange_overflow_is_refused_by_every_rank_together(direct):
     world, cap_rows = 2, 40  # rank 0 would receive 2 * 24 * 2 = 96 rows
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = free_port()
     shared = shared_exchange_buffers(world, cap_rows, 16)
-    procs = [ctx.Process(target=overflow_worker, args=(r, world, port, q, shared, cap_rows)) for r in range(world)]
+    procs = [ctx.Process(target=overflow_worker, args=(r, world, port, q, shared, cap_rows, direct)) for r in range(world)]
     for p in procs:
         p.start()
     results = [q.get(timeout=120) for _ in range(world)]

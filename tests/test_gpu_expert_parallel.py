@@ -36,13 +36,13 @@ def single_rank_group():
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("exchange", ["nccl", "p2p", "p2p_no_host_read", "p2p_pipelined"])
+@pytest.mark.parametrize("exchange", ["nccl", "p2p", "p2p_received_order", "p2p_no_host_read", "p2p_pipelined"])
 @pytest.mark.parametrize("dtype,E,k,H,I,T", [(torch.float32, 8, 2, 128, 256, 300), (torch.bfloat16, 8, 2, 512, 1024, 1000), (torch.bfloat16, 16, 4, 256, 384, 777)])
 def test_single_rank_expert_parallel_matches_single_gpu_layer(single_rank_group, exchange, dtype, E, k, H, I, T):
     dev = torch.device("cuda", 0)
     ep = MoE_B200_EP(E, k, H, I, kh.swiglu_unchunked_torch, True, False, 0.05, group=single_rank_group, device=dev, dtype=dtype, seed=2,
                      exchange=exchange.split("_")[0], exchange_rows=(T * k + 127) // 128 * 128 + 256, sync_free=exchange == "p2p_no_host_read",
-                     micro_batches=2 if exchange == "p2p_pipelined" else 1)
+                     micro_batches=2 if exchange == "p2p_pipelined" else 1, direct=exchange in ("p2p", "p2p_pipelined"))
     ref = kh.MoE_B200(E, k, H, I, kh.swiglu_unchunked_torch, True, False, 0.05).to(dev).to(dtype)
     ref.load_state_dict(ep.full_state_dict())
     g = torch.Generator().manual_seed(3)
@@ -97,4 +97,4 @@ def test_two_rank_exchange_matches_single_gpu_layer():
         assert p.exitcode == 0
     for rank, rep in results:
         assert rep["ok"], (rank, rep)
-        assert len(rep["cases"]) == 8
+        assert len(rep["cases"]) == 9
