@@ -47,7 +47,7 @@ FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_g
 # token count (weights read, weight gradients written) plus a part proportional to it; the two captures give both, and
 # the full-size figure is their extrapolation to the benchmark's token count.
 NCU_TRAFFIC_FIT = {
-    "c2": {"fixed_bytes": 6.581e9, "bytes_per_token": 1.5361e6, "captures": {"4096": 12.873e9, "8192": 19.165e9},
+    "c2": {"fixed_bytes": 7.353e9, "bytes_per_token": 1.3521e6, "captures": {"4096": 12.891e9, "8192": 18.429e9},
            "algorithmic_bytes_at_16384_tokens": 24.1e9},
 }
 
