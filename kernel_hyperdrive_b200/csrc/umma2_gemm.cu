@@ -129,11 +129,6 @@ __device__ __forceinline__ void tc_mma_pair_lh(uint32_t d_tmem, uint32_t a_lo, u
         : "memory");
 }
 
-template <int V>
-struct IntTag {
-    static constexpr int value = V;
-};
-
 // The k loops of the producer and MMA lanes are unrolled over the operand slots of the ring (entered at the ring's
 // current position, Duff's-device style): one thread issues everything, each of its instructions waits for the one
 // before, and with the slot a compile-time constant the barrier and buffer addresses are immediates.  Measured on a
@@ -307,10 +302,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(threads_of(EPI), 1)
             return f_static;
         }
         const uint32_t bar = smem_u32(&ctl.sched_full[f_slot]);
-        if (!mbar_try_wait_cluster(bar, f_phase) && !mbar_wait_cluster(bar, f_phase, abort_flag, p.status, code)) return 0x7fffffff;
-        const int t = *(volatile int*)&ctl.sched_tile[f_slot];
-        if (whole_warp) __syncwarp();
-        if (!whole_warp || lane == 0) mbar_arrive_cluster(lead_sched_empty0 + f_slot * 8);
+        int t;
+        if (rank == 0) {
+            // the leader's own roles: index and barriers are local, CTA-scope ordering suffices (the cluster-scope
+            // forms cost the MMA lane over a thousand clocks per tile)
+            if (!mbar_wait(bar, f_phase, abort_flag, p.status, code)) return 0x7fffffff;
+            t = *(volatile int*)&ctl.sched_tile[f_slot];
+            if (whole_warp) __syncwarp();
+            if (!whole_warp || lane == 0) mbar_arrive(smem_u32(&ctl.sched_empty[f_slot]));
+        } else {
+            if (!mbar_try_wait_cluster(bar, f_phase) && !mbar_wait_cluster(bar, f_phase, abort_flag, p.status, code)) return 0x7fffffff;
+            t = *(volatile int*)&ctl.sched_tile[f_slot];
+            if (whole_warp) __syncwarp();
+            if (!whole_warp || lane == 0) mbar_arrive_cluster(lead_sched_empty0 + f_slot * 8);
+        }
         if (++f_slot == SCHED_SLOTS) {
             f_slot = 0;
             f_phase ^= 1;

@@ -178,6 +178,20 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
         : "memory");
 }
+// The same instruction with the descriptors given as (low, high) words: along the k loop only the 14-bit start-address
+// field in the low word changes (shared memory is below 256 KB, so the field never carries), which keeps the address
+// arithmetic of the issuing lane at one 32-bit add per operand and MMA.
+__device__ __forceinline__ void tc_mma_lh(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                          uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, {%7, %7, %7, %7}, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -222,6 +236,12 @@ __device__ __forceinline__ float round_elem(float v, int is_f16) {
     if (is_f16) return __half2float(__float2half_rn(v));
     return __bfloat162float(__float2bfloat16_rn(v));
 }
+
+// Compile-time integer handed to a generic lambda (selects a code path without a run-time branch in its loop).
+template <int V>
+struct IntTag {
+    static constexpr int value = V;
+};
 
 // ---- tile bookkeeping ----------------------------------------------------------------------------
 struct Tables {

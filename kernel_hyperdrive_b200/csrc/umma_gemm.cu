@@ -199,6 +199,7 @@ int launch_any(UmmaParams& p, const CUtensorMap& ma, const CUtensorMap& mb, cons
 #define B200MOE_STAGES 4
 #endif
 constexpr int STAGES = B200MOE_STAGES;
+static_assert(STAGES == 4 && BK == 64, "the MMA lane writes out four slots and four MMAs per k step");
 constexpr int B_STAGE_BYTES = BN * BK * 2;          // 32 KB
 constexpr int NUM_THREADS = (6 + EPI_WARPS) * 32;   // 448
 constexpr int GATHER_THREADS = 128;
@@ -277,97 +278,146 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             // the router's weight matrix has at most 256 rows: one 128-row box when they fit, else two
             const uint32_t b_bytes = (EPI == EPI_ROUTER && p.N <= 128) ? B_STAGE_BYTES / 2 : B_STAGE_BYTES;
             const uint32_t tx_bytes = (p.a_tma ? A_STAGE_BYTES : 0) + (p.b_tma ? b_bytes : 0);
-            int stage = 0;
+            int slot = 0;  // ring position; `phase` flips when it wraps
             uint32_t phase = 0;
             Tile ti;
-            bool ok = true;
-            for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
-                decode_tile(p, tb, t, ti);
-                for (int ks = 0; ks < ti.ksteps; ++ks) {
-                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 201)) {
-                        ok = false;
-                        break;
+            const uint32_t full0 = smem_u32(&full_bar[0]);
+            const uint32_t empty0 = smem_u32(&empty_bar[0]);
+            const uint32_t sa0 = smem_u32(smem_a), sb0 = smem_u32(smem_b);
+            const bool a_tma = p.a_tma, b_tma = p.b_tma;
+            const bool b_two = EPI != EPI_ROUTER || p.N > 128;
+            // One tile's k loop, unrolled over the ring's slots like the MMA lane's.  MODE 0: K-major operands (one
+            // 64 x 128 box of A, two of B); 1: weight-gradient family (token-major operands, 64 x 64 boxes: two of A,
+            // four of B); 2: B stored MN-major (one box of A, four of B).  `ca`, `cb`, `cb2`: the tile's fixed coordinates;
+            // the other coordinate advances by BK per k step from `ka` / `kb`.
+            auto load_tile = [&](auto mode, const int nk, const int ca, const int cb, const int cb2, int ka, int kb) -> bool {
+                constexpr int MODE = decltype(mode)::value;
+                int ks = 0;
+                for (;;) {
+                    switch (slot) {
+#define B200MOE_LOAD_STEP(S)                                                                                              \
+    case S: {                                                                                                             \
+        if (ks == nk) {                                                                                                   \
+            slot = S;                                                                                                     \
+            return true;                                                                                                  \
+        }                                                                                                                 \
+        if (!mbar_wait(empty0 + S * 8, phase ^ 1, abort_flag, p.status, 201)) return false;                               \
+        constexpr uint32_t bar_off = S * 8, off_a = S * A_STAGE_BYTES, off_b = S * B_STAGE_BYTES;                         \
+        mbar_arrive_expect_tx(full0 + bar_off, tx_bytes);                                                                 \
+        if (MODE == 1) {                                                                                                  \
+            if (a_tma) {                                                                                                  \
+                tma_load_2d(sa0 + off_a, &tmap_a, full0 + bar_off, ca, ka);                                               \
+                tma_load_2d(sa0 + off_a + 8192, &tmap_a, full0 + bar_off, ca + 64, ka);                                   \
+            }                                                                                                             \
+            if (b_tma) {                                                                                                  \
+                tma_load_2d(sb0 + off_b, &tmap_b, full0 + bar_off, cb, kb);                                               \
+                tma_load_2d(sb0 + off_b + 8192, &tmap_b, full0 + bar_off, cb + 64, kb);                                   \
+                tma_load_2d(sb0 + off_b + 16384, &tmap_b, full0 + bar_off, cb + 128, kb);                                 \
+                tma_load_2d(sb0 + off_b + 24576, &tmap_b, full0 + bar_off, cb + 192, kb);                                 \
+            }                                                                                                             \
+        } else if (MODE == 2) {                                                                                           \
+            if (a_tma) tma_load_2d(sa0 + off_a, &tmap_a, full0 + bar_off, ka, ca);                                        \
+            if (b_tma) {                                                                                                  \
+                tma_load_2d(sb0 + off_b, &tmap_b, full0 + bar_off, cb, kb);                                               \
+                tma_load_2d(sb0 + off_b + 8192, &tmap_b, full0 + bar_off, cb + 64, kb);                                   \
+                tma_load_2d(sb0 + off_b + 16384, &tmap_b, full0 + bar_off, cb + 128, kb);                                 \
+                tma_load_2d(sb0 + off_b + 24576, &tmap_b, full0 + bar_off, cb + 192, kb);                                 \
+            }                                                                                                             \
+        } else {                                                                                                          \
+            if (a_tma) tma_load_2d(sa0 + off_a, &tmap_a, full0 + bar_off, ka, ca);                                        \
+            if (b_tma) {                                                                                                  \
+                tma_load_2d(sb0 + off_b, &tmap_b, full0 + bar_off, kb, cb);                                               \
+                if (b_two) tma_load_2d(sb0 + off_b + 16384, &tmap_b, full0 + bar_off, kb, cb2);                           \
+            }                                                                                                             \
+        }                                                                                                                 \
+        ka += BK;                                                                                                         \
+        kb += BK;                                                                                                         \
+        ++ks;                                                                                                             \
+    }
+                        B200MOE_LOAD_STEP(0) B200MOE_LOAD_STEP(1) B200MOE_LOAD_STEP(2) B200MOE_LOAD_STEP(3)
+#undef B200MOE_LOAD_STEP
                     }
-                    const uint32_t bar = smem_u32(&full_bar[stage]);
-                    mbar_arrive_expect_tx(bar, tx_bytes);
-                    const uint32_t sa = smem_u32(smem_a + stage * A_STAGE_BYTES);
-                    const uint32_t sb = smem_u32(smem_b + stage * B_STAGE_BYTES);
-                    const int k0 = ks * BK;
-                    if (p.wfam) {
-                        // both operands MN-major: boxes of 64 columns x 64 token rows
-                        int krow = ti.row0 + k0;
-                        if (p.a_tma) {
-#pragma unroll
-                            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &tmap_a, bar, ti.mb * BM + j * 64, krow);
-                        }
-                        if (p.b_tma) {
-#pragma unroll
-                            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tmap_b, bar, ti.nb * BN + j * 64, krow);
-                        }
-                    } else {
-                        if (p.a_tma) tma_load_2d(sa, &tmap_a, bar, k0, ti.row0);  // box 64 x 128
-                        if (p.b_tma) {
-                            if (p.b_mn) {
-                                int krow = ti.e * p.b_rows_per_expert + k0;
-#pragma unroll
-                                for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tmap_b, bar, ti.nb * BN + j * 64, krow);
-                            } else {
-                                int r0, r1;
-                                if (epi_gated_forward(EPI)) {
-                                    r0 = ti.e * p.b_rows_per_expert + ti.nb * 128;
-                                    r1 = r0 + p.swiglu_half;
-                                } else {
-                                    r0 = ti.e * p.b_rows_per_expert + ti.nb * BN;
-                                    r1 = r0 + 128;
-                                }
-                                tma_load_2d(sb, &tmap_b, bar, k0, r0);  // box 64 x 128
-                                if (EPI != EPI_ROUTER || p.N > 128) tma_load_2d(sb + 16384, &tmap_b, bar, k0, r1);
-                            }
-                        }
-                    }
-                    if (++stage == STAGES) {
-                        stage = 0;
-                        phase ^= 1;
-                    }
+                    slot = 0;
+                    phase ^= 1;
                 }
+            };
+            for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+                decode_tile(p, tb, t, ti);
+                bool ok;
+                if (p.wfam) {
+                    // both operands MN-major: boxes of 64 columns x 64 token rows
+                    ok = load_tile(IntTag<1>{}, ti.ksteps, ti.mb * BM, ti.nb * BN, 0, ti.row0, ti.row0);
+                } else if (p.b_mn) {
+                    ok = load_tile(IntTag<2>{}, ti.ksteps, ti.row0, ti.nb * BN, 0, 0, ti.e * p.b_rows_per_expert);
+                } else {
+                    int r0, r1;
+                    if (epi_gated_forward(EPI)) {
+                        r0 = ti.e * p.b_rows_per_expert + ti.nb * 128;
+                        r1 = r0 + p.swiglu_half;
+                    } else {
+                        r0 = ti.e * p.b_rows_per_expert + ti.nb * BN;
+                        r1 = r0 + 128;
+                    }
+                    ok = load_tile(IntTag<0>{}, ti.ksteps, ti.row0, r0, r1, 0, 0);
+                }
+                if (!ok) break;
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            int stage = 0;
+            int slot = 0;  // ring position; `phase` flips when it wraps
             uint32_t phase = 0;
             int acc = 0;
             uint32_t acc_phase = 0;
             Tile ti;
-            bool ok = true;
             const uint32_t a_step = p.a_mn ? 128u : 2u;  // descriptor address units (16 B) per 16-deep MMA
             const uint32_t b_step = p.b_mn ? 128u : 2u;
-            for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
+            const uint64_t adesc0 = make_desc(smem_u32(smem_a), p.a_mn);
+            const uint64_t bdesc0 = make_desc(smem_u32(smem_b), p.b_mn);
+            const uint32_t a_lo0 = (uint32_t)adesc0, a_hi = (uint32_t)(adesc0 >> 32);
+            const uint32_t b_lo0 = (uint32_t)bdesc0, b_hi = (uint32_t)(bdesc0 >> 32);
+            const uint32_t full0 = smem_u32(&full_bar[0]);
+            const uint32_t empty0 = smem_u32(&empty_bar[0]);
+            const uint32_t idesc = p.idesc;
+            // One tile's k loop, unrolled over the ring's slots and entered at the ring position: one thread issues
+            // everything, each of its instructions waits for the one before, and the tensor pipe queues only a few
+            // MMAs, so whatever this lane executes per k step beyond four MMAs, one wait and one commit is idle time of
+            // the pipe (the rolled loop needed about 610 clocks per k step against the pipe's 512).
+            auto mma_tile = [&](const int nk, const uint32_t d_tmem) -> bool {
+                int ks = 0;
+                uint32_t accum = 0;
+                for (;;) {
+                    switch (slot) {
+#define B200MOE_MMA_STEP(S)                                                                                               \
+    case S: {                                                                                                             \
+        if (ks == nk) {                                                                                                   \
+            slot = S;                                                                                                     \
+            return true;                                                                                                  \
+        }                                                                                                                 \
+        if (!mbar_wait(full0 + S * 8, phase, abort_flag, p.status, 203)) return false;                                    \
+        if (p.full_count > 1) tc_fence_after(); /* operands written by the gather warps' cp.async */                     \
+        constexpr uint32_t off_a = S * (A_STAGE_BYTES >> 4), off_b = S * (B_STAGE_BYTES >> 4);                            \
+        tc_mma_lh(d_tmem, a_lo0 + off_a, a_hi, b_lo0 + off_b, b_hi, idesc, accum);                                        \
+        tc_mma_lh(d_tmem, a_lo0 + off_a + a_step, a_hi, b_lo0 + off_b + b_step, b_hi, idesc, 1u);                         \
+        tc_mma_lh(d_tmem, a_lo0 + off_a + 2 * a_step, a_hi, b_lo0 + off_b + 2 * b_step, b_hi, idesc, 1u);                 \
+        tc_mma_lh(d_tmem, a_lo0 + off_a + 3 * a_step, a_hi, b_lo0 + off_b + 3 * b_step, b_hi, idesc, 1u);                 \
+        tc_commit(empty0 + S * 8); /* frees the slot when these MMAs have read it */                                      \
+        accum = 1u;                                                                                                       \
+        ++ks;                                                                                                             \
+    }
+                        B200MOE_MMA_STEP(0) B200MOE_MMA_STEP(1) B200MOE_MMA_STEP(2) B200MOE_MMA_STEP(3)
+#undef B200MOE_MMA_STEP
+                    }
+                    slot = 0;
+                    phase ^= 1;
+                }
+            };
+            for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
                 decode_tile(p, tb, t, ti);
                 if (!mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1, abort_flag, p.status, 202)) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int ks = 0; ks < ti.ksteps; ++ks) {
-                    if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, 203)) {
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after();
-                    uint64_t adesc = make_desc(smem_u32(smem_a + stage * A_STAGE_BYTES), p.a_mn);
-                    uint64_t bdesc = make_desc(smem_u32(smem_b + stage * B_STAGE_BYTES), p.b_mn);
-#pragma unroll
-                    for (int j = 0; j < BK / 16; ++j) {
-                        tc_mma(d_tmem, adesc + (uint64_t)(j * a_step), bdesc + (uint64_t)(j * b_step), p.idesc,
-                               (ks | j) ? 1u : 0u);
-                    }
-                    tc_commit(smem_u32(&empty_bar[stage]));  // frees the stage when these MMAs have read it
-                    if (++stage == STAGES) {
-                        stage = 0;
-                        phase ^= 1;
-                    }
-                }
-                if (!ok) break;
+                if (!mma_tile(ti.ksteps, tmem_base + acc * BN)) break;
                 tc_commit(smem_u32(&tmem_full_bar[acc]));  // accumulator complete
                 if (++acc == 2) {
                     acc = 0;
