@@ -42,21 +42,29 @@ METRIC = "moe_layer_fwd_bwd_tflops"
 UNIT = "TFLOP/s"
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
 
-# dram__bytes_read.sum + dram__bytes_write.sum of the six grouped-GEMM launches of one step, from ncu captures of two
-# small cases (2048 and 4096 tokens of the Mixtral-shaped layer).  The traffic is a part that does not depend on the
-# token count (weights read, weight gradients written) plus a part proportional to it; the two captures give both, and
-# the full-size figure is their extrapolation to the benchmark's token count.
-NCU_TRAFFIC_FIT = {
-    "c2": {"fixed_bytes": 7.353e9, "bytes_per_token": 1.3521e6, "captures": {"4096": 12.891e9, "8192": 18.429e9},
+# dram__bytes_read.sum + dram__bytes_write.sum of the six grouped-GEMM launches of one step, from ncu captures of the
+# Mixtral-shaped layer at three token counts (these two counters are a one-pass capture, so the benchmark's own size
+# could be captured as well).  Other token counts are interpolated between the neighbouring captures.
+NCU_TRAFFIC = {
+    "c2": {"captures": {4096: 13.020e9, 8192: 21.187e9, 16384: 45.623e9},
+           "per_launch_at_16384_tokens": {"up_forward": 5.525e9, "down_forward": 6.864e9, "down_dgrad": 6.347e9, "down_wgrad": 3.134e9,
+                                          "up_wgrad": 7.428e9, "up_dgrad": 16.325e9},
            "algorithmic_bytes_at_16384_tokens": 24.1e9},
 }
 
 
 def ncu_traffic(w):
-    fit = NCU_TRAFFIC_FIT.get(w.name)
-    if not fit:
+    rec = NCU_TRAFFIC.get(w.name)
+    if not rec:
         return None, None
-    return fit["fixed_bytes"] + fit["bytes_per_token"] * w.tokens, fit
+    pts = sorted(rec["captures"].items())
+    if w.tokens in rec["captures"]:
+        return rec["captures"][w.tokens], rec
+    lo = max([p for p in pts if p[0] <= w.tokens] or [pts[0]])
+    hi = min([p for p in pts if p[0] >= w.tokens] or [pts[-1]])
+    if lo == hi:  # outside the captured range: extend the nearest segment
+        lo, hi = (pts[0], pts[1]) if w.tokens < pts[0][0] else (pts[-2], pts[-1])
+    return lo[1] + (hi[1] - lo[1]) * (w.tokens - lo[0]) / (hi[0] - lo[0]), rec
 
 
 def measured_peaks():
@@ -606,7 +614,7 @@ def run_gpu_arm(args, w):
         "roofline": {
             "bound": "tensor", "kernel": "umma2_grouped_kernel (6 launches per step)", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
             "frac": (achieved / peak) if achieved else None, "peak_kind": f"bf16_tflops_sustained of {peak_kind}",
-            "traffic": ncu_traffic(w)[0], "traffic_fit": ncu_traffic(w)[1], "per_launch": m["per_launch"], "gemm_ms_per_step": m["gemm_ms"],
+            "traffic": ncu_traffic(w)[0], "traffic_captures": ncu_traffic(w)[1], "per_launch": m["per_launch"], "gemm_ms_per_step": m["gemm_ms"],
             "phase_ms_per_step": m["phase_ms"],
         },
     }
