@@ -733,7 +733,7 @@ def main():
     ap.add_argument("--no-ep-configs", action="store_true", help="skip the short runs of the other benchmark configurations appended as `ep_configs`")
     ap.add_argument("--ep-config-steps", type=int, default=5)
     ap.add_argument("--no-triton-reference", action="store_true")
-    ap.add_argument("--tile-order", type=int, default=None, choices=[-1, 0, 1], help="row GEMMs: 1 = column blocks of a row tile first, 0 = row tiles of a column block first, -1 = by weight-matrix size (library default)")
+    ap.add_argument("--tile-order", type=int, default=None, choices=[-1, 0, 1, 2], help="row GEMMs: 1 = column blocks of a row tile first, 0 = row tiles of a column block first, 2 = blocks of 8 x 8 tiles, -1 = by weight-matrix size (library default)")
     ap.add_argument("--micro", action="store_true", help="time the row kernels (SwiGLU operator, histogram, routing sort) instead of the layer")
     ap.add_argument("--profile", action="store_true", help="profiling run under ncu: exactly --warmup warm-up steps, no end-to-end and CPU legs; its numbers are not benchmark values")
     args = ap.parse_args()

@@ -63,7 +63,8 @@ extern "C" {
 #define B200MOE_OPT_TILE_VARIANT 2  /* -1 (default): the per-shape tile table decides; otherwise a B200MOE_TILE_* value
                                      * forced on every tensor-core launch whose operands allow it */
 #define B200MOE_OPT_TILE_ORDER 3    /* row GEMMs, order of an expert's tiles: -1 (default) = by the size of the expert's weight
-                                     * matrix; 1 = the column blocks of a row tile first; 0 = the row tiles of a column block first */
+                                     * matrix; 1 = the column blocks of a row tile first; 0 = the row tiles of a column
+                                     * block first; 2 = blocks of 8 x 8 tiles (two-CTA kernel) */
 #define B200MOE_OPT_COUNT 4
 
 /* Tiles of the tensor-core engine and the operations the tile table is keyed on (b200moe_tile_table_lookup).  The table

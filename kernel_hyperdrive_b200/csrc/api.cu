@@ -144,7 +144,7 @@ extern "C" int b200moe_set_option(int option, int value) {
     if (option <= 0 || option >= B200MOE_OPT_COUNT) return B200MOE_ERR_ARG;
     if (option == B200MOE_OPT_DYNAMIC_TILES && (value < 0 || value > 3)) return B200MOE_ERR_ARG;
     if (option == B200MOE_OPT_TILE_VARIANT && (value < -1 || value >= B200MOE_TILE_COUNT)) return B200MOE_ERR_ARG;
-    if (option == B200MOE_OPT_TILE_ORDER && (value < -1 || value > 1)) return B200MOE_ERR_ARG;
+    if (option == B200MOE_OPT_TILE_ORDER && (value < -1 || value > 2)) return B200MOE_ERR_ARG;
     g_options[option].store(value);
     return B200MOE_OK;
 }

@@ -180,6 +180,22 @@ __device__ __forceinline__ void decode_tile2(const UmmaParams& p, const Tables& 
         if (p.nb_inner) {
             pair = local / p.nb_count;
             ti.nb = local - pair * p.nb_count;
+        } else if (p.blocked_rows > 0 && pairs_e * 2 * BM > p.blocked_rows) {
+            // Blocks of 8 row tiles x 8 column blocks, one block after the other: the 64 tiles of a block are handed out
+            // together and share 8 + 8 operand panels (opt-in: tile-order option 2).
+            const int per_brow = 8 * p.nb_count;
+            int pb = local / per_brow;
+            const int nbr = (pairs_e + 7) >> 3;
+            if (pb > nbr - 1) pb = nbr - 1;
+            const int rows_in = min(8, pairs_e - 8 * pb);
+            const int local2 = local - pb * per_brow;
+            const int nbc = (p.nb_count + 7) >> 3;
+            int qb = local2 / (rows_in * 8);
+            if (qb > nbc - 1) qb = nbc - 1;
+            const int local3 = local2 - qb * rows_in * 8;
+            const int q_in = local3 / rows_in;
+            pair = 8 * pb + (local3 - q_in * rows_in);
+            ti.nb = 8 * qb + q_in;
         } else {
             ti.nb = local / pairs_e;
             pair = local - ti.nb * pairs_e;

@@ -25,6 +25,7 @@ struct UmmaParams {
     int Mout;       // W: rows of the output
     int nb_count;   // column blocks
     int nb_inner;   // R: 1 = walk the column blocks of a row tile first (the expert's weight matrix fits L2), 0 = the row tiles of a column block first
+    int blocked_rows;  // R, pair kernel, nb_inner == 0: experts with more rows than this walk their tiles in 8 x 8 blocks (0 = never)
     int mb_count;   // W: row blocks
     int swiglu_half;  // EPI_SWIGLU: I (columns of one half); tiles cover 128 columns of each half
     // operand A (R: activations; W: P)
@@ -130,35 +131,15 @@ __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
 }
 
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-#ifndef B200MOE_STORE_HINT
-#define B200MOE_STORE_HINT 0
-#endif
-__device__ __forceinline__ uint64_t l2_evict_first_policy() {
-    uint64_t pol;
-    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
-    return pol;
-}
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
-#if B200MOE_STORE_HINT
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;" ::"l"((uint64_t)map),
-                 "r"(src), "r"(c0), "r"(c1), "l"(l2_evict_first_policy())
-                 : "memory");
-#else
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"((uint64_t)map), "r"(src),
                  "r"(c0), "r"(c1)
                  : "memory");
-#endif
 }
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
-#if B200MOE_STORE_HINT
-    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3, %4}], [%1], %5;" ::"l"((uint64_t)map),
-                 "r"(src), "r"(c0), "r"(c1), "r"(c2), "l"(l2_evict_first_policy())
-                 : "memory");
-#else
     asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"((uint64_t)map),
                  "r"(src), "r"(c0), "r"(c1), "r"(c2)
                  : "memory");
-#endif
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }

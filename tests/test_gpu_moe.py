@@ -53,6 +53,27 @@ def check(got, ref, tol, what):
         assert err < tol, (what, key, err)
 
 
+@pytest.mark.parametrize("order", [0, 1, 2])
+def test_tile_orders_give_identical_results(order):
+    """The order in which an expert's tiles are walked (row tiles of a column block first, column blocks of a row tile
+    first, blocks of 8 x 8 tiles) changes which cluster computes a tile and when, not the arithmetic of the tile: every
+    output and gradient is bit-identical to the default order.  Twelve row-tile pairs and ten column blocks per expert, so
+    that the 8 x 8 blocks have ragged edges in both directions."""
+    w = synthetic.scaled(W["c2"], hidden=512, intermediate=1280, tokens=12288, routing="normal_logits")
+    case = to_dev(make_case(w, seed=3, dtype=torch.bfloat16), torch.bfloat16)
+    _lib.set_engine(_lib.ENGINE_UMMA)
+    _lib.set_option(_lib.OPT_TILE_VARIANT, _lib.TILE_PAIR_256x256)
+    try:
+        ref = run_fused(case)
+        _lib.set_option(_lib.OPT_TILE_ORDER, order)
+        got = run_fused(case)
+    finally:
+        _lib.set_option(_lib.OPT_TILE_ORDER, -1)
+        _lib.set_option(_lib.OPT_TILE_VARIANT, -1)
+    for key in ref:
+        assert torch.equal(got[key], ref[key]), (order, key)
+
+
 @pytest.mark.parametrize("name", list(SMALL))
 @pytest.mark.parametrize("engine,dtype", [("simt", torch.float32), ("simt", torch.bfloat16), ("umma", torch.bfloat16), ("umma", torch.float16), ("umma1", torch.bfloat16)])
 def test_fused_experts_match_oracle(name, engine, dtype):
