@@ -65,7 +65,10 @@ extern "C" {
 #define B200MOE_OPT_TILE_ORDER 3    /* row GEMMs, order of an expert's tiles: -1 (default) = by the size of the expert's weight
                                      * matrix; 1 = the column blocks of a row tile first; 0 = the row tiles of a column
                                      * block first; 2 = blocks of 8 x 8 tiles (two-CTA kernel) */
-#define B200MOE_OPT_COUNT 4
+#define B200MOE_OPT_SM_LIMIT 4      /* 0 (default) = the tensor-core GEMM launches use every SM; n > 0 = at most n SMs, which
+                                     * leaves the others to kernels queued on other streams (the expert-parallel
+                                     * transfers: a persistent GEMM grid otherwise holds every SM until it ends) */
+#define B200MOE_OPT_COUNT 5
 
 /* Tiles of the tensor-core engine and the operations the tile table is keyed on (b200moe_tile_table_lookup).  The table
  * plays the part of the reference's autotuner configurations, which are keyed on the same quantities

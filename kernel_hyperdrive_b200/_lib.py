@@ -22,7 +22,7 @@ HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(PKG_DIR, "..", "includ
 
 F32, BF16, F16 = 0, 1, 2
 ENGINE_AUTO, ENGINE_SIMT, ENGINE_UMMA, ENGINE_UMMA_1CTA, ENGINE_UMMA_GATHER4 = 0, 1, 2, 3, 4
-OPT_DYNAMIC_TILES, OPT_TILE_VARIANT, OPT_TILE_ORDER = 1, 2, 3
+OPT_DYNAMIC_TILES, OPT_TILE_VARIANT, OPT_TILE_ORDER, OPT_SM_LIMIT = 1, 2, 3, 4
 TILE_PAIR_256x256, TILE_CTA_128x256 = 0, 1
 OP_UP_FORWARD, OP_ROW_STORE, OP_DOWN_DGRAD, OP_WGRAD = 0, 1, 2, 3
 DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}

@@ -11,7 +11,7 @@ namespace b200moe {
 static thread_local char g_detail[512] = "";
 static std::atomic<int64_t> g_launches{0};
 static std::atomic<int> g_engine{B200MOE_ENGINE_AUTO};
-static std::atomic<int> g_options[B200MOE_OPT_COUNT] = {{0}, {2}, {-1}, {-1}};  // index = option id; [0] unused
+static std::atomic<int> g_options[B200MOE_OPT_COUNT] = {{0}, {2}, {-1}, {-1}, {0}};  // index = option id; [0] unused
 
 void set_error_detail(const char* fmt, ...) {
     va_list ap;
@@ -145,6 +145,7 @@ extern "C" int b200moe_set_option(int option, int value) {
     if (option == B200MOE_OPT_DYNAMIC_TILES && (value < 0 || value > 3)) return B200MOE_ERR_ARG;
     if (option == B200MOE_OPT_TILE_VARIANT && (value < -1 || value >= B200MOE_TILE_COUNT)) return B200MOE_ERR_ARG;
     if (option == B200MOE_OPT_TILE_ORDER && (value < -1 || value > 2)) return B200MOE_ERR_ARG;
+    if (option == B200MOE_OPT_SM_LIMIT && value < 0) return B200MOE_ERR_ARG;
     g_options[option].store(value);
     return B200MOE_OK;
 }

@@ -712,7 +712,7 @@ int launch2(const UmmaParams& p_in, const CUtensorMap& ma, const CUtensorMap& mb
         set_error_detail("cudaFuncSetAttribute(smem=%d): %s", SMEM_BYTES2, cudaGetErrorString(err));
         return B200MOE_ERR_LAUNCH;
     }
-    int grid = sm_count() & ~1;  // whole pairs
+    int grid = gemm_sm_count() & ~1;  // whole pairs
     UmmaParams p = p_in;
     // With no more tiles than clusters the fixed stride is already the best schedule; otherwise draw tiles dynamically
     // (a counter that cannot be had falls back to the fixed stride).

@@ -624,6 +624,7 @@ int make_store_map(CUtensorMap* map, const void* base, int64_t experts, int64_t 
 int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows, int is_f16);
 int make_gather_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t ld, int is_f16);
 int sm_count();
+int gemm_sm_count();
 uint32_t make_idesc(int a_mn, int b_mn, int is_f16, int m, int n = BN);
 
 // two-CTA kernels (umma2_gemm.cu); operands must all be TMA tiles

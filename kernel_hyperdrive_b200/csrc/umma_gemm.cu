@@ -150,6 +150,12 @@ int sm_count() {
     return cached[dev] > 0 ? cached[dev] : 148;
 }
 
+// SMs a tensor-core GEMM launch may occupy: all of them unless the SM-limit option reserves some for other streams.
+int gemm_sm_count() {
+    const int all = sm_count(), limit = option_value(B200MOE_OPT_SM_LIMIT);
+    return limit > 0 && limit < all ? limit : all;
+}
+
 
 uint32_t make_idesc(int a_mn, int b_mn, int is_f16, int m, int n) {
     uint32_t fmt = is_f16 ? 0u : 1u;
@@ -623,7 +629,7 @@ int launch(const UmmaParams& p, const CUtensorMap& ma, const CUtensorMap& mb, co
         set_error_detail("cudaFuncSetAttribute(smem=%d): %s", SMEM_BYTES, cudaGetErrorString(err));
         return B200MOE_ERR_LAUNCH;
     }
-    kern<<<sm_count(), NUM_THREADS, SMEM_BYTES, stream>>>(p, ma, mb, mo, mo2, mo3);
+    kern<<<gemm_sm_count(), NUM_THREADS, SMEM_BYTES, stream>>>(p, ma, mb, mo, mo2, mo3);
     count_launch();
     return check_launch("umma_grouped_kernel");
 }

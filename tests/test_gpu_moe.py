@@ -74,6 +74,24 @@ def test_tile_orders_give_identical_results(order):
         assert torch.equal(got[key], ref[key]), (order, key)
 
 
+@pytest.mark.parametrize("engine", ["umma", "umma1"])
+def test_sm_limit_keeps_the_results(engine):
+    """GEMM launches restricted to part of the SMs (the rest is left to other streams) compute the same tiles with fewer
+    CTAs: bit-identical outputs and gradients."""
+    w = synthetic.scaled(W["c2"], hidden=512, intermediate=1024, tokens=4096, routing="normal_logits")
+    case = to_dev(make_case(w, seed=5, dtype=torch.bfloat16), torch.bfloat16)
+    _lib.set_engine({"umma": _lib.ENGINE_UMMA, "umma1": _lib.ENGINE_UMMA_1CTA}[engine])
+    try:
+        ref = run_fused(case)
+        _lib.set_option(_lib.OPT_SM_LIMIT, 101)
+        assert _lib.get_option(_lib.OPT_SM_LIMIT) == 101
+        got = run_fused(case)
+    finally:
+        _lib.set_option(_lib.OPT_SM_LIMIT, 0)
+    for key in ref:
+        assert torch.equal(got[key], ref[key]), key
+
+
 @pytest.mark.parametrize("name", list(SMALL))
 @pytest.mark.parametrize("engine,dtype", [("simt", torch.float32), ("simt", torch.bfloat16), ("umma", torch.bfloat16), ("umma", torch.float16), ("umma1", torch.bfloat16)])
 def test_fused_experts_match_oracle(name, engine, dtype):
