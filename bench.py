@@ -283,10 +283,15 @@ class Job:
         if world > 1:
             from kernel_hyperdrive_b200.expert_parallel import MoE_B200_EP
 
-            expected = [float(r + 1) ** -1.2 for r in range(E)] if w.routing == "zipf" else [1.0] * E
+            expected = [1.0] * E
+            if w.routing == "zipf":
+                # The skew is a property of the routing distribution: experts are placed by their expected load, as a
+                # deployment would from running token counts.  The counts come from a separate sample of the same
+                # distribution (other seed, 16384 tokens; the same on every rank): the k distinct experts of a token are
+                # drawn without replacement, so the popular experts saturate and the loads are flatter than p ~ rank^-1.2.
+                _, sample = synthetic.make_routing(synthetic.scaled(w, tokens=16384), torch.zeros(16384, 1), None, 987)
+                expected = torch.bincount(sample.flatten(), minlength=E).double().add_(1.0).tolist()
             if placement is None and w.routing == "zipf":
-                # the skew is a property of the routing distribution (p ~ rank^-1.2): experts are placed by their expected
-                # load, as a deployment would from running token counts
                 placement = "balanced"
             self.placement_note = placement or "contiguous"
             rows = (2 if (w.routing != "zipf" or placement == "balanced") else world) * T * k
