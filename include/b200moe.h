@@ -363,6 +363,19 @@ int b200moe_ep_pull_combine_at(const void* const* peer_ptrs, const int64_t* inv,
 int b200moe_zero_filler_rows(void* buf, int64_t ld, const int64_t* expert_offsets, int E, int width, int64_t cap_rows, int dtype,
                              b200moe_stream_t stream);
 
+/* Placement plan of the direct exchange: everything a rank derives from the all-gathered expert counts of a pass, in one
+ * launch.  counts_all: device int32 (R * E), entry s * E + e = rows that rank s routes to expert slot e (rank r owns the
+ * slots [r * E / R, (r + 1) * E / R)).  sorted_scattered_idxs: this rank's M routed rows in expert order (b200moe_route).
+ * Outputs (device): start (R + 1) and base (R) as b200moe_ep_push_rows takes them; dest_pos (M): the row every sorted row
+ * occupies in its owner's padded grouped order (segments of ceil128(rows of the expert over all sources), sources in rank
+ * order inside a segment); local_offsets (E / R, int64): inclusive offsets of this rank's experts over everything it
+ * receives; summary (2, int64): rows this rank receives, and the most padded rows any rank's buffers must hold (the same
+ * on every rank: the collective overflow decision); inverse (M, int64): inverse[sorted_scattered_idxs[i]] = i.
+ * R * E <= 4096.  No counterpart in the reference (it has no multi-GPU path). */
+int b200moe_ep_plan(const int32_t* counts_all, const int64_t* sorted_scattered_idxs, int R, int rank, int E, int64_t M,
+                    int32_t* start, int32_t* base, int32_t* dest_pos, int64_t* local_offsets, int64_t* summary, int64_t* inverse,
+                    b200moe_stream_t stream);
+
 /* Rank barrier on the stream, over a symmetric flag array: flag_ptrs is a HOST array of R device pointers, entry d being
  * rank d's array of R int32 words (zero before the first barrier), mapped into this process.  `epoch` is the number of
  * this barrier (1, 2, 3, ... the same on every rank).  The kernel publishes the epoch to every peer and waits, for at most

@@ -129,6 +129,7 @@ def _declare(lib):
         "b200moe_ep_push_rows_at": (i32, [vp, i64, vp, i32, vp, vp, vp, vp, vp, i32, i64, i32, i64, i32, i32, vp, vp]),
         "b200moe_ep_pull_combine_at": (i32, [vp, vp, vp, vp, vp, i32, i64, i32, vp, vp, i64, vp, i64, i32, i32, i32, vp]),
         "b200moe_zero_filler_rows": (i32, [vp, i64, vp, i32, i32, i64, i32, vp]),
+        "b200moe_ep_plan": (i32, [vp, vp, i32, i32, i32, i64, vp, vp, vp, vp, vp, vp, vp]),
         "b200moe_ep_barrier": (i32, [vp, i32, i32, i32, i64, vp, vp]),
         "b200moe_ep_gate_grad": (i32, [vp, i64, vp, i64, vp, i64, i32, i32, i32, vp]),
         "b200moe_up_dgrad": (i32, [vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, i64, i32, vp, vp]),

@@ -364,3 +364,104 @@ extern "C" int b200moe_zero_filler_rows(void* buf, int64_t ld, const int64_t* ex
     count_launch();
     return check_launch("zero_filler_rows");
 }
+
+// ---- placement plan of the direct exchange ------------------------------------------------------------
+// Everything a rank derives from the all-gathered expert counts, in one launch (it replaces about twenty-five small
+// tensor operations per pass, which weigh as much as the expert GEMMs when a rank holds only a few thousand tokens).
+// counts_all[s * E + e]: rows that rank s routes to expert slot e.  Every block rebuilds the small tables in shared
+// memory; the rows are spread over the grid.
+constexpr int kPlanMaxCounts = 4096;  // world * E
+
+__global__ void __launch_bounds__(256) ep_plan_kernel(const int32_t* __restrict__ counts_all, const int64_t* __restrict__ ss, int world,
+                                                       int rank, int E, int64_t M, int32_t* __restrict__ start, int32_t* __restrict__ base,
+                                                       int32_t* __restrict__ dest_pos, int64_t* __restrict__ local_offsets,
+                                                       int64_t* __restrict__ summary, int64_t* __restrict__ inv) {
+    __shared__ int cnt[kPlanMaxCounts];
+    __shared__ int tot[kMaxExperts], before[kMaxExperts], pad_start[kMaxExperts], excl[kMaxExperts];
+    __shared__ int padded_sum[64], to_own[64], base_s[64], recv_s[64];
+    const int e_local = E / world;
+    for (int i = threadIdx.x; i < world * E; i += blockDim.x) cnt[i] = counts_all[i];
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int t = 0, b = 0;
+        for (int s = 0; s < world; ++s) {
+            const int c = cnt[s * E + e];
+            t += c;
+            if (s < rank) b += c;
+        }
+        tot[e] = t;
+        before[e] = b;
+    }
+    __syncthreads();
+    if (threadIdx.x < world) {  // one thread per owner: the padded segments of its experts, and what this rank sends to it
+        const int d = threadIdx.x;
+        int run = 0, own = 0, bs = 0, rc = 0;
+        for (int j = 0; j < e_local; ++j) {
+            const int e = d * e_local + j;
+            pad_start[e] = run;
+            run += (tot[e] + kPadRows - 1) / kPadRows * kPadRows;
+            own += cnt[rank * E + e];
+            bs += before[e];
+            rc += tot[e];
+        }
+        padded_sum[d] = run;
+        to_own[d] = own;
+        base_s[d] = bs;
+        recv_s[d] = rc;
+    }
+    if (threadIdx.x == 32) {  // first sorted row of every expert on this rank
+        int run = 0;
+        for (int e = 0; e < E; ++e) {
+            excl[e] = run;
+            run += cnt[rank * E + e];
+        }
+    }
+    __syncthreads();
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        int run = 0, mx = 0;
+        start[0] = 0;
+        for (int d = 0; d < world; ++d) {
+            run += to_own[d];
+            start[d + 1] = run;
+            base[d] = base_s[d];
+            mx = padded_sum[d] > mx ? padded_sum[d] : mx;
+        }
+        int64_t off = 0;
+        for (int j = 0; j < e_local; ++j) {
+            off += tot[rank * e_local + j];
+            local_offsets[j] = off;
+        }
+        summary[0] = recv_s[rank];  // real rows this rank receives
+        summary[1] = mx;            // most padded rows any rank's buffers must hold
+    }
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < M; i += (int64_t)gridDim.x * blockDim.x) {
+        int lo = 0, hi = E - 1;  // last expert whose first row is <= i (the experts after it that start there are empty)
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (excl[mid] <= i) {
+                lo = mid;
+            } else {
+                hi = mid - 1;
+            }
+        }
+        dest_pos[i] = pad_start[lo] + before[lo] + (int)(i - excl[lo]);
+        inv[ss[i]] = i;
+    }
+}
+
+extern "C" int b200moe_ep_plan(const int32_t* counts_all, const int64_t* sorted_scattered_idxs, int world, int rank, int E, int64_t M,
+                               int32_t* start, int32_t* base, int32_t* dest_pos, int64_t* local_offsets, int64_t* summary, int64_t* inverse,
+                               b200moe_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    B200MOE_REQUIRE(world > 0 && world <= 64 && rank >= 0 && rank < world && E > 0 && E <= kMaxExperts && E % world == 0 &&
+                        world * E <= kPlanMaxCounts && M >= 0 && M < ((int64_t)1 << 31),
+                    B200MOE_ERR_ARG, "ep_plan: bad sizes");
+    B200MOE_REQUIRE(counts_all && start && base && local_offsets && summary && (M == 0 || (sorted_scattered_idxs && dest_pos && inverse)),
+                    B200MOE_ERR_ARG, "ep_plan: NULL pointer");
+    int64_t blocks = (M + 255) / 256;
+    blocks = blocks < 1 ? 1 : blocks > 592 ? 592 : blocks;
+    ep_plan_kernel<<<(int)blocks, 256, 0, stream>>>(counts_all, sorted_scattered_idxs, world, rank, E, M, start, base, dest_pos, local_offsets,
+                                                    summary, inverse);
+    count_launch();
+    return check_launch("ep_plan");
+}

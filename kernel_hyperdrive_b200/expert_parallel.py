@@ -43,6 +43,25 @@ class CudaRowOps:
         return ss, counts
 
     @staticmethod
+    def plan_tables(counts_all: torch.Tensor, ss: torch.Tensor, world: int, rank: int, num_experts: int):
+        """The tables of the direct exchange in one launch (`b200moe_ep_plan`): start, base, dest_pos, local_offsets,
+        summary, inverse permutation.  None when the sizes are outside the kernel's limits."""
+        from . import _lib
+
+        if world * num_experts > 4096 or num_experts > 256 or counts_all.dtype != torch.int32 or ss.dtype != torch.int64:
+            return None
+        dev, M = ss.device, ss.numel()
+        start = torch.empty(world + 1, dtype=torch.int32, device=dev)
+        base = torch.empty(world, dtype=torch.int32, device=dev)
+        dest_pos = torch.empty(M, dtype=torch.int32, device=dev)
+        local_offsets = torch.empty(num_experts // world, dtype=torch.int64, device=dev)
+        summary = torch.empty(2, dtype=torch.int64, device=dev)
+        inv = torch.empty(M, dtype=torch.int64, device=dev)
+        _lib.check(_lib.lib().b200moe_ep_plan(_lib.ptr(counts_all), _lib.ptr(ss), world, rank, num_experts, M, _lib.ptr(start), _lib.ptr(base),
+                                              _lib.ptr(dest_pos), _lib.ptr(local_offsets), _lib.ptr(summary), _lib.ptr(inv), _lib.stream_ptr(dev)), "ep_plan")
+        return start, base, dest_pos, local_offsets, summary, inv
+
+    @staticmethod
     def gather(x: torch.Tensor, idx: torch.Tensor, fan_out: int, coeff: torch.Tensor | None = None) -> torch.Tensor:
         """out[n, :] = x[idx[n] // fan_out, :] * coeff[idx[n]] (coeff optional), one pass."""
         from .ops import group
@@ -329,11 +348,21 @@ def _make_plan(selected_experts, num_experts: int, world: int, rank: int, group,
     plan.k = k
     ss, counts = ops.route(selected_experts.reshape(-1), num_experts, k)
     plan.ss = ss
-    plan.inv = torch.empty_like(ss)
-    plan.inv[ss] = torch.arange(ss.numel(), device=ss.device)
     counts_all = torch.empty(world * num_experts, dtype=counts.dtype, device=counts.device)
     dist.all_gather_into_tensor(counts_all, counts.contiguous(), group=group)
+    fused = ops.plan_tables(counts_all, ss, world, rank, num_experts) if direct and ss.is_cuda and hasattr(ops, "plan_tables") else None
     counts_all = counts_all.view(world, num_experts)
+    if fused is not None:
+        plan.start, plan.base, plan.dest_pos, plan.local_offsets, summary, plan.inv = fused
+        plan._recv_counts, plan._e_local, plan._world = counts_all[:, rank * e_local : (rank + 1) * e_local], e_local, world
+        plan.m_recv, plan.max_recv, plan.local_ids = None, None, None
+        plan._host = host_rows if host_rows is not None else torch.empty(2, dtype=torch.int64).pin_memory()
+        plan._host.copy_(summary, non_blocking=True)
+        plan._event = torch.cuda.Event()
+        plan._event.record()
+        return plan
+    plan.inv = torch.empty_like(ss)
+    plan.inv[ss] = torch.arange(ss.numel(), device=ss.device)
     to_rank = counts_all.view(world, world, e_local).sum(-1)  # [source, destination]
     zero = torch.zeros(1, dtype=torch.int64, device=ss.device)
     plan.start = torch.cat([zero, to_rank[rank].cumsum(0)]).to(torch.int32)

@@ -36,6 +36,43 @@ def single_rank_group():
     dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("world,rank,E", [(1, 0, 8), (2, 1, 8), (4, 2, 64), (8, 0, 256), (8, 7, 128), (16, 5, 256)])
+def test_plan_kernel_matches_the_tensor_formulas(world, rank, E):
+    """`b200moe_ep_plan` (one launch) against the same tables written as tensor operations: counts of several ranks with
+    empty experts, bit-exact."""
+    from kernel_hyperdrive_b200.expert_parallel import CudaRowOps
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(world * 1000 + rank * 10 + E)
+    counts_all = torch.randint(0, 300, (world, E), generator=g, dtype=torch.int32)
+    counts_all[torch.rand(world, E, generator=g) < 0.2] = 0  # empty experts
+    counts_all[:, E // 2] = 0
+    M = int(counts_all[rank].sum())
+    ss = torch.randperm(M, generator=g)
+    counts_all, ss = counts_all.to(dev), ss.to(dev)
+    start, base, dest_pos, local_offsets, summary, inv = CudaRowOps.plan_tables(counts_all.reshape(-1).contiguous(), ss, world, rank, E)
+    _lib.check_status(dev)
+
+    e_local = E // world
+    ca = counts_all.long()
+    to_rank = ca.view(world, world, e_local).sum(-1)
+    assert torch.equal(start.long(), torch.cat([torch.zeros(1, dtype=torch.long, device=dev), to_rank[rank].cumsum(0)]))
+    assert torch.equal(base.long(), (to_rank.cumsum(0) - to_rank)[rank])
+    total = ca.sum(0)
+    pv = ((total + 127) // 128 * 128).view(world, e_local)
+    pad_start = (pv.cumsum(1) - pv).reshape(-1)
+    before = (ca.cumsum(0) - ca)[rank]
+    own = ca[rank]
+    excl = own.cumsum(0) - own
+    se = torch.repeat_interleave(torch.arange(E, device=dev), own, output_size=M)
+    assert torch.equal(dest_pos.long(), pad_start[se] + before[se] + (torch.arange(M, device=dev) - excl[se]))
+    assert torch.equal(local_offsets, total[rank * e_local : (rank + 1) * e_local].cumsum(0))
+    assert summary.tolist() == [int(to_rank.sum(0)[rank]), int(pv.sum(1).max())]
+    ref_inv = torch.empty_like(ss)
+    ref_inv[ss] = torch.arange(M, device=dev)
+    assert torch.equal(inv, ref_inv)
+
+
 @pytest.mark.parametrize("exchange", ["nccl", "p2p", "p2p_received_order", "p2p_no_host_read", "p2p_pipelined"])
 @pytest.mark.parametrize("dtype,E,k,H,I,T", [(torch.float32, 8, 2, 128, 256, 300), (torch.bfloat16, 8, 2, 512, 1024, 1000), (torch.bfloat16, 16, 4, 256, 384, 777)])
 def test_single_rank_expert_parallel_matches_single_gpu_layer(single_rank_group, exchange, dtype, E, k, H, I, T):
