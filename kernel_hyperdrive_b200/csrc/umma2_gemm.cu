@@ -3,7 +3,7 @@
 //
 // Each CTA stages its own 128 rows of operand A and HALF of operand B (128 of the 256 B rows), so a CTA
 // moves 32 KB per 64-deep k step instead of 48 KB: one third less L2 -> shared-memory traffic and
-// shared-memory read bandwidth per FLOP than the one-CTA kernel, and six pipeline stages fit instead of four.
+// shared-memory read bandwidth per FLOP than the one-CTA kernel, and six operand slots fit instead of four.
 // The accumulator of a CTA's 128 rows lives in that CTA's tensor memory; each CTA runs its own epilogue.
 //
 // Protocol (rank 0 of the pair is the leader):
